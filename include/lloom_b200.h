@@ -1,0 +1,113 @@
+/*
+ * lloom_b200 -- C ABI of the B200 (sm_100a) quantized-weight matmul library.
+ *
+ * This is the boundary a lloom maintainer binds from Rust (`extern "C"`) inside
+ * `QCudaStorage` (lloom-tensor/src/quantized/cuda.rs): plain pointers and sizes,
+ * CUDA stream as `void*` exactly like the launchers it replaces
+ * (candle-kernels/src/ffi.rs).  Every entry point
+ *   - returns an `int` status (0 = ok) instead of the reference's `void`,
+ *   - enqueues on the caller's stream and never synchronises the host,
+ *   - never allocates or frees device memory: scratch comes from the caller
+ *     (`lloom_b200_workspace_bytes`), outputs are caller buffers.
+ *
+ * Arithmetic contract: the CPU path of the reference (`k_quants::matmul`), i.e.
+ * activations quantized to Q8_0 (for Q8_0 weights) or Q8_K (for Q4_K / Q6_K
+ * weights), bit-exact with `BlockQ8_0::from_float` / `BlockQ8K::from_float`;
+ * exact integer block dot products; f32 scale application in the reference's
+ * algebraic form.  Only the f32 summation order across blocks differs.
+ *
+ * dtype codes are the reference's GGUF type ids (lloom-tensor/src/quantized/mod.rs:505-568).
+ * Weight layout is the canonical GGUF block stream, row-major [n][k / block]:
+ * the bytes `QTensor::data()` returns.  Device weight pointers must be 16-byte aligned.
+ */
+#ifndef LLOOM_B200_H
+#define LLOOM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLOOM_B200_VERSION 100
+
+/* GgmlDType ids (mod.rs:505-568): only these are implemented; anything else returns LLOOM_ERR_DTYPE. */
+#define LLOOM_Q8_0 8
+#define LLOOM_Q4_K 12
+#define LLOOM_Q6_K 14
+#define LLOOM_Q8_K 15 /* activation-only */
+
+enum {
+    LLOOM_OK = 0,
+    LLOOM_ERR_DTYPE = 1,     /* unsupported GgmlDType (no fallback exists) */
+    LLOOM_ERR_SHAPE = 2,     /* k not a multiple of the block size, m/n/k <= 0, ldy < n, ... */
+    LLOOM_ERR_ALIGN = 3,     /* pointer alignment (weights 16 B; f32 buffers 4 B; act blocks 4 B) */
+    LLOOM_ERR_NULL = 4,      /* null pointer */
+    LLOOM_ERR_WORKSPACE = 5, /* workspace missing or smaller than lloom_b200_workspace_bytes */
+    LLOOM_ERR_LAUNCH = 6,    /* CUDA reported an error at launch (see lloom_b200_last_cuda_error) */
+    LLOOM_ERR_TIMEOUT = 7,   /* a bounded device-side wait ran out (reported by lloom_b200_device_status) */
+    LLOOM_ERR_DEVICE = 8     /* not an sm_100 device / attribute query failed */
+};
+
+/* Library version (LLOOM_B200_VERSION of the build). */
+int lloom_b200_version(void);
+/* Static description of a status code. */
+const char *lloom_b200_error_string(int status);
+/* The cudaError_t of the last LLOOM_ERR_LAUNCH on this thread (0 if none). */
+int lloom_b200_last_cuda_error(void);
+/* Reads (synchronously) and clears the device-side status word: 0, or LLOOM_ERR_TIMEOUT
+ * when a bounded mbarrier wait inside a kernel gave up.  For tests and post-mortems. */
+int lloom_b200_device_status(int *status_out);
+
+/* GgmlDType::block_size / type_size (mod.rs:663-715): 32|256 elements, 34|144|210|292 bytes; 0 if unsupported. */
+int64_t lloom_b200_block_elems(int dtype);
+int64_t lloom_b200_block_bytes(int dtype);
+/* Activation block type a weight type is dotted with (GgmlType::VecDotType, k_quants.rs:717,1507,2082). */
+int lloom_b200_act_dtype(int w_dtype);
+/* Bytes of one quantized activation row of k elements for this weight type. */
+int64_t lloom_b200_act_row_bytes(int w_dtype, int64_t k);
+
+/* Scratch lloom_b200_qmatmul_fwd needs for an [m,k] x [n,k]^T product (quantized activations
+ * plus the GEMM's per-call planes).  Replaces the grow-only per-device scratch of
+ * fast_mmvq.rs:44-81 / fast_mmq.rs:135-174; the caller owns it.  256-byte aligned. */
+int64_t lloom_b200_workspace_bytes(int w_dtype, int64_t m, int64_t n, int64_t k);
+
+/* Activation quantizer: x f32 [m,k] contiguous -> canonical Q8_0 / Q8_K blocks [m][k/block],
+ * bit-exact with BlockQ8_0::from_float (k_quants.rs:738-767) / BlockQ8K::from_float
+ * (k_quants.rs:2400-2438).  Replaces launch_mmvq_gguf_quantize_q8_1_f32 (ffi.rs:412) and
+ * launch_mmq_quantize_q8_1_* (ffi.rs:424-454), which quantize to Q8_1 instead. */
+int lloom_b200_quantize_act(int w_dtype, const float *x, int64_t m, int64_t k, void *act_blocks, void *stream);
+
+/* Decode GEMV, 1 <= m <= 8: y[r*ldy + c] = vec_dot(W[c], A[r]) for c < n
+ * (GgmlType::vec_dot, k_quants.rs:800-818, 1540-1620, 2115-2172 through matmul :2587-2637).
+ * Replaces launch_mmvq_gguf_{q8_0,q4_k,q6_k}_f32_plain (ffi.rs:217,250,272). */
+int lloom_b200_gemv(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,
+                    int64_t k, int64_t ldy, void *stream);
+
+/* Prefill GEMM, any m >= 1 (meant for m > 8): same result definition as the GEMV
+ * (matmul m > 1 arm, k_quants.rs:2518-2585).  Q4_K runs on tcgen05 tensor cores.
+ * Replaces launch_mmq_gguf_* (ffi.rs:583).  `workspace` as sized by lloom_b200_workspace_bytes. */
+int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,
+                    int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream);
+
+/* QCudaStorage::fwd equivalent (cuda.rs:862-894): quantize x [m,k] f32, then GEMV (m <= 8) or GEMM.
+ * Weight shape [n,k]; y f32 with row stride ldy >= n.  A GPU holding only weight rows
+ * [n0, n0+n) of a larger matrix passes its shard as w_blocks and y + n0 with the full row stride:
+ * per-row arithmetic does not depend on the shard, so sharded == unsharded bit for bit. */
+int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                           int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream);
+
+/* QCudaStorage::dequantize / dequantize_f16 (cuda.rs:647-718; CPU T::to_float k_quants.rs:720-736,
+ * 1747-1774, 2327-2358): elem_count elements (a multiple of the block size) to f32 or f16. */
+int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,
+                          void *stream);
+
+/* QCudaStorage::embedding / get_rows (cuda.rs:225-316, 828-860): out[i, :] = to_float(row ids[i]),
+ * table [rows][hidden/block] blocks, ids u32 on device, out f32 [n_ids, hidden].  Ids >= rows yield zeros. */
+int lloom_b200_get_rows(int dtype, const void *blocks, int64_t rows, int64_t hidden, const uint32_t *ids,
+                        int64_t n_ids, float *out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,70 @@
+"""ctypes binding of the C ABI declared in ``include/lloom_b200.h``.
+
+There is no fallback: if the shared library is missing the import of any compute entry point
+raises, and every non-zero status from the library becomes a ``LloomError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "liblloom_b200.so")
+
+OK, ERR_DTYPE, ERR_SHAPE, ERR_ALIGN, ERR_NULL, ERR_WORKSPACE, ERR_LAUNCH, ERR_TIMEOUT, ERR_DEVICE = range(9)
+
+# Every symbol include/lloom_b200.h declares: (name, restype, argtypes)
+_i64, _vp, _int = C.c_int64, C.c_void_p, C.c_int
+SYMBOLS = [
+    ("lloom_b200_version", _int, []),
+    ("lloom_b200_error_string", C.c_char_p, [_int]),
+    ("lloom_b200_last_cuda_error", _int, []),
+    ("lloom_b200_device_status", _int, [C.POINTER(_int)]),
+    ("lloom_b200_block_elems", _i64, [_int]),
+    ("lloom_b200_block_bytes", _i64, [_int]),
+    ("lloom_b200_act_dtype", _int, [_int]),
+    ("lloom_b200_act_row_bytes", _i64, [_int, _i64]),
+    ("lloom_b200_workspace_bytes", _i64, [_int, _i64, _i64, _i64]),
+    ("lloom_b200_quantize_act", _int, [_int, _vp, _i64, _i64, _vp, _vp]),
+    ("lloom_b200_gemv", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    ("lloom_b200_gemm", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_dequantize", _int, [_int, _vp, _i64, _vp, _int, _vp]),
+    ("lloom_b200_get_rows", _int, [_int, _vp, _i64, _i64, _vp, _i64, _vp, _vp]),
+]
+
+
+class LloomError(RuntimeError):
+    """A non-zero status from the library (the shim maps these to ``Error::Cuda`` on the Rust side)."""
+
+    def __init__(self, status: int, where: str, detail: str = ""):
+        self.status = status
+        super().__init__(f"{where}: status {status} ({detail})")
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m lloom_b200.build` "
+                "(there is no CPU or PyTorch fallback for this library)")
+        L = C.CDLL(LIB_PATH)
+        for name, res, args in SYMBOLS:
+            fn = getattr(L, name)  # AttributeError if the library does not export a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        L = lib()
+        detail = L.lloom_b200_error_string(status).decode()
+        if status == ERR_LAUNCH:
+            detail += f", cudaError {L.lloom_b200_last_cuda_error()}"
+        raise LloomError(status, where, detail)

@@ -1,0 +1,312 @@
+// C ABI of the library (see include/lloom_b200.h).  One translation unit: the kernels live in the
+// headers included below.  No entry point allocates, frees or synchronises.
+#include "common.cuh"
+#include "dequant.cuh"
+#include "gemm_q4k.cuh"
+#include "gemv.cuh"
+#include "quantize_act.cuh"
+
+#include <mutex>
+
+namespace lloom {
+
+static thread_local int t_last_cuda_error = 0;
+
+static int launch_status(cudaError_t e) {
+    if (e == cudaSuccess) return LLOOM_OK;
+    t_last_cuda_error = (int)e;
+    return LLOOM_ERR_LAUNCH;
+}
+
+static bool supported_weight(int dtype) { return dtype == LLOOM_Q8_0 || dtype == LLOOM_Q4_K || dtype == LLOOM_Q6_K; }
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    int cc_major = 0;
+    bool ok = false;
+};
+
+// Per-device attributes, queried once (the reference caches the same facts, fast_mmq.rs device-info cache).
+static int device_info(DeviceInfo &out) {
+    static std::mutex mu;
+    static DeviceInfo cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LLOOM_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo &c = cache[dev];
+    if (!c.ok) {
+        if (cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LLOOM_ERR_DEVICE;
+        if (cudaDeviceGetAttribute(&c.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+            return LLOOM_ERR_DEVICE;
+        if (cudaDeviceGetAttribute(&c.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return LLOOM_ERR_DEVICE;
+        if (c.cc_major != 10) return LLOOM_ERR_DEVICE;  // sm_100a code only
+        c.ok = true;
+    }
+    out = c;
+    return LLOOM_OK;
+}
+
+static int64_t weight_row_bytes(int dtype, int64_t k) {
+    return k / lloom_b200_block_elems(dtype) * lloom_b200_block_bytes(dtype);
+}
+
+// ---- GEMV launch planning ----
+
+template <class Item, int M, int RW>
+static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
+    auto kern = gemv_kernel<Item, M, RW>;
+    static int configured_smem[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_smem[dev] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured_smem[dev] = smem;
+    }
+    kern<<<grid, 32 * (p.n_cwarps + 1), smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <template <int> class Item, int RW>
+static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
+    switch (p.m) {
+    case 1: return launch_gemv_inst<Item<1>, 1, RW>(p, grid, smem, stream);
+    case 2: return launch_gemv_inst<Item<2>, 2, RW>(p, grid, smem, stream);
+    case 3: return launch_gemv_inst<Item<3>, 3, RW>(p, grid, smem, stream);
+    case 4: return launch_gemv_inst<Item<4>, 4, RW>(p, grid, smem, stream);
+    case 5: return launch_gemv_inst<Item<5>, 5, RW>(p, grid, smem, stream);
+    case 6: return launch_gemv_inst<Item<6>, 6, RW>(p, grid, smem, stream);
+    case 7: return launch_gemv_inst<Item<7>, 7, RW>(p, grid, smem, stream);
+    case 8: return launch_gemv_inst<Item<8>, 8, RW>(p, grid, smem, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int RW>
+static cudaError_t launch_gemv_fmt(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
+    switch (p.w_dtype) {
+    case LLOOM_Q8_0: return launch_gemv_m<ItemQ8_0, RW>(p, grid, smem, stream);
+    case LLOOM_Q4_K: return launch_gemv_m<ItemQ4K, RW>(p, grid, smem, stream);
+    case LLOOM_Q6_K: return launch_gemv_m<ItemQ6K, RW>(p, grid, smem, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+static int gemv_launch(int w_dtype, const void *w, const void *act, float *y, int64_t m, int64_t n, int64_t k,
+                       int64_t ldy, cudaStream_t stream) {
+    DeviceInfo di;
+    int rc = device_info(di);
+    if (rc != LLOOM_OK) return rc;
+    GemvParams p;
+    p.w = (const uint8_t *)w;
+    p.act = (const uint8_t *)act;
+    p.y = y;
+    p.ldy = ldy;
+    p.row_bytes = weight_row_bytes(w_dtype, k);
+    p.w_bytes = n * p.row_bytes;
+    p.n = (int)n;
+    p.k = (int)k;
+    p.m = (int)m;
+    p.w_dtype = w_dtype;
+    p.act_bytes = (int)act_plane_bytes(w_dtype, m, k);
+    // Tile shapes, widest first; the first one that leaves room for at least two stages wins.
+    static const int kShapes[][2] = {{8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};  // {consumer warps, rows per warp}
+    const int64_t budget = (int64_t)di.max_smem_optin - 128 - p.act_bytes;
+    for (auto &shape : kShapes) {
+        const int cw = shape[0], rw = shape[1];
+        const int64_t stage = ((int64_t)cw * rw * p.row_bytes + 48 + 127) / 128 * 128;
+        if (budget < 2 * stage) continue;
+        int64_t stages = budget / stage;
+        if (stages > kMaxStages) stages = kMaxStages;
+        p.n_cwarps = cw;
+        p.stages = (int)stages;
+        p.stage_bytes = (int)stage;
+        const int smem = 128 + p.act_bytes + (int)(stages * stage);
+        int grid = di.sm_count;
+        if ((int64_t)grid > n) grid = (int)n;
+        cudaError_t e = (rw == 2) ? launch_gemv_fmt<2>(p, grid, smem, stream) : launch_gemv_fmt<1>(p, grid, smem, stream);
+        return launch_status(e);
+    }
+    return LLOOM_ERR_SHAPE;  // one row of weights plus the activations does not fit in shared memory
+}
+
+static int check_common(int w_dtype, int64_t m, int64_t n, int64_t k) {
+    if (!supported_weight(w_dtype)) return LLOOM_ERR_DTYPE;
+    if (m <= 0 || n <= 0 || k <= 0) return LLOOM_ERR_SHAPE;
+    if (k % lloom_b200_block_elems(w_dtype) != 0) return LLOOM_ERR_SHAPE;
+    if (k % 64 != 0) return LLOOM_ERR_SHAPE;  // kernels work on 64-element items
+    if (m > (1 << 24) || n > (1 << 30) || k > (1 << 24)) return LLOOM_ERR_SHAPE;
+    return LLOOM_OK;
+}
+
+static bool aligned(const void *p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+}  // namespace lloom
+
+using namespace lloom;
+
+extern "C" {
+
+int lloom_b200_version(void) { return LLOOM_B200_VERSION; }
+
+const char *lloom_b200_error_string(int status) {
+    switch (status) {
+    case LLOOM_OK: return "ok";
+    case LLOOM_ERR_DTYPE: return "unsupported GgmlDType (only Q8_0, Q4_K, Q6_K weights)";
+    case LLOOM_ERR_SHAPE: return "bad shape";
+    case LLOOM_ERR_ALIGN: return "misaligned pointer";
+    case LLOOM_ERR_NULL: return "null pointer";
+    case LLOOM_ERR_WORKSPACE: return "workspace missing or too small";
+    case LLOOM_ERR_LAUNCH: return "CUDA launch error";
+    case LLOOM_ERR_TIMEOUT: return "device-side wait timed out";
+    case LLOOM_ERR_DEVICE: return "not an sm_100 device";
+    }
+    return "unknown status";
+}
+
+int lloom_b200_last_cuda_error(void) { return t_last_cuda_error; }
+
+int lloom_b200_device_status(int *status_out) {
+    if (!status_out) return LLOOM_ERR_NULL;
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));
+    if (e != cudaSuccess) return launch_status(e);
+    if (v != 0) {
+        int zero = 0;
+        e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return launch_status(e);
+    }
+    *status_out = v;
+    return LLOOM_OK;
+}
+
+int64_t lloom_b200_block_elems(int dtype) {
+    switch (dtype) {
+    case LLOOM_Q8_0: return QK8_0;
+    case LLOOM_Q4_K: case LLOOM_Q6_K: case LLOOM_Q8_K: return QK_K;
+    }
+    return 0;
+}
+
+int64_t lloom_b200_block_bytes(int dtype) {
+    switch (dtype) {
+    case LLOOM_Q8_0: return Q8_0_BYTES;
+    case LLOOM_Q4_K: return Q4K_BYTES;
+    case LLOOM_Q6_K: return Q6K_BYTES;
+    case LLOOM_Q8_K: return Q8K_BYTES;
+    }
+    return 0;
+}
+
+int lloom_b200_act_dtype(int w_dtype) {
+    switch (w_dtype) {
+    case LLOOM_Q8_0: return LLOOM_Q8_0;
+    case LLOOM_Q4_K: case LLOOM_Q6_K: return LLOOM_Q8_K;
+    }
+    return 0;
+}
+
+int64_t lloom_b200_act_row_bytes(int w_dtype, int64_t k) {
+    const int adt = lloom_b200_act_dtype(w_dtype);
+    if (!adt || k <= 0 || k % lloom_b200_block_elems(adt) != 0) return 0;
+    return k / lloom_b200_block_elems(adt) * lloom_b200_block_bytes(adt);
+}
+
+int64_t lloom_b200_workspace_bytes(int w_dtype, int64_t m, int64_t n, int64_t k) {
+    if (check_common(w_dtype, m, n, k) != LLOOM_OK) return 0;
+    int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
+    return act + gemm_scratch_bytes(w_dtype, m, n, k);
+}
+
+int lloom_b200_quantize_act(int w_dtype, const float *x, int64_t m, int64_t k, void *act_blocks, void *stream) {
+    int rc = check_common(w_dtype, m, 1, k);
+    if (rc != LLOOM_OK) return rc;
+    if (!x || !act_blocks) return LLOOM_ERR_NULL;
+    if (!aligned(x, 16) || !aligned(act_blocks, 4)) return LLOOM_ERR_ALIGN;
+    return launch_status(launch_quantize_act(w_dtype, x, m, k, act_blocks, (cudaStream_t)stream));
+}
+
+int lloom_b200_gemv(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,
+                    int64_t k, int64_t ldy, void *stream) {
+    int rc = check_common(w_dtype, m, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (m > 8 || ldy < n) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !act_blocks || !y) return LLOOM_ERR_NULL;
+    if (!aligned(w_blocks, 16) || !aligned(act_blocks, 4) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    return gemv_launch(w_dtype, w_blocks, act_blocks, y, m, n, k, ldy, (cudaStream_t)stream);
+}
+
+int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,
+                    int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream) {
+    int rc = check_common(w_dtype, m, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (ldy < n) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !act_blocks || !y) return LLOOM_ERR_NULL;
+    if (!aligned(w_blocks, 16) || !aligned(act_blocks, 4) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    const int64_t need = gemm_scratch_bytes(w_dtype, m, n, k);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return LLOOM_ERR_WORKSPACE;
+    if (need > 0 && !aligned(workspace, 256)) return LLOOM_ERR_ALIGN;
+    DeviceInfo di;
+    rc = device_info(di);
+    if (rc != LLOOM_OK) return rc;
+    bool handled = false;
+    rc = gemm_launch(w_dtype, w_blocks, act_blocks, y, m, n, k, ldy, workspace, di.sm_count, di.max_smem_optin,
+                     (cudaStream_t)stream, handled, t_last_cuda_error);
+    if (handled) return rc;
+    // Shapes the tensor-core kernel does not take: slabs of up to 8 activation rows through the GEMV.
+    const int64_t arow = lloom_b200_act_row_bytes(w_dtype, k);
+    for (int64_t r = 0; r < m; r += 8) {
+        const int64_t mm = (m - r < 8) ? (m - r) : 8;
+        rc = gemv_launch(w_dtype, w_blocks, (const uint8_t *)act_blocks + r * arow, y + r * ldy, mm, n, k, ldy,
+                         (cudaStream_t)stream);
+        if (rc != LLOOM_OK) return rc;
+    }
+    return LLOOM_OK;
+}
+
+int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                           int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream) {
+    int rc = check_common(w_dtype, m, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (ldy < n) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !x || !y) return LLOOM_ERR_NULL;
+    const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
+    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
+    if (rc != LLOOM_OK) return rc;
+    if (m <= 8) return gemv_launch(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (cudaStream_t)stream);
+    const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
+    return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
+                           workspace_bytes - act, stream);
+}
+
+int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,
+                          void *stream) {
+    if (!supported_weight(dtype)) return LLOOM_ERR_DTYPE;
+    if (elem_count <= 0 || elem_count % lloom_b200_block_elems(dtype) != 0) return LLOOM_ERR_SHAPE;
+    if (!blocks || !out) return LLOOM_ERR_NULL;
+    if (!aligned(blocks, 16) || !aligned(out, 16)) return LLOOM_ERR_ALIGN;
+    const int64_t threads = elem_count / 4;
+    const unsigned grid = (unsigned)ceil_div64(threads, 256);
+    if (out_is_f16)
+        dequantize_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(dtype, (const uint8_t *)blocks, elem_count, out);
+    else
+        dequantize_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(dtype, (const uint8_t *)blocks, elem_count, out);
+    return launch_status(cudaGetLastError());
+}
+
+int lloom_b200_get_rows(int dtype, const void *blocks, int64_t rows, int64_t hidden, const uint32_t *ids,
+                        int64_t n_ids, float *out, void *stream) {
+    if (!supported_weight(dtype)) return LLOOM_ERR_DTYPE;
+    if (rows <= 0 || hidden <= 0 || n_ids <= 0 || hidden % lloom_b200_block_elems(dtype) != 0) return LLOOM_ERR_SHAPE;
+    if (!blocks || !ids || !out) return LLOOM_ERR_NULL;
+    if (!aligned(blocks, 16) || !aligned(out, 16) || !aligned(ids, 4)) return LLOOM_ERR_ALIGN;
+    const int64_t threads = n_ids * (hidden / 4);
+    get_rows_kernel<<<(unsigned)ceil_div64(threads, 256), 256, 0, (cudaStream_t)stream>>>(
+        dtype, (const uint8_t *)blocks, rows, hidden, weight_row_bytes(dtype, hidden), ids, n_ids, out);
+    return launch_status(cudaGetLastError());
+}
+
+}  // extern "C"
