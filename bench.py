@@ -1,0 +1,386 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight matmul hot path on B200.
+
+Workload (``config.workload``): the Q4_K decode GEMV of the reference's batch-sweep configuration --
+weight [N=14336, K=4096] drawn N(0, 0.02), quantized to Q4_K; activations f32 [M, 4096] drawn N(0, 1),
+quantized to Q8_K on the device.  One *step* is one pass of the hot path (``QMatMul::forward`` =
+activation quantizer + GEMV) over a pool of 16 distinct weight matrices (528 MB, larger than 2x the
+126 MB L2, so every launch streams its weights from HBM).  The headline value is the weight GB/s at
+M = 1: canonical packed weight bytes read per second, whole job.
+
+Printed JSON line: see the keys below; ``roofline`` is the GEMV kernel alone (CUDA events around a graph
+of GEMV launches, same pool), ``e2e`` goes through the public Python API with host buffers, and
+``cpu_baseline`` times the CPU oracle (a restatement of the reference's CPU QMatMul) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N, K = 14336, 4096
+POOL = 16
+Q4K_ROW_BYTES = K // 256 * 144
+WEIGHT_BYTES = N * Q4K_ROW_BYTES  # 33,030,144: algorithmic bytes of one GEMV launch
+SWEEP_M = (1, 2, 4, 8)
+METRIC = "q4k_decode_gemv_weight_GBps"
+
+
+def physical_cores() -> int:
+    try:
+        import psutil
+
+        return psutil.cpu_count(logical=False) or os.cpu_count() or 1
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def synth_weights_f32(seed: int) -> np.ndarray:
+    return np.random.default_rng(seed).standard_normal((N, K)).astype(np.float32) * np.float32(0.02)
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(smax))
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU legs (the only places this file touches oracle/)
+# --------------------------------------------------------------------------------------------------
+
+def cpu_reference_rate(seconds_budget: float = 12.0, copies: int = 8):
+    """Times the CPU oracle's QMatMul (AVX2 arm order, all physical cores) on the same [14336,4096] Q4_K
+    GEMV at M = 1, rotating over `copies` distinct weight buffers so the host LLC cannot hold them."""
+    from oracle import oracle as O
+
+    O.build()
+    cores = physical_cores()
+    w = synth_weights_f32(2)
+    wq = O.quantize(O.Q4_K, w, nthreads=cores)
+    del w
+    pool = [wq.copy() for _ in range(copies)]
+    x = np.random.default_rng(3).standard_normal((1, K)).astype(np.float32)
+    order = O.best_order()
+    for i in range(2):
+        O.matmul(O.Q4_K, x, pool[i], N, order=order, nthreads=cores)
+    t0 = time.perf_counter()
+    launches = 0
+    while True:
+        for wb in pool:
+            O.matmul(O.Q4_K, x, wb, N, order=order, nthreads=cores)
+            launches += 1
+        if time.perf_counter() - t0 > seconds_budget or launches >= 4000:
+            break
+    dt = time.perf_counter() - t0
+    gbps = launches * WEIGHT_BYTES / dt / 1e9
+    kind = "port"
+    sample = (f"{launches} GEMVs (M=1) of the full [14336,4096] Q4_K matrix over {copies} distinct copies, "
+              f"{dt:.1f} s, {'AVX2+FMA' if order == O.ORDER_AVX2 else 'portable'} vec_dot")
+    return gbps, cores, kind, sample, dt / launches * 1e3
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU QMatMul for this path.  The Rust reference cannot be built here
+    (no rustc/cargo), so this times its C restatement in oracle/ on all physical host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = args.steps, args.warmup
+    per_step_budget = 1.5
+    from oracle import oracle as O
+
+    O.build()
+    cores = physical_cores()
+    wq = O.quantize(O.Q4_K, synth_weights_f32(2), nthreads=cores)
+    pool = [wq.copy() for _ in range(8)]
+    x = np.random.default_rng(3).standard_normal((1, K)).astype(np.float32)
+    order = O.best_order()
+
+    def step():
+        # a bounded sample of the workload's step: one GEMV on each of 8 of the 16 pool matrices
+        for wb in pool:
+            O.matmul(O.Q4_K, x, wb, N, order=order, nthreads=cores)
+        return len(pool)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    launches = 0
+    for _ in range(steps):
+        launches += step()
+        if time.perf_counter() - t0 > per_step_budget * steps + 60:
+            break
+    dt = time.perf_counter() - t0
+    value = launches * WEIGHT_BYTES / dt / 1e9
+    sample = f"{launches} GEMVs (M=1) over 8 distinct copies of the [14336,4096] Q4_K matrix per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt / max(steps, 1) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": "C2 Q4_K decode GEMV [14336x4096], M=1", "pool": 8, "l2": "inputs larger than LLC"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    multi = world > 1
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if multi:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    dtype = lb.GgmlDType.Q4K
+    # Two seeded matrices (the C2 and C4 weights), quantized by the library's host quantizer and laid
+    # out as 16 distinct device buffers: distinct memory is what defeats L2, values repeat.
+    base = [Q.quantize_weights_host(synth_weights_f32(seed), dtype) for seed in (2, 6)]
+    pool = [lb.QTensor.from_data(base[i % 2], dtype, (N, K), dev) for i in range(POOL)]
+    mats = [lb.QMatMul.from_qtensor(q) for q in pool]
+    xs_host = {m: torch.from_numpy(np.random.default_rng(3).standard_normal((m, K)).astype(np.float32)).pin_memory()
+               for m in SWEEP_M}
+    xs = {m: xs_host[m].to(dev) for m in SWEEP_M}
+    stream = torch.cuda.Stream(device=dev)
+
+    def fwd_pass(m, outs):
+        for i, mm in enumerate(mats):
+            mm.qtensor.storage.fwd((N, K), xs[m], out=outs[i])
+
+    def gemv_pass(m, act, outs):
+        L = __import__("lloom_b200._lib", fromlist=["lib"]).lib()
+        for i, q in enumerate(pool):
+            rc = L.lloom_b200_gemv(int(dtype), q.device_ptr(), act.data_ptr(), outs[i].data_ptr(), m, N, K, N,
+                                   stream.cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"gemv status {rc}")
+
+    def capture(fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            fn()  # warm (sets kernel attributes, sizes the workspace) before capture
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+        return g
+
+    def time_graph(g, iters, warm):
+        with torch.cuda.stream(stream):
+            for _ in range(warm):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            if multi:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(iters):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if multi:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    results = {}
+    outs = {m: [torch.empty(m, N, dtype=torch.float32, device=dev) for _ in range(POOL)] for m in SWEEP_M}
+    graphs = {}
+    with torch.cuda.stream(stream):
+        for m in SWEEP_M:
+            graphs[m] = capture(lambda m=m: fwd_pass(m, outs[m]))
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_total = time_graph(graphs[1], steps, warmup)
+    clocks = sampler.stop()
+    ms_per_step = ms_total / steps
+    value = world * POOL * WEIGHT_BYTES / (ms_per_step * 1e-3) / 1e9
+
+    sweep = {}
+    for m in SWEEP_M[1:]:
+        it = max(steps // 2, 3)
+        ms = time_graph(graphs[m], it, 3) / it
+        sweep[f"M={m}"] = round(world * POOL * WEIGHT_BYTES / (ms * 1e-3) / 1e9, 1)
+
+    # roofline leg: the GEMV kernel alone over the same pool
+    with torch.cuda.stream(stream):
+        act = Q.quantize_act(dtype, xs[1])
+        g_gemv = capture(lambda: gemv_pass(1, act, outs[1]))
+    it = max(steps, 10)
+    ms_gemv = time_graph(g_gemv, it, 3) / it / POOL  # average launch duration
+    peak, peak_kind = measured_peaks()
+    achieved = WEIGHT_BYTES / (ms_gemv * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": GEMV_DRAM_TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}",
+                "kernel": "gemv_kernel<ItemQ4K<1>,1,RW>", "algorithmic_bytes_per_launch": WEIGHT_BYTES,
+                "us_per_launch": round(ms_gemv * 1e3, 3)}
+
+    # e2e leg: public API, host buffers in, host buffers out, every step
+    y_host = torch.empty(POOL, 1, N, dtype=torch.float32).pin_memory()
+    y_dev = torch.empty(POOL, 1, N, dtype=torch.float32, device=dev)
+    x_dev = torch.empty(1, K, dtype=torch.float32, device=dev)
+
+    def e2e_step():
+        x_dev.copy_(xs_host[1], non_blocking=True)
+        for i, mm in enumerate(mats):
+            mm.qtensor.storage.fwd((N, K), x_dev, out=y_dev[i])
+        y_host.copy_(y_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_steps = max(steps, 5)
+    if multi:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if multi:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * POOL * WEIGHT_BYTES / (e2e_ms * 1e-3) / 1e9
+    status = Q.device_status()
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "i8", "data": "synthetic",
+        "config": {"workload": "C2 Q4_K decode GEMV [14336x4096], M=1: quantize_act + gemv per matrix", "pool": POOL,
+                   "pool_bytes": POOL * WEIGHT_BYTES, "l2": "inputs larger than L2 (16 distinct weight buffers, 528 MB)",
+                   "timing": "CUDA events around CUDA-graph replays on the launching stream",
+                   "multi_gpu": "independent matrices per rank, no collective" if multi else "single GPU"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": 4 * K,
+                "d2h_bytes_per_step": 4 * POOL * N, "ms_per_step": round(e2e_ms, 4)},
+        "gpu_launches": steps * POOL * 2,
+        "roofline": roofline,
+        "sweep_GBps": sweep,
+        "device_status": status,
+    }
+    if rank == 0:
+        if not args.no_cpu and not multi:
+            v, cores, kind, sample, ms = cpu_reference_rate()
+            line["cpu_baseline"] = {"value": round(v, 2), "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample,
+                                    "ms_per_gemv": round(ms, 3)}
+        print(json.dumps(line), flush=True)
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one M=1 GEMV launch on the full [14336,4096] matrix,
+# from the ncu capture summarised in profiles/gemv_q4k_m1.md (None until captured).
+GEMV_DRAM_TRAFFIC_BYTES = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -31,6 +31,18 @@ SYMBOLS = [
     ("lloom_b200_qmatmul_fwd", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_dequantize", _int, [_int, _vp, _i64, _vp, _int, _vp]),
     ("lloom_b200_get_rows", _int, [_int, _vp, _i64, _i64, _vp, _i64, _vp, _vp]),
+    # include/lloom_b200_host.h: C view of the C++ host layer
+    ("lloom_b200_host_last_error", C.c_char_p, []),
+    ("lloom_b200_host_quantize_rows", _int, [_int, _vp, _vp, _i64, _i64, _int]),
+    ("lloom_b200_host_qtensor_quantize", _int, [_int, _vp, _vp, _i64, _i64, _int, _int, C.POINTER(_vp)]),
+    ("lloom_b200_host_qtensor_from_data", _int, [_int, _vp, _vp, _i64, _int, _i64, _i64, C.POINTER(_vp)]),
+    ("lloom_b200_host_qtensor_free", None, [_vp]),
+    ("lloom_b200_host_qtensor_nbytes", _i64, [_vp]),
+    ("lloom_b200_host_qtensor_device_ptr", _vp, [_vp]),
+    ("lloom_b200_host_qtensor_data", _int, [_vp, _vp, _i64]),
+    ("lloom_b200_host_qmatmul_forward", _int, [_vp, _vp, _i64, _vp]),
+    ("lloom_b200_host_qtensor_dequantize", _int, [_vp, _vp, _int]),
+    ("lloom_b200_host_qtensor_embedding", _int, [_vp, _vp, _i64, _vp]),
 ]
 
 

@@ -13,6 +13,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-ffp-contract=off",  # host-side quantizers: strict sequential f32, like the reference
 ]
 
 
@@ -27,7 +28,8 @@ def sources() -> list[str]:
     out = []
     for root, _, files in os.walk(SRC_DIR):
         out += [os.path.join(root, f) for f in files if f.endswith((".cu", ".cuh", ".h", ".hpp", ".cpp"))]
-    out.append(os.path.join(os.path.dirname(_PKG), "include", "lloom_b200.h"))
+    inc = os.path.join(os.path.dirname(_PKG), "include")
+    out += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
     return sorted(out)
 
 

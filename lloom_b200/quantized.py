@@ -214,6 +214,14 @@ class QTensor:
         """``QStorage::from_data`` + ``load_quantized`` (mod.rs:136-223): raw GGUF block bytes to the device."""
         return cls(QCudaStorage.load_quantized(device, data, GgmlDType(dtype)), shape)
 
+    @classmethod
+    def quantize(cls, src, dtype: GgmlDType, device="cuda", nthreads: int = 0) -> "QTensor":
+        """``QTensor::quantize`` (mod.rs:919-938): f32 ``[.., k]`` -> packed blocks on the device.  As in the
+        reference's CUDA slot (cuda.rs:720-741) the weight quantizer runs on the CPU (the library's host
+        layer), then the blocks are uploaded."""
+        return cls.from_data(quantize_weights_host(src, dtype, nthreads), dtype,
+                             tuple(src.shape), device)
+
     def dtype(self) -> GgmlDType:
         return self.storage.dtype()
 
@@ -266,6 +274,27 @@ class QMatMul:
         return self.qtensor.fwd(xs)
 
     __call__ = forward
+
+
+def quantize_weights_host(src, dtype: GgmlDType, nthreads: int = 0) -> np.ndarray:
+    """CPU ``T::from_float`` over the rows of ``src`` through the library's host layer; uint8 [rows, row_bytes]."""
+    import os
+
+    dtype = GgmlDType(dtype)
+    if isinstance(src, torch.Tensor):
+        src = src.detach().to("cpu", torch.float32).numpy()
+    src = np.ascontiguousarray(src, dtype=np.float32)
+    k = src.shape[-1]
+    if dtype not in _WEIGHT_TYPES or k % dtype.block_size() != 0:
+        raise LloomError(_lib.ERR_SHAPE, "quantize", f"cannot quantize shape {src.shape} to {dtype!r}")
+    rows = src.size // k
+    out = np.zeros((rows, k // dtype.block_size() * dtype.type_size()), dtype=np.uint8)
+    L = _lib.lib()
+    rc = L.lloom_b200_host_quantize_rows(int(dtype), src.ctypes.data, out.ctypes.data, rows, k,
+                                         nthreads or (os.cpu_count() or 1))
+    if rc != 0:
+        raise LloomError(rc, "quantize", L.lloom_b200_host_last_error().decode())
+    return out
 
 
 # ---- thin functional access to the individual kernels (used by the parity tests and the bench) ----

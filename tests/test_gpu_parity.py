@@ -1,0 +1,243 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the committed
+golden fixtures.
+
+Tolerances (stated here, used everywhere below):
+  * quantized activation blocks: bit-exact (byte equality).
+  * dequantize / get_rows: bit-exact.
+  * f32 matmul outputs: |got - ref| <= 1e-5 * A, where A is the sum of the magnitudes of the element's
+    per-block f32 terms (the scale a re-ordered f32 summation is bounded by), and plain relative error
+    |got - ref| <= 1e-5 * |ref| for every element that is not a cancellation (|ref| >= A / 32).
+    Only the f32 summation order across blocks differs from the reference's AVX2 arm.
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+REL_TOL = 1e-5
+DT_NAMES = {8: "Q8_0", 12: "Q4K", 14: "Q6K"}
+
+
+@pytest.fixture(scope="module")
+def dev(cuda_lib):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def assert_matmul_close(got, ref, absum, what=""):
+    got, ref, absum = np.asarray(got, np.float64), np.asarray(ref, np.float64), np.asarray(absum, np.float64)
+    assert got.shape == ref.shape
+    err = np.abs(got - ref)
+    scaled = err / np.maximum(absum, 1e-30)
+    assert scaled.max() <= REL_TOL, f"{what}: max |err|/A = {scaled.max():.3e}"
+    solid = np.abs(ref) >= absum / 32
+    if solid.any():
+        rel = err[solid] / np.abs(ref[solid])
+        assert rel.max() <= REL_TOL, f"{what}: max relative error {rel.max():.3e}"
+
+
+def make_case(oracle, dt, n, k, m, seed, sigma_w=0.02):
+    rng = np.random.default_rng(seed)
+    w = rng.standard_normal((n, k)).astype(np.float32) * np.float32(sigma_w)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    wq = oracle.quantize(dt, w, nthreads=8)
+    return w, x, wq
+
+
+def run_fwd(dev, dt, wq, n, k, x):
+    import lloom_b200 as lb
+
+    qt = lb.QTensor.from_data(wq.tobytes(), dt, (n, k), dev)
+    y = lb.QMatMul.from_qtensor(qt).forward(torch.from_numpy(x).to(dev))
+    torch.cuda.synchronize()
+    return y.cpu().numpy()
+
+
+def test_golden_fixtures(dev):
+    """Committed vectors: activation blocks byte-equal, outputs within tolerance, through the C ABI."""
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+
+    z = np.load(os.path.join(HERE, "golden", "qmatmul_small.npz"))
+    for key in [k[:-2] for k in z.files if k.endswith("_w")]:
+        dt, n, k, m = [int(v) for v in z[key + "_meta"]]
+        xt = torch.from_numpy(z[key + "_x"]).to(dev)
+        aq = Q.quantize_act(lb.GgmlDType(dt), xt)
+        np.testing.assert_array_equal(aq.cpu().numpy(), z[key + "_aq"], err_msg=key)
+        got = run_fwd(dev, dt, z[key + "_wq"], n, k, z[key + "_x"])
+        assert_matmul_close(got, z[key + "_y"], z[key + "_absum"], key)
+    assert Q.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [8, 12, 14])
+def test_activation_quantizer_bit_exact(dev, oracle, dt):
+    """Seeded normals plus adversarial rows: ties, zeros, denormals, huge values, infinities, NaN."""
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+
+    rng = np.random.default_rng(100 + dt)
+    k = 2048
+    rows = [rng.standard_normal(k).astype(np.float32) for _ in range(6)]
+    rows.append(np.zeros(k, np.float32))
+    t = np.zeros(k, np.float32); t[5], t[300], t[301], t[700] = 3.0, -3.0, 3.0, -3.0  # magnitude ties
+    rows.append(t)
+    t = np.zeros(k, np.float32); t[::2] = -1.5; t[1::2] = 1.5  # every element ties; first is negative
+    rows.append(t)
+    rows.append((rng.standard_normal(k) * 1e-41).astype(np.float32))  # denormals
+    rows.append((rng.standard_normal(k) * 1e37).astype(np.float32))   # near overflow
+    h = (rng.integers(-254, 255, k) / 2.0).astype(np.float32)          # exact .5 rounding cases
+    h[0] = 127.0
+    rows.append(h)
+    s = rng.standard_normal(k).astype(np.float32); s[3] = np.inf; s[900] = -np.inf
+    rows.append(s)
+    s = rng.standard_normal(k).astype(np.float32); s[17] = np.nan
+    rows.append(s)
+    x = np.stack(rows)
+    with np.errstate(all="ignore"):
+        ref = oracle.quantize_act(dt, x)
+    got = Q.quantize_act(lb.GgmlDType(dt), torch.from_numpy(x).to(dev)).cpu().numpy()
+    np.testing.assert_array_equal(got, ref)
+
+
+@pytest.mark.parametrize("dt", [8, 12, 14])
+def test_gemv_exhaustive_small_shapes(dev, oracle, dt):
+    """k in {256,512,768}, n in {1..9,65}, m in 1..8: ragged tiles, partial warps, unaligned rows."""
+    for k in (256, 512, 768):
+        for n in (1, 2, 3, 4, 5, 6, 7, 8, 9, 65):
+            for m in (1, 2, 3, 4, 5, 6, 7, 8):
+                _, x, wq = make_case(oracle, dt, n, k, m, seed=1000 * k + 10 * n + m)
+                ref = oracle.matmul(dt, x, wq, n)
+                absum = oracle.matmul_absum(dt, x, wq, n)
+                got = run_fwd(dev, dt, wq, n, k, x)
+                assert_matmul_close(got, ref, absum, f"{DT_NAMES[dt]} n={n} k={k} m={m}")
+
+
+@pytest.mark.parametrize("dt,n,k", [(8, 8192, 2048), (12, 1792, 4096), (14, 2004, 4096), (12, 512, 14336)])
+@pytest.mark.parametrize("m", [1, 2, 4, 8])
+def test_gemv_config_shapes(dev, oracle, dt, n, k, m):
+    """Row counts and K of the decode configurations (full C1; one 8-GPU shard of C2/C3; the down projection)."""
+    _, x, wq = make_case(oracle, dt, n, k, m, seed=dt * 7 + m)
+    ref = oracle.matmul(dt, x, wq, n, nthreads=8)
+    absum = oracle.matmul_absum(dt, x, wq, n, nthreads=8)
+    got = run_fwd(dev, dt, wq, n, k, x)
+    assert_matmul_close(got, ref, absum, f"{DT_NAMES[dt]} n={n} k={k} m={m}")
+
+
+def test_reference_integer_pattern_inputs(dev, oracle):
+    """Inputs of cpu_prompt_gemm_is_bit_identical_to_decode_rows (quantized_tests.rs:1816-1823): each row
+    of a batch equals the same row run alone, bit for bit, and matches the oracle within tolerance."""
+    for dt in (8, 12, 14):
+        for m in (2, 8, 17, 33):
+            for n in (1, 3, 7, 65):
+                for k in (256, 768):
+                    i = np.arange(m * k, dtype=np.int64)
+                    lhs = (((i * 17 % 211).astype(np.float32) - np.float32(103.0)) / np.float32(73.0)).reshape(m, k)
+                    i = np.arange(n * k, dtype=np.int64)
+                    w = (((i * 31 % 173).astype(np.float32) - np.float32(87.0)) / np.float32(61.0)).reshape(n, k)
+                    wq = oracle.quantize(dt, w)
+                    got = run_fwd(dev, dt, wq, n, k, lhs)
+                    ref = oracle.matmul(dt, lhs, wq, n)
+                    assert_matmul_close(got, ref, oracle.matmul_absum(dt, lhs, wq, n), f"{DT_NAMES[dt]} m={m} n={n} k={k}")
+                    if m <= 8:  # rows of a GEMV batch do not depend on the batch (qmm_batch, :239-275)
+                        alone = np.concatenate([run_fwd(dev, dt, wq, n, k, lhs[r:r + 1]) for r in range(m)])
+                        assert alone.tobytes() == got.tobytes()
+
+
+def test_run_to_run_bit_stable_and_shard_invariant(dev, oracle):
+    """Same launch twice gives identical bits; a row shard computed alone equals the same rows of the
+    full product (what N-sharding across GPUs relies on)."""
+    import lloom_b200 as lb
+
+    for dt, n, k in ((12, 1792, 4096), (14, 1336, 4096), (8, 1024, 2048)):
+        for m in (1, 8):
+            _, x, wq = make_case(oracle, dt, n, k, m, seed=5)
+            a = run_fwd(dev, dt, wq, n, k, x)
+            b = run_fwd(dev, dt, wq, n, k, x)
+            assert a.tobytes() == b.tobytes()
+            g = 8
+            rows = n // g
+            full = torch.empty(m, n, dtype=torch.float32, device=dev)
+            xt = torch.from_numpy(x).to(dev)
+            for r in range(g):
+                shard = lb.QCudaStorage.load_quantized(dev, wq[r * rows:(r + 1) * rows].tobytes(), lb.GgmlDType(dt))
+                shard.fwd((rows, k), xt, out=full, out_col_offset=r * rows)
+            torch.cuda.synchronize()
+            assert full.cpu().numpy().tobytes() == a.tobytes()
+
+
+def test_full_size_properties_q4k(dev, oracle):
+    """C2 at full size [14336, 4096]: linearity in the weights' row order and agreement with the oracle on
+    a row sample (the oracle on all 14336 x 8 outputs would take minutes)."""
+    n, k = 14336, 4096
+    rng = np.random.default_rng(2)
+    w = rng.standard_normal((n, k)).astype(np.float32) * np.float32(0.02)
+    wq = oracle.quantize(12, w, nthreads=8)
+    x = np.random.default_rng(3).standard_normal((8, k)).astype(np.float32)
+    got = run_fwd(dev, 12, wq, n, k, x)
+    perm = rng.permutation(n)
+    got_perm = run_fwd(dev, 12, np.ascontiguousarray(wq[perm]), n, k, x)
+    assert got_perm.tobytes() == np.ascontiguousarray(got[:, perm]).tobytes()  # rows are independent
+    sample = np.sort(rng.choice(n, 1024, replace=False))
+    ref = oracle.matmul(12, x, np.ascontiguousarray(wq[sample]), len(sample), nthreads=8)
+    absum = oracle.matmul_absum(12, x, np.ascontiguousarray(wq[sample]), len(sample), nthreads=8)
+    assert_matmul_close(got[:, sample], ref, absum, "C2 sample")
+    for m in (1, 2, 4):
+        assert run_fwd(dev, 12, wq, n, k, x[:m]).tobytes() == got[:m].tobytes()
+
+
+@pytest.mark.parametrize("dt", [8, 12, 14])
+def test_dequantize_and_embedding_bit_exact(dev, oracle, dt):
+    """T::to_float parity (f32 and f16) and the embedding gather (run_quantized_embedding, :304-315)."""
+    import lloom_b200 as lb
+
+    i = np.arange(8 * 256, dtype=np.float32)
+    table = (np.sin(i * np.float32(0.003)) * np.float32(0.5) + np.cos(i * np.float32(0.007)) * np.float32(0.25)).astype(np.float32).reshape(8, 256)
+    wq = oracle.quantize(dt, table)
+    qt = lb.QTensor.from_data(wq.tobytes(), dt, (8, 256), dev)
+    ref = oracle.dequantize(dt, wq, 256)
+    deq = qt.dequantize().cpu().numpy()
+    assert deq.tobytes() == ref.tobytes()
+    f16 = qt.dequantize_f16().cpu().numpy()
+    assert f16.tobytes() == ref.astype(np.float16).tobytes()
+    ids = torch.tensor([[3, 1], [3, 7]], dtype=torch.int64, device=dev)
+    emb = qt.embedding(ids).cpu().numpy()
+    assert emb.shape == (2, 2, 256)
+    assert emb.tobytes() == ref[[3, 1, 3, 7]].reshape(2, 2, 256).tobytes()
+    assert qt.data() == wq.tobytes()  # packed byte identity (ggml_file_tests.rs:78-82)
+    # larger random table
+    rng = np.random.default_rng(9)
+    w = rng.standard_normal((300, 1024)).astype(np.float32)
+    wq = oracle.quantize(dt, w, nthreads=8)
+    qt = lb.QTensor.from_data(wq.tobytes(), dt, (300, 1024), dev)
+    assert qt.dequantize().cpu().numpy().tobytes() == oracle.dequantize(dt, wq, 1024).tobytes()
+
+
+def test_fwd_shape_rules_and_errors(dev, oracle):
+    """QTensor::cuda_fwd layout rules (mod.rs:1906-1925): rank >= 2, contiguous, last dim == k; batch dims kept."""
+    import lloom_b200 as lb
+
+    _, x, wq = make_case(oracle, 12, 16, 256, 6, seed=1)
+    qt = lb.QTensor.from_data(wq.tobytes(), 12, (16, 256), dev)
+    mm = lb.QMatMul.from_qtensor(qt)
+    xt = torch.from_numpy(x).to(dev)
+    y3 = mm.forward(xt.reshape(2, 3, 256))
+    assert tuple(y3.shape) == (2, 3, 16)
+    assert y3.reshape(6, 16).cpu().numpy().tobytes() == mm.forward(xt).cpu().numpy().tobytes()
+    with pytest.raises(lb.LloomError, match="only one dimension"):
+        mm.forward(xt[0])
+    with pytest.raises(lb.LloomError, match="incompatible"):
+        mm.forward(torch.zeros(2, 512, device=dev))
+    with pytest.raises(lb.LloomError, match="not contiguous"):
+        mm.forward(torch.zeros(256, 2, device=dev).t())
+    with pytest.raises(lb.LloomError):
+        lb.QTensor.from_data(wq.tobytes(), 12, (16, 250), dev)
+    # f16 input widens to f32, output returns in f16 (the CPU f16 arm, k_quants.rs:2802-2835)
+    yh = mm.forward(xt.half())
+    assert yh.dtype == torch.float16
+    ref = mm.forward(xt.half().float()).half()
+    assert yh.cpu().numpy().tobytes() == ref.cpu().numpy().tobytes()
