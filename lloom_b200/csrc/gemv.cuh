@@ -1,34 +1,47 @@
 // Decode GEMV (1 <= M <= 8) over canonical GGUF block rows, HBM-bound by design.
 //
-// One persistent CTA per SM.  A producer warp streams tiles of consecutive weight rows (one
-// contiguous byte range of the canonical [n][k/block] stream) into a ring of shared-memory stages
-// with the bulk-async copy engine; consumer warps unpack nibbles / 6-bit codes in registers, take
-// exact integer dot products with dp4a against the quantized activations (held once per CTA in
-// shared memory as aligned planes), apply the block scales in f32 in the reference's algebraic form
-// and reduce with warp shuffles.  Per-row arithmetic never depends on the row's position in a tile
-// or on n, so any row shard of a matrix gives bit-identical rows.
+// One persistent CTA per SM, each owning an equal contiguous range of weight rows.  A producer warp
+// streams tiles of consecutive rows (one contiguous byte range of the canonical [n][k/block] stream)
+// into a ring of shared-memory stages with the bulk-async copy engine; consumer warps unpack nibbles
+// / 6-bit codes in registers, take exact integer dot products with dp4a against the quantized
+// activations (held once per CTA in shared memory as aligned planes), apply the block scales in f32
+// in the reference's algebraic form -- one FMA per 256-element superblock (per 32-element block for
+// Q8_0), exactly the reference's granularity -- and reduce across lanes with warp shuffles.
+// Per-row arithmetic never depends on the row's position in a tile or on n, so any row shard of a
+// matrix gives bit-identical rows.
 #pragma once
 
 #include "common.cuh"
 
 namespace lloom {
 
-// Activation planes in shared memory (built by stage_acts from the canonical blocks):
-//   qs    int8  [M][K]            16-byte aligned rows
-//   d     f32   [M][K/32] (Q8_0 acts, f16 scale widened) or [M][K/256] (Q8_K acts)
-//   bsums int16 [M][K/16]         (Q8_K acts only)
+// Activation planes in shared memory, built once per CTA from the canonical blocks:
+//   qs   int8  per unit, padded by 16 bytes so that the lanes of a quarter-warp, one unit apart, hit
+//              distinct banks: Q8_K acts [M][K/256][256+16], Q8_0 acts [M][K/64][64+16]
+//   d    f32   [M][K/32]  (Q8_0 acts: f16 scale widened)   or [M][K/256] (Q8_K acts)
+//   sums int16 [M][K/32]  for Q4_K weights: bsums[2j] + bsums[2j+1] (one per 32-element sub-block)
+//        int16 [M][2][K/256][8] for Q6_K weights: the 16-element bsums, split by superblock half
 struct ActPlanes {
     const int8_t *qs;
     const float *d;
-    const short *bsums;
+    const short *sums;
     int k;
 };
 
+constexpr int kQ8KUnitStride = 256 + 16;
+constexpr int kQ8_0UnitStride = 64 + 16;
+
+__host__ __device__ inline int64_t round16(int64_t v) { return (v + 15) / 16 * 16; }
+
+__host__ __device__ inline int64_t act_qs_bytes(int w_dtype, int64_t m, int64_t k) {
+    return (w_dtype == LLOOM_Q8_0) ? m * (k / 64) * kQ8_0UnitStride : m * (k / 256) * kQ8KUnitStride;
+}
+
 __host__ __device__ inline int64_t act_plane_bytes(int w_dtype, int64_t m, int64_t k) {
-    int64_t qs = m * k;
-    int64_t d = (w_dtype == LLOOM_Q8_0) ? m * (k / 32) * 4 : m * (k / 256) * 4;
-    int64_t bs = (w_dtype == LLOOM_Q8_0) ? 0 : m * (k / 16) * 2;
-    return ((qs + 15) / 16) * 16 + ((d + 15) / 16) * 16 + ((bs + 15) / 16) * 16;
+    const int64_t qs = act_qs_bytes(w_dtype, m, k);
+    const int64_t d = (w_dtype == LLOOM_Q8_0) ? m * (k / 32) * 4 : m * (k / 256) * 4;
+    const int64_t sums = (w_dtype == LLOOM_Q8_0) ? 0 : (w_dtype == LLOOM_Q4_K ? m * (k / 32) * 2 : m * (k / 16) * 2);
+    return round16(qs) + round16(d) + round16(sums);
 }
 
 // Read NWORDS 32-bit words starting at a 2-byte aligned shared-memory address.
@@ -40,192 +53,222 @@ __device__ __forceinline__ void lds_words_unaligned(const uint8_t *p, uint32_t (
     uint32_t prev = wp[0];
 #pragma unroll
     for (int i = 0; i < NWORDS; ++i) {
-        uint32_t next = wp[i + 1];
+        const uint32_t next = wp[i + 1];
         out[i] = __funnelshift_r(prev, next, sh);
         prev = next;
     }
 }
 
+__device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int c) {
+    c = __dp4a((int)a.x, (int)b.x, c);
+    c = __dp4a((int)a.y, (int)b.y, c);
+    c = __dp4a((int)a.z, (int)b.z, c);
+    return __dp4a((int)a.w, (int)b.w, c);
+}
+
 // ---------------------------------------------------------------------------------------------
-// Per-format work items.  An item is 64 consecutive-in-layout elements of one weight row; a lane
-// loads the matching activation bytes once and reuses them for every row it handles.
+// Per-format units.  A unit is the span of one weight row that a single lane owns: one 256-element
+// superblock for the k-quants, two 32-element blocks for Q8_0.  The lane loads the matching
+// activation bytes once and reuses them for the RW rows it handles.  MC = activation rows handled
+// per pass (<= 4 keeps the activation registers bounded; M > 4 takes two passes over the unit).
 // ---------------------------------------------------------------------------------------------
 
-// Q4_K x Q8_K (k_quants.rs:1540-1620, avx.rs:443-525):
+// Q4_K x Q8_K (k_quants.rs:1540-1620, avx.rs:443-525), per superblock:
 //   out += (d_a*d_w) * sum_j sc_j * dot32(q4_j, q8_j)  +  (-d_a*dmin_w) * sum_j m_j * (bsums[2j]+bsums[2j+1])
-// item = (superblock b, 64-group g): sub-blocks 2g (low nibbles) and 2g+1 (high nibbles).
-template <int M>
-struct ItemQ4K {
-    static constexpr int kItemsPerBlock = 4;
-    static constexpr int kBlockBytes = Q4K_BYTES;
-    struct Act {
-        uint4 lo[M][2], hi[M][2];
-        int s0[M], s1[M];
-        float d[M];
-    };
-    __device__ static __forceinline__ void load_act(Act &a, const ActPlanes &p, int item) {
-        const int b = item >> 2, g = item & 3;
+struct FmtQ4K {
+    static constexpr int kUnitElems = 256;
+    template <int MC, int RW>
+    __device__ static __forceinline__ void unit(const ActPlanes &p, int m0, int b, const uint8_t *const (&rowp)[RW],
+                                                const bool (&valid)[RW], float (&acc)[RW][MC]) {
+        // headers of the RW rows: d, dmin and the 6-bit (scale, min) pairs (utils.rs:50-60) unpacked to bytes
+        float dw[RW], dminw[RW];
+        uint32_t scw[RW][2], mnw[RW][2];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const uint4 *q = reinterpret_cast<const uint4 *>(p.qs + (size_t)m * p.k + b * 256 + g * 64);
-            a.lo[m][0] = q[0]; a.lo[m][1] = q[1];
-            a.hi[m][0] = q[2]; a.hi[m][1] = q[3];
-            const short *bs = p.bsums + (size_t)m * (p.k >> 4) + b * 16 + g * 4;
-            a.s0[m] = (int)bs[0] + (int)bs[1];
-            a.s1[m] = (int)bs[2] + (int)bs[3];
-            a.d[m] = p.d[m * (p.k >> 8) + b];
-        }
-    }
-    __device__ static __forceinline__ void row(const uint8_t *rowp, int item, const Act &a, float (&acc)[M]) {
-        const int b = item >> 2, g = item & 3;
-        const uint8_t *blk = rowp + b * Q4K_BYTES;
-        const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
-        const float dw = f16_bits_to_f32(dd & 0xffffu), dminw = f16_bits_to_f32(dd >> 16);
-        // 6-bit (scale, min) pairs of sub-blocks 2g and 2g+1 (utils.rs:50-60), as byte pairs
-        const unsigned short *s16 = reinterpret_cast<const unsigned short *>(blk + 4);
-        const uint32_t X = s16[g + 2];      // scale bytes 2g+4, 2g+5
-        const uint32_t Y = s16[g & 1];      // scale bytes 2g (g<2) or 2g-4 (g>=2)
-        const uint32_t Z = s16[g];          // scale bytes 2g, 2g+1
-        uint32_t scp, mnp;
-        if (g < 2) {
-            scp = Y & 0x3f3fu;
-            mnp = X & 0x3f3fu;
-        } else {
-            scp = (X & 0x0f0fu) | (((Y >> 6) & 0x0303u) << 4);
-            mnp = ((X >> 4) & 0x0f0fu) | (((Z >> 6) & 0x0303u) << 4);
-        }
-        const int sc0 = scp & 0xff, sc1 = scp >> 8, mn0 = mnp & 0xff, mn1 = mnp >> 8;
-        const uint4 *qp = reinterpret_cast<const uint4 *>(blk + 16 + g * 32);
-        const uint4 q0 = qp[0], q1 = qp[1];
-        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        uint32_t ql[8], qh[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            ql[i] = qw[i] & 0x0f0f0f0fu;
-            qh[i] = (qw[i] >> 4) & 0x0f0f0f0fu;
-        }
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const uint32_t al[8] = {a.lo[m][0].x, a.lo[m][0].y, a.lo[m][0].z, a.lo[m][0].w,
-                                    a.lo[m][1].x, a.lo[m][1].y, a.lo[m][1].z, a.lo[m][1].w};
-            const uint32_t ah[8] = {a.hi[m][0].x, a.hi[m][0].y, a.hi[m][0].z, a.hi[m][0].w,
-                                    a.hi[m][1].x, a.hi[m][1].y, a.hi[m][1].z, a.hi[m][1].w};
-            int pl = 0, ph = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                pl = __dp4a((int)ql[i], (int)al[i], pl);
-                ph = __dp4a((int)qh[i], (int)ah[i], ph);
+        for (int r = 0; r < RW; ++r) {
+            if (valid[r]) {
+                const uint4 h = *reinterpret_cast<const uint4 *>(rowp[r] + (size_t)b * Q4K_BYTES);
+                dw[r] = f16_bits_to_f32(h.x & 0xffffu);
+                dminw[r] = f16_bits_to_f32(h.x >> 16);
+                scw[r][0] = h.y & 0x3f3f3f3fu;
+                scw[r][1] = (h.w & 0x0f0f0f0fu) | (((h.y >> 6) & 0x03030303u) << 4);
+                mnw[r][0] = h.z & 0x3f3f3f3fu;
+                mnw[r][1] = ((h.w >> 4) & 0x0f0f0f0fu) | (((h.z >> 6) & 0x03030303u) << 4);
+            } else {
+                dw[r] = dminw[r] = 0.0f;
+                scw[r][0] = scw[r][1] = mnw[r][0] = mnw[r][1] = 0;
             }
-            const int v = sc0 * pl + sc1 * ph;
-            const int mv = mn0 * a.s0[m] + mn1 * a.s1[m];
-            acc[m] = fmaf(__fmul_rn(a.d[m], dw), (float)v, acc[m]);
-            acc[m] = fmaf(__fmul_rn(-a.d[m], dminw), (float)mv, acc[m]);
+        }
+        int S[RW][MC];
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int m = 0; m < MC; ++m) S[r][m] = 0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            uint4 alo[MC][2], ahi[MC][2];
+#pragma unroll
+            for (int m = 0; m < MC; ++m) {
+                const uint4 *q = reinterpret_cast<const uint4 *>(
+                    p.qs + ((size_t)(m0 + m) * (p.k >> 8) + b) * kQ8KUnitStride + g * 64);
+                alo[m][0] = q[0]; alo[m][1] = q[1];
+                ahi[m][0] = q[2]; ahi[m][1] = q[3];
+            }
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                if (!valid[r]) continue;
+                const uint4 *qp = reinterpret_cast<const uint4 *>(rowp[r] + (size_t)b * Q4K_BYTES + 16 + g * 32);
+                const uint4 q0 = qp[0], q1 = qp[1];
+                uint4 l0, l1, h0, h1;
+                l0.x = q0.x & 0x0f0f0f0fu; l0.y = q0.y & 0x0f0f0f0fu; l0.z = q0.z & 0x0f0f0f0fu; l0.w = q0.w & 0x0f0f0f0fu;
+                l1.x = q1.x & 0x0f0f0f0fu; l1.y = q1.y & 0x0f0f0f0fu; l1.z = q1.z & 0x0f0f0f0fu; l1.w = q1.w & 0x0f0f0f0fu;
+                h0.x = (q0.x >> 4) & 0x0f0f0f0fu; h0.y = (q0.y >> 4) & 0x0f0f0f0fu;
+                h0.z = (q0.z >> 4) & 0x0f0f0f0fu; h0.w = (q0.w >> 4) & 0x0f0f0f0fu;
+                h1.x = (q1.x >> 4) & 0x0f0f0f0fu; h1.y = (q1.y >> 4) & 0x0f0f0f0fu;
+                h1.z = (q1.z >> 4) & 0x0f0f0f0fu; h1.w = (q1.w >> 4) & 0x0f0f0f0fu;
+                const int sc_lo = (scw[r][g >> 1] >> (16 * (g & 1))) & 0xff;
+                const int sc_hi = (scw[r][g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
+#pragma unroll
+                for (int m = 0; m < MC; ++m) {
+                    const int pl = dot16(l1, alo[m][1], dot16(l0, alo[m][0], 0));
+                    const int ph = dot16(h1, ahi[m][1], dot16(h0, ahi[m][0], 0));
+                    S[r][m] += sc_lo * pl + sc_hi * ph;
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MC; ++m) {
+            // eight sub-block sums of this superblock, packed 2 x int16 per word
+            const uint4 sp = *reinterpret_cast<const uint4 *>(p.sums + (size_t)(m0 + m) * (p.k >> 5) + b * 8);
+            const float da = p.d[(m0 + m) * (p.k >> 8) + b];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                int mv = __dp2a_lo((int)sp.x, (int)mnw[r][0], 0);
+                mv = __dp2a_hi((int)sp.y, (int)mnw[r][0], mv);
+                mv = __dp2a_lo((int)sp.z, (int)mnw[r][1], mv);
+                mv = __dp2a_hi((int)sp.w, (int)mnw[r][1], mv);
+                acc[r][m] = fmaf(__fmul_rn(da, dw[r]), (float)S[r][m], acc[r][m]);
+                acc[r][m] = fmaf(__fmul_rn(-da, dminw[r]), (float)mv, acc[r][m]);
+            }
         }
     }
 };
 
-// Q6_K x Q8_K (k_quants.rs:2115-2172, avx.rs:131-216):
-//   out += (d_a*d_w) * sum_{j<16} sc_j * dot16(q6_j - 32, q8_j)
-// item = (superblock b, half h, 16 l-values at l0): the four 16-element groups l0 + {0,32,64,96}
-// of the half, each with one scale.  (q6-32).q8 is taken as q6u.q8 - 32*bsum like the AVX2 arm.
-template <int M>
-struct ItemQ6K {
-    static constexpr int kItemsPerBlock = 4;
-    static constexpr int kBlockBytes = Q6K_BYTES;
-    struct Act {
-        uint4 q[M][4];
-        int bs[M][4];
-        float d[M];
-    };
-    __device__ static __forceinline__ void load_act(Act &a, const ActPlanes &p, int item) {
-        const int b = item >> 2, h = (item >> 1) & 1, l0 = (item & 1) * 16;
+// Q6_K x Q8_K (k_quants.rs:2115-2172, avx.rs:131-216), per superblock:
+//   out += (d_a*d_w) * sum_{j<16} sc_j * dot16(q6_j - 32, q8_j),   (q6-32).q8 taken as q6u.q8 - 32*bsum
+struct FmtQ6K {
+    static constexpr int kUnitElems = 256;
+    template <int MC, int RW>
+    __device__ static __forceinline__ void unit(const ActPlanes &p, int m0, int b, const uint8_t *const (&rowp)[RW],
+                                                const bool (&valid)[RW], float (&acc)[RW][MC]) {
+        int S[RW][MC];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const int8_t *base = p.qs + (size_t)m * p.k + b * 256 + h * 128 + l0;
-            const short *bs = p.bsums + (size_t)m * (p.k >> 4) + b * 16 + h * 8 + (l0 >> 4);
+        for (int r = 0; r < RW; ++r)
 #pragma unroll
-            for (int gq = 0; gq < 4; ++gq) {
-                a.q[m][gq] = *reinterpret_cast<const uint4 *>(base + 32 * gq);
-                a.bs[m][gq] = (int)bs[2 * gq];
+            for (int m = 0; m < MC; ++m) S[r][m] = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            // the half's eight 16-element sums and its scales
+            uint4 bsw[MC];
+#pragma unroll
+            for (int m = 0; m < MC; ++m)
+                bsw[m] = *reinterpret_cast<const uint4 *>(p.sums + (((size_t)(m0 + m) * 2 + h) * (p.k >> 8) + b) * 8);
+            uint32_t scw[RW][2];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                scw[r][0] = scw[r][1] = 0;
+                if (valid[r]) lds_words_unaligned<2>(rowp[r] + (size_t)b * Q6K_BYTES + 192 + 8 * h, scw[r]);
             }
-            a.d[m] = p.d[m * (p.k >> 8) + b];
-        }
-    }
-    __device__ static __forceinline__ void row(const uint8_t *rowp, int item, const Act &a, float (&acc)[M]) {
-        const int b = item >> 2, h = (item >> 1) & 1, l0 = (item & 1) * 16;
-        const uint8_t *blk = rowp + (size_t)b * Q6K_BYTES;  // 2-byte aligned
-        uint32_t la[4], lb[4], hh[4];
-        lds_words_unaligned<4>(blk + 64 * h + l0, la);
-        lds_words_unaligned<4>(blk + 64 * h + 32 + l0, lb);
-        lds_words_unaligned<4>(blk + 128 + 32 * h + l0, hh);
-        const int8_t *scp = reinterpret_cast<const int8_t *>(blk + 192 + 8 * h + (l0 >> 4));
-        const int sc[4] = {scp[0], scp[2], scp[4], scp[6]};
-        const float dw = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(blk + 208));
-        uint32_t c[4][4];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            c[0][w] = (la[w] & 0x0f0f0f0fu) | ((hh[w] << 4) & 0x30303030u);
-            c[1][w] = (lb[w] & 0x0f0f0f0fu) | ((hh[w] << 2) & 0x30303030u);
-            c[2][w] = ((la[w] >> 4) & 0x0f0f0f0fu) | (hh[w] & 0x30303030u);
-            c[3][w] = ((lb[w] >> 4) & 0x0f0f0f0fu) | ((hh[w] >> 2) & 0x30303030u);
-        }
+            for (int lq = 0; lq < 2; ++lq) {  // l0 = 16*lq
+                uint4 aq[MC][4];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            int v = 0;
+                for (int m = 0; m < MC; ++m) {
+                    const int8_t *base =
+                        p.qs + ((size_t)(m0 + m) * (p.k >> 8) + b) * kQ8KUnitStride + h * 128 + lq * 16;
 #pragma unroll
-            for (int gq = 0; gq < 4; ++gq) {
-                const uint4 aq = a.q[m][gq];
-                int p = __dp4a((int)c[gq][0], (int)aq.x, 0);
-                p = __dp4a((int)c[gq][1], (int)aq.y, p);
-                p = __dp4a((int)c[gq][2], (int)aq.z, p);
-                p = __dp4a((int)c[gq][3], (int)aq.w, p);
-                v += sc[gq] * (p - 32 * a.bs[m][gq]);
+                    for (int gq = 0; gq < 4; ++gq) aq[m][gq] = *reinterpret_cast<const uint4 *>(base + 32 * gq);
+                }
+#pragma unroll
+                for (int r = 0; r < RW; ++r) {
+                    if (!valid[r]) continue;
+                    const uint8_t *blk = rowp[r] + (size_t)b * Q6K_BYTES;  // 2-byte aligned
+                    uint32_t la[4], lb[4], hh[4];
+                    lds_words_unaligned<4>(blk + 64 * h + 16 * lq, la);
+                    lds_words_unaligned<4>(blk + 64 * h + 32 + 16 * lq, lb);
+                    lds_words_unaligned<4>(blk + 128 + 32 * h + 16 * lq, hh);
+                    uint32_t cw[4][4];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        cw[0][w] = (la[w] & 0x0f0f0f0fu) | ((hh[w] << 4) & 0x30303030u);
+                        cw[1][w] = (lb[w] & 0x0f0f0f0fu) | ((hh[w] << 2) & 0x30303030u);
+                        cw[2][w] = ((la[w] >> 4) & 0x0f0f0f0fu) | (hh[w] & 0x30303030u);
+                        cw[3][w] = ((lb[w] >> 4) & 0x0f0f0f0fu) | ((hh[w] >> 2) & 0x30303030u);
+                    }
+#pragma unroll
+                    for (int gq = 0; gq < 4; ++gq) {
+                        // scale index within the half: lq + 2*gq  (byte of scw), sum index the same
+                        const int idx = lq + 2 * gq;
+                        const int sc = (int)(int8_t)((scw[r][idx >> 2] >> (8 * (idx & 3))) & 0xff);
+                        const uint4 cv = make_uint4(cw[gq][0], cw[gq][1], cw[gq][2], cw[gq][3]);
+#pragma unroll
+                        for (int m = 0; m < MC; ++m) {
+                            const uint32_t bsv[4] = {bsw[m].x, bsw[m].y, bsw[m].z, bsw[m].w};
+                            const uint32_t bw = bsv[idx >> 1];
+                            const int bs = (int)(short)((idx & 1) ? (bw >> 16) : (bw & 0xffffu));
+                            S[r][m] += sc * (dot16(cv, aq[m][gq], 0) - 32 * bs);
+                        }
+                    }
+                }
             }
-            acc[m] = fmaf(__fmul_rn(a.d[m], dw), (float)v, acc[m]);
+        }
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            float dw = 0.0f;
+            if (valid[r]) dw = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(rowp[r] + (size_t)b * Q6K_BYTES + 208));
+#pragma unroll
+            for (int m = 0; m < MC; ++m) {
+                const float da = p.d[(m0 + m) * (p.k >> 8) + b];
+                acc[r][m] = fmaf(__fmul_rn(da, dw), (float)S[r][m], acc[r][m]);
+            }
         }
     }
 };
 
-// Q8_0 x Q8_0 (k_quants.rs:800-818, avx.rs:71-87):  out += (d_w*d_a) * dot32(q_w, q_a) per block.
-// item = two consecutive 34-byte blocks.
-template <int M>
-struct ItemQ8_0 {
-    static constexpr int kItemsPerBlock = 0;  // items are pairs of blocks: items per row = k / 64
-    static constexpr int kBlockBytes = Q8_0_BYTES;
-    struct Act {
-        uint4 q[M][4];
-        float d[M][2];
-    };
-    __device__ static __forceinline__ void load_act(Act &a, const ActPlanes &p, int item) {
+// Q8_0 x Q8_0 (k_quants.rs:800-818, avx.rs:71-87):  out += (d_w*d_a) * dot32(q_w, q_a) per 32-element block.
+// unit = two consecutive 34-byte blocks (k must be a multiple of 64).
+struct FmtQ8_0 {
+    static constexpr int kUnitElems = 64;
+    template <int MC, int RW>
+    __device__ static __forceinline__ void unit(const ActPlanes &p, int m0, int u, const uint8_t *const (&rowp)[RW],
+                                                const bool (&valid)[RW], float (&acc)[RW][MC]) {
+        uint4 aq[MC][4];
+        float da[MC][2];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const uint4 *q = reinterpret_cast<const uint4 *>(p.qs + (size_t)m * p.k + item * 64);
+        for (int m = 0; m < MC; ++m) {
+            const uint4 *q = reinterpret_cast<const uint4 *>(
+                p.qs + ((size_t)(m0 + m) * (p.k >> 6) + u) * kQ8_0UnitStride);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a.q[m][i] = q[i];
-            a.d[m][0] = p.d[m * (p.k >> 5) + item * 2];
-            a.d[m][1] = p.d[m * (p.k >> 5) + item * 2 + 1];
+            for (int i = 0; i < 4; ++i) aq[m][i] = q[i];
+            const float2 dd = *reinterpret_cast<const float2 *>(p.d + (size_t)(m0 + m) * (p.k >> 5) + u * 2);
+            da[m][0] = dd.x;
+            da[m][1] = dd.y;
         }
-    }
-    __device__ static __forceinline__ void row(const uint8_t *rowp, int item, const Act &a, float (&acc)[M]) {
-        const uint8_t *blk = rowp + (size_t)item * (2 * Q8_0_BYTES);  // 2-byte aligned
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const uint8_t *bp = blk + half * Q8_0_BYTES;
-            const float dw = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(bp));
-            uint32_t q[8];
-            lds_words_unaligned<8>(bp + 2, q);
+        for (int r = 0; r < RW; ++r) {
+            if (!valid[r]) continue;
+            const uint8_t *blk = rowp[r] + (size_t)u * (2 * Q8_0_BYTES);  // 2-byte aligned
 #pragma unroll
-            for (int m = 0; m < M; ++m) {
-                const uint4 a0 = a.q[m][2 * half], a1 = a.q[m][2 * half + 1];
-                int p = __dp4a((int)q[0], (int)a0.x, 0);
-                p = __dp4a((int)q[1], (int)a0.y, p);
-                p = __dp4a((int)q[2], (int)a0.z, p);
-                p = __dp4a((int)q[3], (int)a0.w, p);
-                p = __dp4a((int)q[4], (int)a1.x, p);
-                p = __dp4a((int)q[5], (int)a1.y, p);
-                p = __dp4a((int)q[6], (int)a1.z, p);
-                p = __dp4a((int)q[7], (int)a1.w, p);
-                acc[m] = fmaf(__fmul_rn(dw, a.d[m][half]), (float)p, acc[m]);
+            for (int half = 0; half < 2; ++half) {
+                const uint8_t *bp = blk + half * Q8_0_BYTES;
+                const float dw = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(bp));
+                uint32_t q[8];
+                lds_words_unaligned<8>(bp + 2, q);
+                const uint4 q0 = make_uint4(q[0], q[1], q[2], q[3]), q1 = make_uint4(q[4], q[5], q[6], q[7]);
+#pragma unroll
+                for (int m = 0; m < MC; ++m) {
+                    const int pi = dot16(q1, aq[m][2 * half + 1], dot16(q0, aq[m][2 * half], 0));
+                    acc[r][m] = fmaf(__fmul_rn(dw, da[m][half]), (float)pi, acc[r][m]);
+                }
             }
         }
     }
@@ -241,6 +284,7 @@ struct GemvParams {
     int n, k, m;
     int w_dtype;
     int n_cwarps;      // consumer warps; blockDim.x = 32 * (n_cwarps + 1)
+    int lpr_log2;      // lanes per row = 1 << lpr_log2 (a warp handles 32 / lanes-per-row row groups)
     int stages;
     int stage_bytes;   // multiple of 128
     int act_bytes;     // multiple of 16
@@ -248,9 +292,77 @@ struct GemvParams {
 
 constexpr int kMaxStages = 8;
 
+// Canonical activation blocks (global) -> planes (shared); all `nthreads` consumer threads take part.
+__device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_smem, int tid, int nthreads,
+                                           ActPlanes &planes) {
+    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k));
+    float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
+    planes.qs = reinterpret_cast<const int8_t *>(act_smem);
+    planes.d = dpl;
+    planes.k = p.k;
+    constexpr int kUnroll = 4;
+    if (p.w_dtype == LLOOM_Q8_0) {
+        // 17 half-words per block: [0] = f16 d, [1..16] = 32 int8
+        const unsigned short *src = reinterpret_cast<const unsigned short *>(p.act);
+        unsigned short *q16 = reinterpret_cast<unsigned short *>(act_smem);
+        const int total = p.m * (p.k / 32) * 17;
+        for (int base = tid; base < total; base += nthreads * kUnroll) {
+            unsigned short v[kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int i = base + j * nthreads;
+                v[j] = i < total ? __ldg(src + i) : (unsigned short)0;
+            }
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int i = base + j * nthreads;
+                if (i < total) {
+                    const int blk = i / 17, hw = i - blk * 17;
+                    if (hw == 0) dpl[blk] = __half2float(__ushort_as_half(v[j]));
+                    else q16[(blk >> 1) * (kQ8_0UnitStride / 2) + (blk & 1) * 16 + hw - 1] = v[j];
+                }
+            }
+        }
+        planes.sums = nullptr;
+    } else {
+        // 73 words per block: [0] = f32 d, [1..64] = 256 int8, [65..72] = 16 int16 bsums
+        const int nb = p.k / 256;
+        short *sums = reinterpret_cast<short *>(act_smem + qs_bytes + round16((int64_t)p.m * nb * 4));
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(p.act);
+        uint32_t *q32 = reinterpret_cast<uint32_t *>(act_smem);
+        const bool pair = p.w_dtype == LLOOM_Q4_K;
+        const int total = p.m * nb * 73;
+        for (int base = tid; base < total; base += nthreads * kUnroll) {
+            uint32_t v[kUnroll];
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int i = base + j * nthreads;
+                v[j] = i < total ? __ldg(src + i) : 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < kUnroll; ++j) {
+                const int i = base + j * nthreads;
+                if (i < total) {
+                    const int blk = i / 73, w = i - blk * 73;
+                    if (w == 0) dpl[blk] = __uint_as_float(v[j]);
+                    else if (w <= 64) q32[blk * (kQ8KUnitStride / 4) + w - 1] = v[j];
+                    else if (pair) sums[blk * 8 + w - 65] = (short)((int)(short)(v[j] & 0xffffu) + (int)(short)(v[j] >> 16));
+                    else {
+                        const int mrow = blk / nb, b = blk - mrow * nb, jj = w - 65;  // word jj: bsums 2jj, 2jj+1
+                        reinterpret_cast<uint32_t *>(sums)[((mrow * 2 + (jj >> 2)) * nb + b) * 4 + (jj & 3)] = v[j];
+                    }
+                }
+            }
+        }
+        planes.sums = sums;
+    }
+}
+
 // Dynamic shared memory: [barriers 128 B][act planes][stage 0][stage 1]...
-template <class Item, int M, int RW>
+template <class Fmt, int M, int RW>
 __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
+    constexpr int MC = M > 4 ? (M + 1) / 2 : M;  // activation rows per pass
+    constexpr int NPASS = (M + MC - 1) / MC;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + kMaxStages;
@@ -258,7 +370,9 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
     uint8_t *stage0 = act_smem + p.act_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_rows = p.n_cwarps * RW;
+    const int lpr = 1 << p.lpr_log2;
+    const int groups = 32 >> p.lpr_log2;
+    const int tile_rows = p.n_cwarps * groups * RW;
     // equal contiguous row ranges per CTA: HBM bytes per SM differ by at most one row
     const int r_begin = (int)(((int64_t)blockIdx.x * p.n) / gridDim.x);
     const int r_end = (int)(((int64_t)(blockIdx.x + 1) * p.n) / gridDim.x);
@@ -309,94 +423,73 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
 
     // ---------------- consumer warps ----------------
     ActPlanes planes;
-    // all consumer warps stage the activations together (named barrier over consumers only)
     {
         const int nthreads = p.n_cwarps * 32;
-        // canonical activation blocks (global) -> aligned planes (shared), once per CTA
-        const size_t qs_bytes = (((size_t)p.m * p.k + 15) / 16) * 16;
-        float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
-        if (p.w_dtype == LLOOM_Q8_0) {
-            const int nb = p.k / 32;
-            const unsigned short *src = reinterpret_cast<const unsigned short *>(p.act);
-            unsigned short *q16 = reinterpret_cast<unsigned short *>(act_smem);
-            const int total = p.m * nb * 17;
-            for (int i = threadIdx.x; i < total; i += nthreads) {
-                const int blk = i / 17, hw = i - blk * 17;
-                const unsigned short v = __ldg(src + i);
-                if (hw == 0) dpl[blk] = __half2float(__ushort_as_half(v));
-                else q16[blk * 16 + hw - 1] = v;
-            }
-            planes.bsums = nullptr;
-        } else {
-            const int nb = p.k / 256;
-            const size_t d_bytes = (((size_t)p.m * nb * 4 + 15) / 16) * 16;
-            uint32_t *bs32 = reinterpret_cast<uint32_t *>(act_smem + qs_bytes + d_bytes);
-            const uint32_t *src = reinterpret_cast<const uint32_t *>(p.act);
-            uint32_t *q32 = reinterpret_cast<uint32_t *>(act_smem);
-            const int total = p.m * nb * 73;
-            for (int i = threadIdx.x; i < total; i += nthreads) {
-                const int blk = i / 73, w = i - blk * 73;
-                const uint32_t v = __ldg(src + i);
-                if (w == 0) dpl[blk] = __uint_as_float(v);
-                else if (w <= 64) q32[blk * 64 + w - 1] = v;
-                else bs32[blk * 8 + w - 65] = v;
-            }
-            planes.bsums = reinterpret_cast<const short *>(bs32);
-        }
-        planes.qs = reinterpret_cast<const int8_t *>(act_smem);
-        planes.d = dpl;
-        planes.k = p.k;
+        stage_acts(p, act_smem, threadIdx.x, nthreads, planes);
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     }
 
-    const int items_per_row = p.k >> 6;
+    const int units = p.k / Fmt::kUnitElems;
+    const int group = lane >> p.lpr_log2, lig = lane & (lpr - 1);
     int it = 0;
     for (int trow = r_begin; trow < r_end; trow += tile_rows, ++it) {
         const int s = it % p.stages;
         if (!mbar_wait(&full[s], (it / p.stages) & 1)) return;
         const int64_t start = (int64_t)trow * p.row_bytes;
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
-        const int row0 = trow + warp * RW;
+        const int local0 = (warp * groups + group) * RW;
+        const int row0 = trow + local0;
+        const uint8_t *rowp[RW];
+        bool valid[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            valid[r] = row0 + r < r_end;
+            rowp[r] = tile_base + (size_t)(local0 + r) * p.row_bytes;
+        }
 
-        float acc[RW][M];
+        float out[RW][M];
 #pragma unroll
-        for (int r = 0; r < RW; ++r)
+        for (int pass = 0; pass < NPASS; ++pass) {
+            const int m0 = pass * MC;
+            float acc[RW][MC];
 #pragma unroll
-            for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
-
-        if (row0 < r_end) {
-            for (int item = lane; item < items_per_row; item += 32) {
-                typename Item::Act a;
-                Item::load_act(a, planes, item);
+            for (int r = 0; r < RW; ++r)
 #pragma unroll
-                for (int r = 0; r < RW; ++r) {
-                    if (row0 + r < r_end) {
-                        const uint8_t *rowp = tile_base + (size_t)(warp * RW + r) * p.row_bytes;
-                        Item::row(rowp, item, a, acc[r]);
-                    }
+                for (int m = 0; m < MC; ++m) acc[r][m] = 0.0f;
+            if (valid[0]) {
+                // the last pass of an odd M re-reads row m0+MC-1 == M-1 ... clamp instead: see m_hi below
+                for (int u = lig; u < units; u += lpr) {
+                    if (m0 + MC <= M) Fmt::template unit<MC, RW>(planes, m0, u, rowp, valid, acc);
+                    else Fmt::template unit<MC, RW>(planes, M - MC, u, rowp, valid, acc);  // overlap the previous pass
                 }
             }
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+#pragma unroll
+                for (int m = 0; m < MC; ++m) {
+                    const int mi = (m0 + MC <= M) ? m0 + m : M - MC + m;
+                    out[r][mi] = acc[r][m];
+                }
         }
         // this warp is done reading the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
 
-        if (row0 < r_end) {
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float v = out[r][m];
+                for (int off = lpr >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                out[r][m] = v;
+            }
+        if (lig == 0) {
 #pragma unroll
             for (int r = 0; r < RW; ++r)
+                if (valid[r]) {
 #pragma unroll
-                for (int m = 0; m < M; ++m) {
-                    float v = acc[r][m];
-#pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-                    acc[r][m] = v;
+                    for (int m = 0; m < M; ++m) p.y[(int64_t)m * p.ldy + row0 + r] = out[r][m];
                 }
-            // lane (r*M + m) writes its value
-#pragma unroll
-            for (int r = 0; r < RW; ++r)
-#pragma unroll
-                for (int m = 0; m < M; ++m)
-                    if (lane == r * M + m && row0 + r < r_end) p.y[(int64_t)m * p.ldy + row0 + r] = acc[r][m];
         }
     }
 }

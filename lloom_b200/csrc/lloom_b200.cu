@@ -6,6 +6,8 @@
 #include "gemv.cuh"
 #include "quantize_act.cuh"
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace lloom {
@@ -68,17 +70,17 @@ static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, cud
     return cudaGetLastError();
 }
 
-template <template <int> class Item, int RW>
+template <class Fmt, int RW>
 static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
     switch (p.m) {
-    case 1: return launch_gemv_inst<Item<1>, 1, RW>(p, grid, smem, stream);
-    case 2: return launch_gemv_inst<Item<2>, 2, RW>(p, grid, smem, stream);
-    case 3: return launch_gemv_inst<Item<3>, 3, RW>(p, grid, smem, stream);
-    case 4: return launch_gemv_inst<Item<4>, 4, RW>(p, grid, smem, stream);
-    case 5: return launch_gemv_inst<Item<5>, 5, RW>(p, grid, smem, stream);
-    case 6: return launch_gemv_inst<Item<6>, 6, RW>(p, grid, smem, stream);
-    case 7: return launch_gemv_inst<Item<7>, 7, RW>(p, grid, smem, stream);
-    case 8: return launch_gemv_inst<Item<8>, 8, RW>(p, grid, smem, stream);
+    case 1: return launch_gemv_inst<Fmt, 1, RW>(p, grid, smem, stream);
+    case 2: return launch_gemv_inst<Fmt, 2, RW>(p, grid, smem, stream);
+    case 3: return launch_gemv_inst<Fmt, 3, RW>(p, grid, smem, stream);
+    case 4: return launch_gemv_inst<Fmt, 4, RW>(p, grid, smem, stream);
+    case 5: return launch_gemv_inst<Fmt, 5, RW>(p, grid, smem, stream);
+    case 6: return launch_gemv_inst<Fmt, 6, RW>(p, grid, smem, stream);
+    case 7: return launch_gemv_inst<Fmt, 7, RW>(p, grid, smem, stream);
+    case 8: return launch_gemv_inst<Fmt, 8, RW>(p, grid, smem, stream);
     }
     return cudaErrorInvalidValue;
 }
@@ -86,11 +88,23 @@ static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, cudaSt
 template <int RW>
 static cudaError_t launch_gemv_fmt(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
     switch (p.w_dtype) {
-    case LLOOM_Q8_0: return launch_gemv_m<ItemQ8_0, RW>(p, grid, smem, stream);
-    case LLOOM_Q4_K: return launch_gemv_m<ItemQ4K, RW>(p, grid, smem, stream);
-    case LLOOM_Q6_K: return launch_gemv_m<ItemQ6K, RW>(p, grid, smem, stream);
+    case LLOOM_Q8_0: return launch_gemv_m<FmtQ8_0, RW>(p, grid, smem, stream);
+    case LLOOM_Q4_K: return launch_gemv_m<FmtQ4K, RW>(p, grid, smem, stream);
+    case LLOOM_Q6_K: return launch_gemv_m<FmtQ6K, RW>(p, grid, smem, stream);
     }
     return cudaErrorInvalidValue;
+}
+
+// Development knob: LLOOM_GEMV_SHAPE="<consumer warps>,<rows per lane>" pins the tile shape.
+static bool gemv_shape_override(int &cw, int &rw) {
+    static int cached = -1, ccw = 0, crw = 0;
+    if (cached < 0) {
+        const char *e = getenv("LLOOM_GEMV_SHAPE");
+        cached = (e && sscanf(e, "%d,%d", &ccw, &crw) == 2 && ccw >= 1 && ccw <= 8 && (crw == 1 || crw == 2)) ? 1 : 0;
+    }
+    cw = ccw;
+    rw = crw;
+    return cached == 1;
 }
 
 static int gemv_launch(int w_dtype, const void *w, const void *act, float *y, int64_t m, int64_t n, int64_t k,
@@ -110,12 +124,20 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, float *y, in
     p.m = (int)m;
     p.w_dtype = w_dtype;
     p.act_bytes = (int)act_plane_bytes(w_dtype, m, k);
-    // Tile shapes, widest first; the first one that leaves room for at least two stages wins.
-    static const int kShapes[][2] = {{8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};  // {consumer warps, rows per warp}
+    // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
+    const int64_t units = k / (w_dtype == LLOOM_Q8_0 ? 64 : 256);
+    int lpr_log2 = 0;
+    while ((1 << lpr_log2) < units && lpr_log2 < 5) ++lpr_log2;
+    p.lpr_log2 = lpr_log2;
+    const int groups = 32 >> lpr_log2;
+    // Tile shapes, widest first (after an optional pinned shape); the first one that leaves room for
+    // at least two stages wins.
+    int shapes[6][2] = {{0, 0}, {8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};  // {consumer warps, rows per lane}
+    const int first = gemv_shape_override(shapes[0][0], shapes[0][1]) ? 0 : 1;
     const int64_t budget = (int64_t)di.max_smem_optin - 128 - p.act_bytes;
-    for (auto &shape : kShapes) {
-        const int cw = shape[0], rw = shape[1];
-        const int64_t stage = ((int64_t)cw * rw * p.row_bytes + 48 + 127) / 128 * 128;
+    for (int si = first; si < 6; ++si) {
+        const int cw = shapes[si][0], rw = shapes[si][1];
+        const int64_t stage = ((int64_t)cw * groups * rw * p.row_bytes + 48 + 127) / 128 * 128;
         if (budget < 2 * stage) continue;
         int64_t stages = budget / stage;
         if (stages > kMaxStages) stages = kMaxStages;

@@ -710,47 +710,66 @@ int lo_has_avx2(void) { return __builtin_cpu_supports("avx2") && __builtin_cpu_s
 int lo_has_avx2(void) { return 0; }
 #endif
 
-/* ---- per-element error scale: sum of |per-block f32 terms| ---- */
+/* ---- per-element error scale ----
+ * Sum of the magnitudes of the f32 summands the AVX2 arm actually adds for this element: per block,
+ * the eight lane terms d * lane_sum (and, for Q4_K, the four min-lane terms).  Any re-ordering of that
+ * f32 summation -- including the reference's own lane order -- is bounded relative to this scale. */
 static float vec_dot_absum(int w_dtype, int64_t k, const void *w, const void *act) {
     float a = 0.0f;
     if (w_dtype == LO_Q8_0) {
         const blk_q8_0 *x = w, *y = act;
         for (int64_t i = 0; i < k / QK8_0; ++i) {
-            int32_t s = 0;
-            for (int j = 0; j < QK8_0; ++j) s += (int32_t)x[i].qs[j] * (int32_t)y[i].qs[j];
-            a += fabsf((float)s * (lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d)));
+            float d = lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d);
+            for (int l = 0; l < 8; ++l) {
+                int32_t s = 0;
+                for (int t = 0; t < 4; ++t) s += (int32_t)x[i].qs[4 * l + t] * (int32_t)y[i].qs[4 * l + t];
+                a += fabsf(d * (float)s);
+            }
         }
     } else if (w_dtype == LO_Q4_K) {
         const blk_q4k *x = w;
         const blk_q8k *y = act;
         for (int64_t i = 0; i < k / QK_K; ++i) {
+            const blk_q4k *b = &x[i];
+            float d = y[i].d * lo_f16_to_f32(b->d);
+            float dmin = y[i].d * lo_f16_to_f32(b->dmin);
             uint8_t sc[8], mn[8];
-            q4k_scales_mins(&x[i], sc, mn);
-            int32_t S = 0, Mn = 0;
-            for (int j = 0; j < 8; ++j) {
-                int32_t p = 0;
-                for (int t = 0; t < 32; ++t) {
-                    uint8_t q = x[i].qs[32 * (j / 2) + t];
-                    p += (int32_t)((j & 1) ? (q >> 4) : (q & 0xF)) * (int32_t)y[i].qs[32 * j + t];
-                }
-                S += (int32_t)sc[j] * p;
-                Mn += (int32_t)mn[j] * ((int32_t)y[i].bsums[2 * j] + (int32_t)y[i].bsums[2 * j + 1]);
+            q4k_scales_mins(b, sc, mn);
+            for (int p = 0; p < 4; ++p) {
+                int32_t prod = (int32_t)mn[2 * p] * ((int32_t)y[i].bsums[4 * p] + y[i].bsums[4 * p + 1]) +
+                               (int32_t)mn[2 * p + 1] * ((int32_t)y[i].bsums[4 * p + 2] + y[i].bsums[4 * p + 3]);
+                a += fabsf(dmin * (float)prod);
             }
-            a += fabsf((y[i].d * lo_f16_to_f32(x[i].d)) * (float)S) + fabsf((y[i].d * lo_f16_to_f32(x[i].dmin)) * (float)Mn);
+            for (int l = 0; l < 8; ++l) {
+                int32_t sumi = 0;
+                for (int g = 0; g < 4; ++g) {
+                    int32_t lo = 0, hi = 0;
+                    for (int t = 0; t < 4; ++t) {
+                        uint8_t q = b->qs[32 * g + 4 * l + t];
+                        lo += (int32_t)(q & 0xF) * (int32_t)y[i].qs[64 * g + 4 * l + t];
+                        hi += (int32_t)(q >> 4) * (int32_t)y[i].qs[64 * g + 32 + 4 * l + t];
+                    }
+                    sumi += (int32_t)sc[2 * g] * lo + (int32_t)sc[2 * g + 1] * hi;
+                }
+                a += fabsf(d * (float)sumi);
+            }
         }
     } else if (w_dtype == LO_Q6_K) {
         const blk_q6k *x = w;
         const blk_q8k *y = act;
         int8_t c[QK_K];
         for (int64_t i = 0; i < k / QK_K; ++i) {
+            float d = y[i].d * lo_f16_to_f32(x[i].d);
             q6k_codes(&x[i], c);
-            int32_t S = 0;
-            for (int j = 0; j < 16; ++j) {
-                int32_t p = 0;
-                for (int t = 0; t < 16; ++t) p += (int32_t)c[16 * j + t] * (int32_t)y[i].qs[16 * j + t];
-                S += (int32_t)x[i].scales[j] * p;
+            for (int l = 0; l < 8; ++l) {
+                int32_t sumi = 0;
+                for (int g = 0; g < 8; ++g) {
+                    int32_t p = 0;
+                    for (int t = 0; t < 4; ++t) p += (int32_t)c[32 * g + 4 * l + t] * (int32_t)y[i].qs[32 * g + 4 * l + t];
+                    sumi += (int32_t)x[i].scales[2 * g + l / 4] * p;
+                }
+                a += fabsf(d * (float)sumi);
             }
-            a += fabsf((y[i].d * lo_f16_to_f32(x[i].d)) * (float)S);
         }
     }
     return a;

@@ -50,8 +50,8 @@ int lo_dequantize_row(int dtype, const void *blocks, float *y, int64_t k);
 
 /* T::vec_dot(k, w_row, act_row) in the requested order. */
 float lo_vec_dot(int w_dtype, int64_t k, const void *w, const void *act, int order);
-/* Sum of the magnitudes of the per-block f32 terms of the same dot product:
- * the scale a re-ordered f32 summation error is measured against. */
+/* Sum of the magnitudes of the f32 summands the AVX2 arm adds for this dot product (eight lane terms
+ * per block, plus four min-lane terms for Q4_K): the scale a re-ordered f32 summation is bounded by. */
 float lo_vec_dot_absum(int w_dtype, int64_t k, const void *w, const void *act);
 
 /* k_quants::matmul: lhs f32 [m,k] is quantized row by row with the weight

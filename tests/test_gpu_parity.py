@@ -4,10 +4,12 @@ golden fixtures.
 Tolerances (stated here, used everywhere below):
   * quantized activation blocks: bit-exact (byte equality).
   * dequantize / get_rows: bit-exact.
-  * f32 matmul outputs: |got - ref| <= 1e-5 * A, where A is the sum of the magnitudes of the element's
-    per-block f32 terms (the scale a re-ordered f32 summation is bounded by), and plain relative error
-    |got - ref| <= 1e-5 * |ref| for every element that is not a cancellation (|ref| >= A / 32).
-    Only the f32 summation order across blocks differs from the reference's AVX2 arm.
+  * f32 matmul outputs: |got - ref| <= 1e-5 * A, where A is the sum of the magnitudes of the f32
+    summands the reference's AVX2 arm adds for that element (eight lane terms per block, plus the four
+    min-lane terms of Q4_K) -- the scale any re-ordered f32 summation, the reference's own included, is
+    bounded by -- and plain relative error |got - ref| <= 1e-5 * |ref| for every element that is not a
+    cancellation (|ref| >= A / 32).  Integer block sums are exact on both sides; only the f32
+    summation order differs from the reference's AVX2 arm.
 """
 import os
 
