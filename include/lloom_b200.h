@@ -46,7 +46,8 @@ enum {
     LLOOM_ERR_WORKSPACE = 5, /* workspace missing or smaller than lloom_b200_workspace_bytes */
     LLOOM_ERR_LAUNCH = 6,    /* CUDA reported an error at launch (see lloom_b200_last_cuda_error) */
     LLOOM_ERR_TIMEOUT = 7,   /* a bounded device-side wait ran out (reported by lloom_b200_device_status) */
-    LLOOM_ERR_DEVICE = 8     /* not an sm_100 device / attribute query failed */
+    LLOOM_ERR_DEVICE = 8,    /* not an sm_100 device / attribute query failed */
+    LLOOM_ERR_STATIC_LIMIT = 9 /* request exceeds the built-in scratch of lloom_b200_qmatmul_fwd_static */
 };
 
 /* Library version (LLOOM_B200_VERSION of the build). */
@@ -96,6 +97,31 @@ int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, f
  * per-row arithmetic does not depend on the shard, so sharded == unsharded bit for bit. */
 int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
                            int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream);
+
+/* Decode forward for callers that have no way to provide scratch memory.  (No counterpart in the
+ * reference: its CUDA path always allocates its Q8_1 scratch through cudarc.)
+ *
+ * Who needs it: code that runs where device allocation is off limits -- a host thread that must not
+ * call cudaMalloc because allocation synchronises the device or is reserved to another component,
+ * a plugin handed only input and output buffers by its framework, a tight decode loop that wants
+ * zero allocator traffic.  Same result as lloom_b200_qmatmul_fwd for 1 <= m <= 8 (bit for bit: the
+ * same kernels run), but the quantized activations live in a fixed array inside the library
+ * instead of a caller workspace.
+ *
+ * Limits and rules:
+ *   - m <= 8 and m * lloom_b200_act_row_bytes(w_dtype, k) <= LLOOM_B200_STATIC_SCRATCH_BYTES
+ *     (256 KiB: e.g. m = 8 with k up to 28672 for Q4_K / Q6_K); anything larger returns
+ *     LLOOM_ERR_STATIC_LIMIT and launches nothing.
+ *   - Every GPU that loads the library holds that array until the process exits.
+ *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress,
+ *     with that device current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call wrote.  Each call
+ *     overwrites every byte it later reads, so nothing needs clearing, but two calls whose kernels
+ *     overlap on the GPU (different streams, no ordering) race on it: serialise them.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define LLOOM_B200_STATIC_SCRATCH_BYTES (256 * 1024)
+int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                                  int64_t k, int64_t ldy, void *stream);
 
 /* QCudaStorage::dequantize / dequantize_f16 (cuda.rs:647-718; CPU T::to_float k_quants.rs:720-736,
  * 1747-1774, 2327-2358): elem_count elements (a multiple of the block size) to f32 or f16. */

@@ -11,7 +11,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "liblloom_b200.so")
 
-OK, ERR_DTYPE, ERR_SHAPE, ERR_ALIGN, ERR_NULL, ERR_WORKSPACE, ERR_LAUNCH, ERR_TIMEOUT, ERR_DEVICE = range(9)
+OK, ERR_DTYPE, ERR_SHAPE, ERR_ALIGN, ERR_NULL, ERR_WORKSPACE, ERR_LAUNCH, ERR_TIMEOUT, ERR_DEVICE, ERR_STATIC_LIMIT = range(10)
 
 # Every symbol include/lloom_b200.h declares: (name, restype, argtypes)
 _i64, _vp, _int = C.c_int64, C.c_void_p, C.c_int
@@ -29,6 +29,7 @@ SYMBOLS = [
     ("lloom_b200_gemv", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     ("lloom_b200_gemm", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd_static", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     ("lloom_b200_dequantize", _int, [_int, _vp, _i64, _vp, _int, _vp]),
     ("lloom_b200_get_rows", _int, [_int, _vp, _i64, _i64, _vp, _i64, _vp, _vp]),
     # include/lloom_b200_host.h: C view of the C++ host layer

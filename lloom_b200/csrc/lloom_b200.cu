@@ -164,6 +164,29 @@ static int check_common(int w_dtype, int64_t m, int64_t n, int64_t k) {
 
 static bool aligned(const void *p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
+// ---- built-in scratch of lloom_b200_qmatmul_fwd_static ----
+// Lives in every device's copy of this module until the process exits.  In host code the name
+// below is only a host-side stand-in for the symbol, never a device address: the address a kernel
+// may use is the one cudaGetSymbolAddress returns, looked up once per device.
+static __device__ __align__(256) uint8_t g_static_scratch[LLOOM_B200_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_ptr(void **out) {
+    static std::mutex mu;
+    static void *cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LLOOM_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);  // `dev` is current here
+        if (e != cudaSuccess) return launch_status(e);
+        if (!p) return LLOOM_ERR_DEVICE;
+        cache[dev] = p;
+    }
+    *out = cache[dev];
+    return LLOOM_OK;
+}
+
 }  // namespace lloom
 
 using namespace lloom;
@@ -183,6 +206,7 @@ const char *lloom_b200_error_string(int status) {
     case LLOOM_ERR_LAUNCH: return "CUDA launch error";
     case LLOOM_ERR_TIMEOUT: return "device-side wait timed out";
     case LLOOM_ERR_DEVICE: return "not an sm_100 device";
+    case LLOOM_ERR_STATIC_LIMIT: return "request exceeds the built-in scratch (m <= 8 and m * act_row_bytes <= 256 KiB)";
     }
     return "unknown status";
 }
@@ -302,6 +326,25 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
     return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
                            workspace_bytes - act, stream);
+}
+
+int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                                  int64_t k, int64_t ldy, void *stream) {
+    int rc = check_common(w_dtype, m, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (ldy < n) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !x || !y) return LLOOM_ERR_NULL;
+    if (!aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    if (m > 8 || m * lloom_b200_act_row_bytes(w_dtype, k) > (int64_t)LLOOM_B200_STATIC_SCRATCH_BYTES)
+        return LLOOM_ERR_STATIC_LIMIT;
+    void *scratch = nullptr;
+    rc = static_scratch_ptr(&scratch);  // first call per device: cudaGetSymbolAddress (keep it out of captures)
+    if (rc != LLOOM_OK) return rc;
+    // The quantizer writes every byte of the m activation rows the GEMV then reads; the rest of the
+    // array (left over from earlier calls) is never touched.
+    rc = launch_status(launch_quantize_act(w_dtype, x, m, k, scratch, (cudaStream_t)stream));
+    if (rc != LLOOM_OK) return rc;
+    return gemv_launch(w_dtype, w_blocks, scratch, y, m, n, k, ldy, (cudaStream_t)stream);
 }
 
 int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,
