@@ -60,6 +60,15 @@ int lloom_b200_last_cuda_error(void);
  * when a bounded mbarrier wait inside a kernel gave up.  For tests and post-mortems. */
 int lloom_b200_device_status(int *status_out);
 
+/* Launch overlap for the decode GEMV (off by default; returns the previous setting).  When on, GEMV
+ * launches carry the programmatic-stream-serialization attribute: a GEMV may start streaming its
+ * weights while the kernel before it in the stream is still finishing, and waits for that kernel
+ * only before it reads activations or writes outputs.  Turn it on once weights are resident; the one
+ * rule it adds is that the kernel launched immediately before a GEMV on the same stream must not be
+ * the one that writes that GEMV's weight blocks (copies and earlier kernels are fine).  Results are
+ * unchanged. */
+int lloom_b200_set_launch_overlap(int enable);
+
 /* GgmlDType::block_size / type_size (mod.rs:663-715): 32|256 elements, 34|144|210|292 bytes; 0 if unsupported. */
 int64_t lloom_b200_block_elems(int dtype);
 int64_t lloom_b200_block_bytes(int dtype);

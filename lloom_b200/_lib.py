@@ -20,6 +20,7 @@ SYMBOLS = [
     ("lloom_b200_error_string", C.c_char_p, [_int]),
     ("lloom_b200_last_cuda_error", _int, []),
     ("lloom_b200_device_status", _int, [C.POINTER(_int)]),
+    ("lloom_b200_set_launch_overlap", _int, [_int]),
     ("lloom_b200_block_elems", _i64, [_int]),
     ("lloom_b200_block_bytes", _i64, [_int]),
     ("lloom_b200_act_dtype", _int, [_int]),

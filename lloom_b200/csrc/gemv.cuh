@@ -12,6 +12,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "quantize_act.cuh"
 
 namespace lloom {
 
@@ -276,7 +277,8 @@ struct FmtQ8_0 {
 
 struct GemvParams {
     const uint8_t *w;    // canonical blocks, 16-byte aligned
-    const uint8_t *act;  // canonical activation blocks [m][k/block]
+    const uint8_t *act;  // canonical activation blocks [m][k/block] (used when x == nullptr)
+    const float *x;      // f32 activations [m][k], 16-byte aligned: quantized in the prologue (fused forward)
     float *y;
     int64_t ldy;
     int64_t row_bytes;
@@ -291,6 +293,19 @@ struct GemvParams {
 };
 
 constexpr int kMaxStages = 8;
+
+#ifdef LLOOM_TRACE
+// Development build only: per-CTA timestamps (ns) of the GEMV's phases.
+__device__ unsigned long long g_trace[256][16];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define LLOOM_TRACE_MARK(slot) do { if ((threadIdx.x & 31) == 0) g_trace[blockIdx.x][slot] = trace_now(); } while (0)
+#else
+#define LLOOM_TRACE_MARK(slot) do { } while (0)
+#endif
 
 // Canonical activation blocks (global) -> planes (shared); all `nthreads` consumer threads take part.
 __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_smem, int tid, int nthreads,
@@ -358,9 +373,73 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
     }
 }
 
+// f32 activations (global) -> planes (shared), quantized on the way with the same warp-level block
+// arithmetic as the stand-alone quantizer kernels (bit-identical codes, scales and sums).
+__device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uint8_t *act_smem, int warp, int lane,
+                                                        ActPlanes &planes) {
+    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k));
+    float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
+    uint32_t *q32 = reinterpret_cast<uint32_t *>(act_smem);
+    planes.qs = reinterpret_cast<const int8_t *>(act_smem);
+    planes.d = dpl;
+    planes.k = p.k;
+    if (p.w_dtype == LLOOM_Q8_0) {
+        const int total = p.m * (p.k / 32);
+        for (int base = warp * 8; base < total; base += p.n_cwarps * 8) {
+            const int blk = base + (lane >> 2), part = lane & 3;
+            const bool live = blk < total;
+            float v[8];
+            if (live) load8(p.x + (size_t)blk * 32 + part * 8, v);
+            else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+            }
+            uint32_t q_lo, q_hi;
+            unsigned short d16;
+            q8_0_quantize_quad(v, q_lo, q_hi, d16);
+            if (live) {
+                uint32_t *dst = q32 + ((blk >> 1) * kQ8_0UnitStride + (blk & 1) * 32 + part * 8) / 4;
+                dst[0] = q_lo;
+                dst[1] = q_hi;
+                if (part == 0) dpl[blk] = __half2float(__ushort_as_half(d16));
+            }
+        }
+        planes.sums = nullptr;
+    } else {
+        const int nb = p.k / 256;
+        short *sums = reinterpret_cast<short *>(act_smem + qs_bytes + round16((int64_t)p.m * nb * 4));
+        const int total = p.m * nb;
+        for (int blk = warp; blk < total; blk += p.n_cwarps) {
+            float v[8];
+            load8(p.x + (size_t)blk * 256 + lane * 8, v);
+            uint32_t q_lo, q_hi;
+            float d;
+            int sum16;
+            q8k_quantize_warp(v, lane, q_lo, q_hi, d, sum16);
+            q32[blk * (kQ8KUnitStride / 4) + lane * 2] = q_lo;
+            q32[blk * (kQ8KUnitStride / 4) + lane * 2 + 1] = q_hi;
+            if (lane == 0) dpl[blk] = d;
+            if (p.w_dtype == LLOOM_Q4_K) {
+                const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+                if ((lane & 3) == 0) sums[blk * 8 + (lane >> 2)] = (short)sum32;
+            } else if ((lane & 1) == 0) {
+                const int mrow = blk / nb, b = blk - mrow * nb, j = lane >> 1;
+                sums[((mrow * 2 + (j >> 3)) * nb + b) * 8 + (j & 7)] = (short)sum16;
+            }
+        }
+        planes.sums = sums;
+    }
+}
+
 // Dynamic shared memory: [barriers 128 B][act planes][stage 0][stage 1]...
+// Launch overlap: the kernel lets its stream successor start as soon as it is set up
+// (griddepcontrol.launch_dependents) and itself waits for its predecessor (griddepcontrol.wait) only
+// before it reads activations or writes outputs.  The producer warp starts streaming weights right
+// away -- weights are read-only for the life of a QTensor.  Without the programmatic-serialization
+// launch attribute both instructions do nothing.  RW == 1 instances are built to fit two per SM, so
+// a successor's CTA can sit beside its predecessor's and keep the HBM stream going across launches.
 template <class Fmt, int M, int RW>
-__global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(288, RW == 1 ? 2 : 1) gemv_kernel(const GemvParams p) {
     constexpr int MC = M > 4 ? (M + 1) / 2 : M;  // activation rows per pass
     constexpr int NPASS = (M + MC - 1) / MC;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -377,6 +456,7 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
     const int r_begin = (int)(((int64_t)blockIdx.x * p.n) / gridDim.x);
     const int r_end = (int)(((int64_t)(blockIdx.x + 1) * p.n) / gridDim.x);
 
+    if (threadIdx.x == 0) LLOOM_TRACE_MARK(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
@@ -385,6 +465,7 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
         fence_mbar_init();
     }
     __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == p.n_cwarps) {
         // ---------------- producer warp ----------------
@@ -425,8 +506,11 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
     ActPlanes planes;
     {
         const int nthreads = p.n_cwarps * 32;
-        stage_acts(p, act_smem, threadIdx.x, nthreads, planes);
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // predecessor's writes (x, act blocks) are visible
+        if (p.x) quantize_acts_to_planes(p, act_smem, warp, lane, planes);
+        else stage_acts(p, act_smem, threadIdx.x, nthreads, planes);
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (threadIdx.x == 0) LLOOM_TRACE_MARK(1);
     }
 
     const int units = p.k / Fmt::kUnitElems;
@@ -435,6 +519,7 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
     for (int trow = r_begin; trow < r_end; trow += tile_rows, ++it) {
         const int s = it % p.stages;
         if (!mbar_wait(&full[s], (it / p.stages) & 1)) return;
+        if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(2 + 2 * it);
         const int64_t start = (int64_t)trow * p.row_bytes;
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
         const int local0 = (warp * groups + group) * RW;
@@ -474,6 +559,7 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
         // this warp is done reading the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+        if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(3 + 2 * it);
 
 #pragma unroll
         for (int r = 0; r < RW; ++r)
@@ -492,6 +578,7 @@ __global__ void __launch_bounds__(288, 1) gemv_kernel(const GemvParams p) {
                 }
         }
     }
+    if (threadIdx.x == 0) LLOOM_TRACE_MARK(15);
 }
 
 }  // namespace lloom

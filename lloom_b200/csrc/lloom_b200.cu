@@ -6,6 +6,7 @@
 #include "gemv.cuh"
 #include "quantize_act.cuh"
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
@@ -24,10 +25,15 @@ static bool supported_weight(int dtype) { return dtype == LLOOM_Q8_0 || dtype ==
 
 struct DeviceInfo {
     int sm_count = 0;
-    int max_smem_optin = 0;
+    int max_smem_optin = 0;   // per block
+    int smem_per_sm = 0;      // per multiprocessor
+    int smem_reserved = 0;    // per block, taken by the driver
     int cc_major = 0;
     bool ok = false;
 };
+
+// Launch overlap (programmatic dependent launch); off until lloom_b200_set_launch_overlap(1).
+static std::atomic<int> g_launch_overlap{0};
 
 // Per-device attributes, queried once (the reference caches the same facts, fast_mmq.rs device-info cache).
 static int device_info(DeviceInfo &out) {
@@ -40,6 +46,10 @@ static int device_info(DeviceInfo &out) {
     if (!c.ok) {
         if (cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LLOOM_ERR_DEVICE;
         if (cudaDeviceGetAttribute(&c.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+            return LLOOM_ERR_DEVICE;
+        if (cudaDeviceGetAttribute(&c.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess)
+            return LLOOM_ERR_DEVICE;
+        if (cudaDeviceGetAttribute(&c.smem_reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess)
             return LLOOM_ERR_DEVICE;
         if (cudaDeviceGetAttribute(&c.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return LLOOM_ERR_DEVICE;
         if (c.cc_major != 10) return LLOOM_ERR_DEVICE;  // sm_100a code only
@@ -56,7 +66,7 @@ static int64_t weight_row_bytes(int dtype, int64_t k) {
 // ---- GEMV launch planning ----
 
 template <class Item, int M, int RW>
-static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
+static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
     auto kern = gemv_kernel<Item, M, RW>;
     static int configured_smem[64] = {0};
     int dev = 0;
@@ -66,31 +76,40 @@ static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, cud
         if (e != cudaSuccess) return e;
         configured_smem[dev] = smem;
     }
-    kern<<<grid, 32 * (p.n_cwarps + 1), smem, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(32u * (unsigned)(p.n_cwarps + 1));
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <class Fmt, int RW>
-static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
+static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
     switch (p.m) {
-    case 1: return launch_gemv_inst<Fmt, 1, RW>(p, grid, smem, stream);
-    case 2: return launch_gemv_inst<Fmt, 2, RW>(p, grid, smem, stream);
-    case 3: return launch_gemv_inst<Fmt, 3, RW>(p, grid, smem, stream);
-    case 4: return launch_gemv_inst<Fmt, 4, RW>(p, grid, smem, stream);
-    case 5: return launch_gemv_inst<Fmt, 5, RW>(p, grid, smem, stream);
-    case 6: return launch_gemv_inst<Fmt, 6, RW>(p, grid, smem, stream);
-    case 7: return launch_gemv_inst<Fmt, 7, RW>(p, grid, smem, stream);
-    case 8: return launch_gemv_inst<Fmt, 8, RW>(p, grid, smem, stream);
+    case 1: return launch_gemv_inst<Fmt, 1, RW>(p, grid, smem, overlap, stream);
+    case 2: return launch_gemv_inst<Fmt, 2, RW>(p, grid, smem, overlap, stream);
+    case 3: return launch_gemv_inst<Fmt, 3, RW>(p, grid, smem, overlap, stream);
+    case 4: return launch_gemv_inst<Fmt, 4, RW>(p, grid, smem, overlap, stream);
+    case 5: return launch_gemv_inst<Fmt, 5, RW>(p, grid, smem, overlap, stream);
+    case 6: return launch_gemv_inst<Fmt, 6, RW>(p, grid, smem, overlap, stream);
+    case 7: return launch_gemv_inst<Fmt, 7, RW>(p, grid, smem, overlap, stream);
+    case 8: return launch_gemv_inst<Fmt, 8, RW>(p, grid, smem, overlap, stream);
     }
     return cudaErrorInvalidValue;
 }
 
 template <int RW>
-static cudaError_t launch_gemv_fmt(const GemvParams &p, int grid, int smem, cudaStream_t stream) {
+static cudaError_t launch_gemv_fmt(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
     switch (p.w_dtype) {
-    case LLOOM_Q8_0: return launch_gemv_m<FmtQ8_0, RW>(p, grid, smem, stream);
-    case LLOOM_Q4_K: return launch_gemv_m<FmtQ4K, RW>(p, grid, smem, stream);
-    case LLOOM_Q6_K: return launch_gemv_m<FmtQ6K, RW>(p, grid, smem, stream);
+    case LLOOM_Q8_0: return launch_gemv_m<FmtQ8_0, RW>(p, grid, smem, overlap, stream);
+    case LLOOM_Q4_K: return launch_gemv_m<FmtQ4K, RW>(p, grid, smem, overlap, stream);
+    case LLOOM_Q6_K: return launch_gemv_m<FmtQ6K, RW>(p, grid, smem, overlap, stream);
     }
     return cudaErrorInvalidValue;
 }
@@ -107,14 +126,17 @@ static bool gemv_shape_override(int &cw, int &rw) {
     return cached == 1;
 }
 
-static int gemv_launch(int w_dtype, const void *w, const void *act, float *y, int64_t m, int64_t n, int64_t k,
-                       int64_t ldy, cudaStream_t stream) {
+// Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
+// quantized in the kernel's prologue) is non-null.
+static int gemv_launch(int w_dtype, const void *w, const void *act, const float *x, float *y, int64_t m, int64_t n,
+                       int64_t k, int64_t ldy, cudaStream_t stream) {
     DeviceInfo di;
     int rc = device_info(di);
     if (rc != LLOOM_OK) return rc;
     GemvParams p;
     p.w = (const uint8_t *)w;
     p.act = (const uint8_t *)act;
+    p.x = x;
     p.y = y;
     p.ldy = ldy;
     p.row_bytes = weight_row_bytes(w_dtype, k);
@@ -130,14 +152,31 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, float *y, in
     while ((1 << lpr_log2) < units && lpr_log2 < 5) ++lpr_log2;
     p.lpr_log2 = lpr_log2;
     const int groups = 32 >> lpr_log2;
-    // Tile shapes, widest first (after an optional pinned shape); the first one that leaves room for
-    // at least two stages wins.
-    int shapes[6][2] = {{0, 0}, {8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};  // {consumer warps, rows per lane}
-    const int first = gemv_shape_override(shapes[0][0], shapes[0][1]) ? 0 : 1;
-    const int64_t budget = (int64_t)di.max_smem_optin - 128 - p.act_bytes;
-    for (int si = first; si < 6; ++si) {
-        const int cw = shapes[si][0], rw = shapes[si][1];
-        const int64_t stage = ((int64_t)cw * groups * rw * p.row_bytes + 48 + 127) / 128 * 128;
+    // A stage holds one tile of rows, widened to 16-byte boundaries, plus slack for the word-wide
+    // over-read of the unaligned loaders.
+    const int64_t pad = (p.row_bytes % 16 == 0) ? 16 : 48;
+    int grid = di.sm_count;
+    if ((int64_t)grid > n) grid = (int)n;
+    // Tile shapes {consumer warps, rows per lane}, widest first (after an optional pinned shape); the
+    // first that leaves room for at least two stages wins.  With launch overlap on, m <= 2 tries shapes
+    // that fit two CTAs per SM first, so that consecutive launches can sit side by side.
+    struct Shape { int cw, rw; bool half; };
+    Shape shapes[10];
+    int ns = 0, ocw = 0, orw = 0;
+    const bool overlap = g_launch_overlap.load(std::memory_order_relaxed) != 0;
+    if (gemv_shape_override(ocw, orw)) shapes[ns++] = {ocw, orw, overlap && orw == 1};
+    if (overlap && m <= 2) {  // HBM-bound batch sizes only: wider batches need the registers and the row tiling
+        const int half_cw[4] = {8, 4, 2, 1};
+        for (int c : half_cw) shapes[ns++] = {c, 1, true};
+    }
+    const int full[5][2] = {{8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};
+    for (auto &f : full) shapes[ns++] = {f[0], f[1], false};
+    for (int si = 0; si < ns; ++si) {
+        const int cw = shapes[si].cw, rw = shapes[si].rw;
+        const int64_t per_block = shapes[si].half ? (int64_t)(di.smem_per_sm - 2 * di.smem_reserved) / 2 / 16 * 16
+                                                  : (int64_t)di.max_smem_optin;
+        const int64_t budget = per_block - 128 - p.act_bytes;
+        const int64_t stage = round16((int64_t)cw * groups * rw * p.row_bytes + pad);
         if (budget < 2 * stage) continue;
         int64_t stages = budget / stage;
         if (stages > kMaxStages) stages = kMaxStages;
@@ -145,9 +184,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, float *y, in
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
         const int smem = 128 + p.act_bytes + (int)(stages * stage);
-        int grid = di.sm_count;
-        if ((int64_t)grid > n) grid = (int)n;
-        cudaError_t e = (rw == 2) ? launch_gemv_fmt<2>(p, grid, smem, stream) : launch_gemv_fmt<1>(p, grid, smem, stream);
+        cudaError_t e = (rw == 2) ? launch_gemv_fmt<2>(p, grid, smem, overlap, stream)
+                                  : launch_gemv_fmt<1>(p, grid, smem, overlap, stream);
         return launch_status(e);
     }
     return LLOOM_ERR_SHAPE;  // one row of weights plus the activations does not fit in shared memory
@@ -212,6 +250,10 @@ const char *lloom_b200_error_string(int status) {
 }
 
 int lloom_b200_last_cuda_error(void) { return t_last_cuda_error; }
+
+int lloom_b200_set_launch_overlap(int enable) {
+    return g_launch_overlap.exchange(enable ? 1 : 0, std::memory_order_relaxed);
+}
 
 int lloom_b200_device_status(int *status_out) {
     if (!status_out) return LLOOM_ERR_NULL;
@@ -280,7 +322,7 @@ int lloom_b200_gemv(int w_dtype, const void *w_blocks, const void *act_blocks, f
     if (m > 8 || ldy < n) return LLOOM_ERR_SHAPE;
     if (!w_blocks || !act_blocks || !y) return LLOOM_ERR_NULL;
     if (!aligned(w_blocks, 16) || !aligned(act_blocks, 4) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
-    return gemv_launch(w_dtype, w_blocks, act_blocks, y, m, n, k, ldy, (cudaStream_t)stream);
+    return gemv_launch(w_dtype, w_blocks, act_blocks, nullptr, y, m, n, k, ldy, (cudaStream_t)stream);
 }
 
 int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,
@@ -304,7 +346,7 @@ int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, f
     const int64_t arow = lloom_b200_act_row_bytes(w_dtype, k);
     for (int64_t r = 0; r < m; r += 8) {
         const int64_t mm = (m - r < 8) ? (m - r) : 8;
-        rc = gemv_launch(w_dtype, w_blocks, (const uint8_t *)act_blocks + r * arow, y + r * ldy, mm, n, k, ldy,
+        rc = gemv_launch(w_dtype, w_blocks, (const uint8_t *)act_blocks + r * arow, nullptr, y + r * ldy, mm, n, k, ldy,
                          (cudaStream_t)stream);
         if (rc != LLOOM_OK) return rc;
     }
@@ -320,9 +362,10 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
     if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
     if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    // decode: one launch, the activation quantizer is the GEMV's prologue (the workspace stays unused)
+    if (m <= 8) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
     rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
     if (rc != LLOOM_OK) return rc;
-    if (m <= 8) return gemv_launch(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (cudaStream_t)stream);
     const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
     return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
                            workspace_bytes - act, stream);
@@ -344,8 +387,14 @@ int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float
     // array (left over from earlier calls) is never touched.
     rc = launch_status(launch_quantize_act(w_dtype, x, m, k, scratch, (cudaStream_t)stream));
     if (rc != LLOOM_OK) return rc;
-    return gemv_launch(w_dtype, w_blocks, scratch, y, m, n, k, ldy, (cudaStream_t)stream);
+    return gemv_launch(w_dtype, w_blocks, scratch, nullptr, y, m, n, k, ldy, (cudaStream_t)stream);
 }
+
+#ifdef LLOOM_TRACE
+int lloom_b200_read_trace(unsigned long long *out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+}
+#endif
 
 int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,
                           void *stream) {
