@@ -1,16 +1,496 @@
-// Prefill GEMM for Q4_K weights on tcgen05 tensor cores (placeholder: not yet taken).
+// Prefill GEMM for Q4_K weights on tcgen05 tensor cores (sm_100a), exact-integer formulation.
+//
+//   y[m, n] = sum over superblocks b of  (d_a[m,b]*d_w[n,b]) * S[n,m,b]  +  (-d_a[m,b]*dmin_w[n,b]) * Mn[n,m,b]
+//   S  = sum_j sc_j * dot32(q4_j, q8_j)      Mn = sum_j m_j * (bsums[2j] + bsums[2j+1])
+// (BlockQ4K::vec_dot, lloom-tensor/src/quantized/k_quants.rs:1540-1620 / avx.rs:443-525, through the
+// m > 1 arm of k_quants::matmul, :2518-2585).
+//
+// S and Mn are integer contractions, so they run on the tensor cores with every operand an integer
+// that f16 represents exactly:  A = sc_j*q4 (<= 945),  B = q8 codes (|.| <= 127),  A_min = m_j (<= 63,
+// each duplicated against the two 16-element bsums it multiplies),  B_min = bsums (|.| <= 2032); the
+// f32 accumulators in tensor memory then hold the integers.  One 128x128 accumulator pair (S, Mn)
+// is produced per 256-element superblock and drained by the epilogue warps, which apply the two f32
+// scales in the reference's algebraic form and keep the running sum in registers -- the per-block
+// scale granularity of the format is what forces a drain per superblock.  Tensor memory holds two
+// accumulator pairs (2 x (128 + 128) = 512 columns), so the drain of superblock b overlaps the MMAs
+// of superblock b+1.
+//
+// CTA = one 128 (weight rows) x 128 (activation rows) output tile.  Warp roles:
+//   warps 0-7   epilogue: tcgen05.ld -> f32x2 FMAs; warp w reads TMEM lanes 32*(w%4).., columns 64*(w/4)..
+//   warps 8-11  weight producers: one thread per weight row, Q4_K block -> f16 (sc*q) written straight
+//               into the 128B-swizzled K-major UMMA layout (4 k-stages of 64 per superblock) + min tile
+//   warp 12     bulk-copy (TMA engine) producer of the activation tiles, which gemm_prep_kernel laid out
+//               in global memory as ready-made shared-memory images
+//   warp 13     MMA issuer (one elected thread): 4 x tcgen05.mma.kind::f16 (K = 16) per k-stage
+// All mbarrier waits are bounded and abortable; on a time-out the status word is set, every role
+// leaves its loop, and tensor memory is still released.
 #pragma once
+
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
 namespace lloom {
 
-inline int64_t gemm_scratch_bytes(int /*w_dtype*/, int64_t /*m*/, int64_t /*n*/, int64_t /*k*/) { return 0; }
+constexpr int kGemmBN = 128;          // weight rows per tile (UMMA M)
+constexpr int kGemmBM = 128;          // activation rows per tile (UMMA N)
+constexpr int kGemmStageBytes = 128 * 64 * 2;  // one k-stage (64 of K) of either operand, f16
+constexpr int kGemmMinBytes = 128 * 16 * 2;    // min-term operand tile (K = 16), f16
+constexpr int kGemmDaBytes = 128 * 4;
+constexpr int kGemmStages = 4;
+constexpr int kGemmThreads = 512;
 
-inline int gemm_launch(int /*w_dtype*/, const void * /*w*/, const void * /*act*/, float * /*y*/, int64_t /*m*/,
-                       int64_t /*n*/, int64_t /*k*/, int64_t /*ldy*/, void * /*workspace*/, int /*sm_count*/,
-                       int /*max_smem*/, cudaStream_t /*stream*/, bool &handled, int & /*cuda_err*/) {
+// ---- shared memory map (offsets from a 1024-byte aligned base) ----
+constexpr int kOffA = 0;
+constexpr int kOffB = kOffA + kGemmStages * kGemmStageBytes;
+constexpr int kOffMinA = kOffB + kGemmStages * kGemmStageBytes;
+constexpr int kOffMinB = kOffMinA + 2 * kGemmMinBytes;
+constexpr int kOffDa = kOffMinB + 2 * kGemmMinBytes;
+constexpr int kOffBars = kOffDa + 2 * kGemmDaBytes;
+constexpr int kGemmNumBars = 4 * kGemmStages + 12;
+constexpr int kOffMisc = kOffBars + kGemmNumBars * 8;
+constexpr int kGemmSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
+
+__host__ __device__ inline int64_t gemm_m_tiles(int64_t m) { return (m + kGemmBM - 1) / kGemmBM; }
+
+// Workspace planes the GEMM reads (after the canonical activation blocks): B images, min-B images, scales.
+struct GemmScratch {
+    int64_t bimg, minb, dat, total;
+};
+__host__ __device__ inline GemmScratch gemm_scratch_layout(int64_t m, int64_t k) {
+    GemmScratch s;
+    const int64_t mt = gemm_m_tiles(m), nb = k / 256;
+    s.bimg = 0;
+    s.minb = s.bimg + mt * (k / 64) * kGemmStageBytes;
+    s.dat = s.minb + mt * nb * kGemmMinBytes;
+    s.total = (s.dat + mt * nb * kGemmDaBytes + 255) / 256 * 256;
+    return s;
+}
+
+inline int64_t gemm_scratch_bytes(int w_dtype, int64_t m, int64_t /*n*/, int64_t k) {
+    if (w_dtype != LLOOM_Q4_K || m <= 8) return 0;
+    return gemm_scratch_layout(m, k).total;
+}
+
+// Byte offset of element (row r, k-element e in [0,64)) inside a 128-row k-stage image:
+// K-major, 128-byte rows, 8-row groups of 1024 bytes, 16-byte chunks XOR-swizzled by the row (SWIZZLE_128B).
+__host__ __device__ inline int sw128_offset(int r, int e) {
+    return (r >> 3) * 1024 + (r & 7) * 128 + ((((e >> 3) ^ (r & 7)) & 7) << 4) + (e & 7) * 2;
+}
+// Byte offset inside a min-term tile (128 rows x 16 f16), K-major without swizzle:
+// core matrices of 8 rows x 16 bytes; K-chunk stride 128 bytes, 8-row-group stride 256 bytes.
+__host__ __device__ inline int min_tile_offset(int r, int e) {
+    return ((r >> 3) * 2 + (e >> 3)) * 128 + (r & 7) * 16 + (e & 7) * 2;
+}
+
+// Canonical Q8_K activation blocks -> the GEMM's operand images.  One CTA per (m-tile, superblock):
+// thread (t, c) converts 8 consecutive codes of token t to f16 and stores one 16-byte chunk.
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restrict__ act, int m, int k,
+                                                        uint8_t *__restrict__ scratch) {
+    const int nb = k / 256;
+    const int mt = blockIdx.x / nb, b = blockIdx.x % nb;
+    const GemmScratch lay = gemm_scratch_layout(m, k);
+    uint8_t *bimg = scratch + lay.bimg + ((int64_t)mt * (k / 64) + (int64_t)b * 4) * kGemmStageBytes;
+    uint8_t *minb = scratch + lay.minb + ((int64_t)mt * nb + b) * kGemmMinBytes;
+    float *dat = reinterpret_cast<float *>(scratch + lay.dat) + ((int64_t)mt * nb + b) * 128;
+    for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
+        const int t = i >> 5, c = i & 31;  // token in tile, 8-element chunk of the superblock
+        const int row = mt * kGemmBM + t;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (row < m) {
+            const uint8_t *blk = act + ((int64_t)row * nb + b) * Q8K_BYTES;
+            const uint32_t *qp = reinterpret_cast<const uint32_t *>(blk + 4 + c * 8);  // 4-byte aligned only
+            const uint2 q = make_uint2(qp[0], qp[1]);
+            auto cvt2 = [](uint32_t w, int sh) -> uint32_t {
+                const __half2 h = __floats2half2_rn((float)(int)(int8_t)(w >> sh), (float)(int)(int8_t)(w >> (sh + 8)));
+                return *reinterpret_cast<const uint32_t *>(&h);
+            };
+            out = make_uint4(cvt2(q.x, 0), cvt2(q.x, 16), cvt2(q.y, 0), cvt2(q.y, 16));
+        }
+        const int ks = c >> 3, e = (c & 7) * 8;
+        *reinterpret_cast<uint4 *>(bimg + (int64_t)ks * kGemmStageBytes + sw128_offset(t, e)) = out;
+    }
+    for (int i = threadIdx.x; i < 128 * 2; i += blockDim.x) {
+        const int t = i >> 1, c = i & 1;
+        const int row = mt * kGemmBM + t;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (row < m) {
+            const uint8_t *blk = act + ((int64_t)row * nb + b) * Q8K_BYTES;
+            const short *bs = reinterpret_cast<const short *>(blk + 4 + 256) + c * 8;
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn((float)bs[2 * j], (float)bs[2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            out = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        *reinterpret_cast<uint4 *>(minb + min_tile_offset(t, c * 8)) = out;
+    }
+    for (int t = threadIdx.x; t < 128; t += blockDim.x) {
+        const int row = mt * kGemmBM + t;
+        dat[t] = row < m ? *reinterpret_cast<const float *>(act + ((int64_t)row * nb + b) * Q8K_BYTES) : 0.0f;
+    }
+}
+
+// ---- tcgen05 wrappers ----
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+    return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// Abortable bounded wait: gives up when the CTA-wide abort flag is raised or the poll budget runs out.
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < kMaxSpins; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63) {
+            if (*abort_flag) return false;
+            if (i > 4096) __nanosleep(32);
+        }
+    }
+    *abort_flag = 1;
+    atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
+    return false;
+}
+
+struct GemmParams {
+    const uint8_t *w;        // Q4_K blocks [n][k/256], 16-byte aligned
+    const uint8_t *scratch;  // planes written by gemm_prep_kernel
+    float *y;
+    int64_t ldy;
+    int64_t row_bytes;
+    int m, n, k;
+    int n_tiles;  // tiles along the weight rows
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
+    uint64_t *a_full = bars, *a_empty = bars + kGemmStages, *b_full = bars + 2 * kGemmStages, *b_empty = bars + 3 * kGemmStages;
+    uint64_t *mina_full = bars + 4 * kGemmStages, *mina_empty = mina_full + 2, *minb_full = mina_full + 4,
+             *minb_empty = mina_full + 6, *acc_full = mina_full + 8, *acc_empty = mina_full + 10;
+    // da tiles ride on the min-B barriers for "full"; their release needs the epilogue warps as well
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + kOffMisc + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nt = blockIdx.x % p.n_tiles, mt = blockIdx.x / p.n_tiles;
+    const int n0 = nt * kGemmBN, m0 = mt * kGemmBM;
+    const int nb = p.k / 256;
+    const GemmScratch lay = gemm_scratch_layout(p.m, p.k);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(&a_full[s], 4);
+            mbar_init(&a_empty[s], 1);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&mina_full[i], 4);
+            mbar_init(&mina_empty[i], 1);
+            mbar_init(&minb_full[i], 1);
+            mbar_init(&minb_empty[i], 1 + 8);  // MMA commit + the eight epilogue warps (da scales)
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 8);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 13) {  // tensor memory: all 512 columns, two (S, Mn) accumulator pairs
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3, half = warp >> 2;
+        const int r = q * 32 + lane;  // row of the tile == TMEM lane
+        const int n = n0 + r;
+        const bool row_ok = n < p.n;
+        const uint8_t *wrow = p.w + (int64_t)(row_ok ? n : 0) * p.row_bytes;
+        uint64_t out2[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) out2[j] = 0ull;
+        uint32_t hdr_next = row_ok ? __ldg(reinterpret_cast<const uint32_t *>(wrow)) : 0u;
+        bool ok = true;
+        for (int b = 0; b < nb && ok; ++b) {
+            const int buf = b & 1;
+            const uint32_t par = (b >> 1) & 1;
+            const uint32_t hdr = hdr_next;
+            if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * Q4K_BYTES));
+            const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
+            const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
+            ok = mbar_wait_abortable(&acc_full[buf], par, abort_flag) && mbar_wait_abortable(&minb_full[buf], par, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const float *da = reinterpret_cast<const float *>(smem + kOffDa + buf * kGemmDaBytes) + half * 64;
+            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * 64);
+#pragma unroll
+            for (int chunk = 0; chunk < 2; ++chunk) {
+                uint32_t v[32];
+                tmem_ld32(t_main + chunk * 32, v);  // S
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float2 d2 = *reinterpret_cast<const float2 *>(da + chunk * 32 + 2 * j);
+                    const uint64_t t = mul_f32x2(pack2f(d2.x, d2.y), dw2);
+                    out2[chunk * 16 + j] = fma_f32x2(t, (uint64_t)v[2 * j] | ((uint64_t)v[2 * j + 1] << 32), out2[chunk * 16 + j]);
+                }
+                tmem_ld32(t_main + 128 + chunk * 32, v);  // Mn
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float2 d2 = *reinterpret_cast<const float2 *>(da + chunk * 32 + 2 * j);
+                    const uint64_t t = mul_f32x2(pack2f(d2.x, d2.y), ndmin2);
+                    out2[chunk * 16 + j] = fma_f32x2(t, (uint64_t)v[2 * j] | ((uint64_t)v[2 * j + 1] << 32), out2[chunk * 16 + j]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&acc_empty[buf]);
+                mbar_arrive(&minb_empty[buf]);
+            }
+        }
+        if (ok && row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int mrow = m0 + half * 64 + 2 * j;
+                if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] & 0xffffffffu));
+                if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
+            }
+        }
+    } else if (warp < 12) {
+        // ------------------------------ weight producers ------------------------------
+        const int r = threadIdx.x - 256;  // row of the tile
+        const int n = n0 + r;
+        const bool row_ok = n < p.n;
+        const uint8_t *wrow = p.w + (int64_t)(row_ok ? n : 0) * p.row_bytes;
+        uint8_t *a_base = smem + kOffA + (r >> 3) * 1024 + (r & 7) * 128;
+        const int sw = r & 7;
+        bool ok = true;
+        for (int b = 0; b < nb && ok; ++b) {
+            const uint4 *blk = reinterpret_cast<const uint4 *>(wrow + (int64_t)b * Q4K_BYTES);
+            uint4 hq = make_uint4(0, 0, 0, 0);
+            if (row_ok) hq = __ldg(blk);
+            // 6-bit scales / mins (utils.rs:50-60), four per word
+            const uint32_t scw[2] = {hq.y & 0x3f3f3f3fu, (hq.w & 0x0f0f0f0fu) | (((hq.y >> 6) & 0x03030303u) << 4)};
+            const uint32_t mnw[2] = {hq.z & 0x3f3f3f3fu, ((hq.w >> 4) & 0x0f0f0f0fu) | (((hq.z >> 6) & 0x03030303u) << 4)};
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int it = b * 4 + g, s = it % kGemmStages;
+                uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
+                if (row_ok) {
+                    q0 = __ldg(blk + 1 + 2 * g);
+                    q1 = __ldg(blk + 2 + 2 * g);
+                }
+                if (it >= kGemmStages) ok = mbar_wait_abortable(&a_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+                if (!ok) break;
+                const uint32_t sc_lo = (scw[g >> 1] >> (16 * (g & 1))) & 0xff, sc_hi = (scw[g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
+                // f16 value of sc*q without an int->float convert: (1024 + q) * sc - 1024 * sc, one exact FMA
+                const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo));
+                const __half2 s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
+                const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), c_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
+                const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                uint8_t *dst = a_base + s * kGemmStageBytes;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the stage
+                    // chunks 0-3: low nibbles of bytes 8c..8c+7; chunks 4-7: high nibbles of bytes 8(c-4)..
+                    const uint32_t w0 = qw[2 * (c & 3)], w1 = qw[2 * (c & 3) + 1];
+                    const uint32_t n0w = (c < 4) ? (w0 & 0x0f0f0f0fu) : ((w0 >> 4) & 0x0f0f0f0fu);
+                    const uint32_t n1w = (c < 4) ? (w1 & 0x0f0f0f0fu) : ((w1 >> 4) & 0x0f0f0f0fu);
+                    const __half2 sc2 = (c < 4) ? s_lo : s_hi, cc2 = (c < 4) ? c_lo : c_hi;
+                    uint32_t h[4];
+                    h[0] = __byte_perm(n0w, 0x64646464u, 0x4140);
+                    h[1] = __byte_perm(n0w, 0x64646464u, 0x4342);
+                    h[2] = __byte_perm(n1w, 0x64646464u, 0x4140);
+                    h[3] = __byte_perm(n1w, 0x64646464u, 0x4342);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __half2 v = __hfma2(*reinterpret_cast<const __half2 *>(&h[j]), sc2, cc2);
+                        h[j] = *reinterpret_cast<const uint32_t *>(&v);
+                    }
+                    *reinterpret_cast<uint4 *>(dst + ((c ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+                fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[s]);
+            }
+            if (!ok) break;
+            // min tile: m_j duplicated against the two 16-element bsums of sub-block j
+            const int buf = b & 1;
+            if (b >= 2) ok = mbar_wait_abortable(&mina_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+            if (!ok) break;
+            uint8_t *md = smem + kOffMinA + buf * kGemmMinBytes;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned short mv = (unsigned short)((mnw[c] >> (8 * j)) & 0xff);
+                    const __half2 v = __half2half2(__ushort2half_rn(mv));
+                    h[j] = *reinterpret_cast<const uint32_t *>(&v);
+                }
+                *reinterpret_cast<uint4 *>(md + min_tile_offset(r, c * 8)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&mina_full[buf]);
+        }
+    } else if (warp == 12) {
+        // ------------------------------ activation tiles: bulk copies ------------------------------
+        if (lane == 0) {
+            const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmStageBytes;
+            const uint8_t *minb = p.scratch + lay.minb + (int64_t)mt * nb * kGemmMinBytes;
+            const uint8_t *dat = p.scratch + lay.dat + (int64_t)mt * nb * kGemmDaBytes;
+            bool ok = true;
+            for (int b = 0; b < nb && ok; ++b) {
+                for (int g = 0; g < 4 && ok; ++g) {
+                    const int it = b * 4 + g, s = it % kGemmStages;
+                    if (it >= kGemmStages) ok = mbar_wait_abortable(&b_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&b_full[s], kGemmStageBytes);
+                    bulk_g2s(smem + kOffB + s * kGemmStageBytes, bimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &b_full[s]);
+                }
+                if (!ok) break;
+                const int buf = b & 1;
+                if (b >= 2) ok = mbar_wait_abortable(&minb_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&minb_full[buf], kGemmMinBytes + kGemmDaBytes);
+                bulk_g2s(smem + kOffMinB + buf * kGemmMinBytes, minb + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &minb_full[buf]);
+                bulk_g2s(smem + kOffDa + buf * kGemmDaBytes, dat + (int64_t)b * kGemmDaBytes, kGemmDaBytes, &minb_full[buf]);
+            }
+        }
+    } else if (warp == 13) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(kGemmBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
+            bool ok = true;
+            for (int b = 0; b < nb && ok; ++b) {
+                const int buf = b & 1;
+                const uint32_t par = (b >> 1) & 1;
+                if (b >= 2) ok = mbar_wait_abortable(&acc_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
+                for (int g = 0; g < 4 && ok; ++g) {
+                    const int it = b * 4 + g, s = it % kGemmStages;
+                    const uint32_t sp = (it / kGemmStages) & 1;
+                    ok = mbar_wait_abortable(&a_full[s], sp, abort_flag) && mbar_wait_abortable(&b_full[s], sp, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + kOffA + s * kGemmStageBytes);
+                    const uint32_t b_addr = smem_u32(smem + kOffB + s * kGemmStageBytes);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {  // K = 16 per instruction: 32 bytes along the swizzled row
+                        const uint64_t ad = umma_desc(a_addr + kk * 32, 16, 1024, 2);
+                        const uint64_t bd = umma_desc(b_addr + kk * 32, 16, 1024, 2);
+                        umma_f16(d_main, ad, bd, idesc, (g | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&a_empty[s]);
+                    umma_commit(&b_empty[s]);
+                }
+                if (!ok) break;
+                ok = mbar_wait_abortable(&mina_full[buf], par, abort_flag) && mbar_wait_abortable(&minb_full[buf], par, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t mad = umma_desc(smem_u32(smem + kOffMinA + buf * kGemmMinBytes), 128, 256, 0);
+                const uint64_t mbd = umma_desc(smem_u32(smem + kOffMinB + buf * kGemmMinBytes), 128, 256, 0);
+                umma_f16(d_min, mad, mbd, idesc, 0u);
+                umma_commit(&mina_empty[buf]);
+                umma_commit(&minb_empty[buf]);
+                umma_commit(&acc_full[buf]);
+            }
+        }
+    }
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 13) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, int64_t m, int64_t n, int64_t k,
+                       int64_t ldy, void *workspace, int /*sm_count*/, int max_smem, cudaStream_t stream, bool &handled,
+                       int &cuda_err) {
     handled = false;
+    if (w_dtype != LLOOM_Q4_K || m <= 8) return LLOOM_OK;
+    if (kGemmSmemBytes > max_smem) return LLOOM_OK;
+    handled = true;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+        if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
+        configured = true;
+    }
+    const int64_t mt = gemm_m_tiles(m), nb = k / 256;
+    gemm_prep_kernel<<<(unsigned)(mt * nb), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, (uint8_t *)workspace);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
+    GemmParams p;
+    p.w = (const uint8_t *)w;
+    p.scratch = (const uint8_t *)workspace;
+    p.y = y;
+    p.ldy = ldy;
+    p.row_bytes = nb * Q4K_BYTES;
+    p.m = (int)m;
+    p.n = (int)n;
+    p.k = (int)k;
+    p.n_tiles = (int)((n + kGemmBN - 1) / kGemmBN);
+    gemm_q4k_kernel<<<(unsigned)(p.n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
     return LLOOM_OK;
 }
 
