@@ -57,13 +57,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: every spin in this library has an iteration limit.  On expiry the status word is
-// set and false is returned; the caller unwinds (no trap, the context stays usable).
+// Bounded wait: every spin in this library is limited both in polls and in wall time (a single
+// mbarrier.try_wait may itself suspend the thread for a while, so a poll count alone is not a time
+// bound).  On expiry the status word is set and false is returned; the caller unwinds (no trap, the
+// context stays usable).
 constexpr uint32_t kMaxSpins = 1u << 24;
+constexpr unsigned long long kMaxWaitNs = 2000000000ull;  // 2 s
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < kMaxSpins; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 1024) __nanosleep(64);
+        if ((i & 255) == 255) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kMaxWaitNs) break;
+            __nanosleep(64);
+        }
     }
     atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
     return false;

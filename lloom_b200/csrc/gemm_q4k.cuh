@@ -28,6 +28,8 @@
 
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace lloom {
@@ -180,19 +182,37 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
     return d;
 }
 
-// Abortable bounded wait: gives up when the CTA-wide abort flag is raised or the poll budget runs out.
+// Abortable bounded wait: gives up when the CTA-wide abort flag is raised or the time budget runs out.
+// kSleepNs > 0 makes the waiter back off between polls: every role except the MMA issuer waits this
+// way, so that their polling does not crowd the shared-memory pipe the issuer's own barrier
+// operations and commits go through.
+template <int kSleepNs>
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < kMaxSpins; ++i) {
+        if (kSleepNs > 0) __nanosleep(kSleepNs);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63) {
             if (*abort_flag) return false;
-            if (i > 4096) __nanosleep(32);
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kMaxWaitNs) break;
         }
     }
     *abort_flag = 1;
     atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
     return false;
 }
+
+#ifdef LLOOM_TRACE
+__device__ unsigned long long g_gemm_trace[4][64][8];
+__device__ unsigned long long g_mma_micro[64][8];  // per superblock (stage 1): clock64 after each step of the MMA loop  // development build: [role][superblock][event] of CTA 0, SM cycles
+#define LLOOM_GTRACE(role, b, ev) do { if (blockIdx.x == 0 && (b) < 64) { \
+    g_gemm_trace[role][b][ev] = (unsigned long long)clock64(); } } while (0)
+#else
+#define LLOOM_GTRACE(role, b, ev) do { } while (0)
+#endif
 
 struct GemmParams {
     const uint8_t *w;        // Q4_K blocks [n][k/256], 16-byte aligned
@@ -202,6 +222,7 @@ struct GemmParams {
     int64_t row_bytes;
     int m, n, k;
     int n_tiles;  // tiles along the weight rows
+    int dbg;      // development switches (always 0 outside trace builds)
 };
 
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmParams p) {
@@ -268,11 +289,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * Q4K_BYTES));
             const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
             const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
-            ok = mbar_wait_abortable(&acc_full[buf], par, abort_flag) && mbar_wait_abortable(&minb_full[buf], par, abort_flag);
+            ok = mbar_wait_abortable<96>(&acc_full[buf], par, abort_flag) && mbar_wait_abortable<96>(&minb_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            if (threadIdx.x == 0) LLOOM_GTRACE(1, b, 0);
             const float *da = reinterpret_cast<const float *>(smem + kOffDa + buf * kGemmDaBytes) + half * 64;
             const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * 64);
+            if (!(p.dbg & 2))
 #pragma unroll
             for (int chunk = 0; chunk < 2; ++chunk) {
                 uint32_t v[32];
@@ -299,6 +322,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
                 mbar_arrive(&acc_empty[buf]);
                 mbar_arrive(&minb_empty[buf]);
             }
+            if (threadIdx.x == 0) LLOOM_GTRACE(1, b, 1);
         }
         if (ok && row_ok) {
 #pragma unroll
@@ -317,23 +341,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
         uint8_t *a_base = smem + kOffA + (r >> 3) * 1024 + (r & 7) * 128;
         const int sw = r & 7;
         bool ok = true;
+        // the row's 144-byte block, fetched one superblock ahead so that the L2/HBM latency is off the stage loop
+        uint4 nxt[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) nxt[i] = make_uint4(0, 0, 0, 0);
+        if (row_ok) {
+            const uint4 *blk0 = reinterpret_cast<const uint4 *>(wrow);
+#pragma unroll
+            for (int i = 0; i < 9; ++i) nxt[i] = __ldg(blk0 + i);
+        }
         for (int b = 0; b < nb && ok; ++b) {
-            const uint4 *blk = reinterpret_cast<const uint4 *>(wrow + (int64_t)b * Q4K_BYTES);
-            uint4 hq = make_uint4(0, 0, 0, 0);
-            if (row_ok) hq = __ldg(blk);
+            uint4 cur[9];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+            if (row_ok && b + 1 < nb) {
+                const uint4 *blk1 = reinterpret_cast<const uint4 *>(wrow + (int64_t)(b + 1) * Q4K_BYTES);
+#pragma unroll
+                for (int i = 0; i < 9; ++i) nxt[i] = __ldg(blk1 + i);
+            }
+            const uint4 hq = cur[0];
             // 6-bit scales / mins (utils.rs:50-60), four per word
             const uint32_t scw[2] = {hq.y & 0x3f3f3f3fu, (hq.w & 0x0f0f0f0fu) | (((hq.y >> 6) & 0x03030303u) << 4)};
             const uint32_t mnw[2] = {hq.z & 0x3f3f3f3fu, ((hq.w >> 4) & 0x0f0f0f0fu) | (((hq.z >> 6) & 0x03030303u) << 4)};
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 const int it = b * 4 + g, s = it % kGemmStages;
-                uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
-                if (row_ok) {
-                    q0 = __ldg(blk + 1 + 2 * g);
-                    q1 = __ldg(blk + 2 + 2 * g);
-                }
-                if (it >= kGemmStages) ok = mbar_wait_abortable(&a_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+                const uint4 q0 = cur[1 + 2 * g], q1 = cur[2 + 2 * g];
+                if (it >= kGemmStages) ok = mbar_wait_abortable<96>(&a_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
                 if (!ok) break;
+                if (threadIdx.x == 256) LLOOM_GTRACE(2, b, g);
                 const uint32_t sc_lo = (scw[g >> 1] >> (16 * (g & 1))) & 0xff, sc_hi = (scw[g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
                 // f16 value of sc*q without an int->float convert: (1024 + q) * sc - 1024 * sc, one exact FMA
                 const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo));
@@ -341,6 +377,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
                 const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), c_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
                 const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
                 uint8_t *dst = a_base + s * kGemmStageBytes;
+                if (!(p.dbg & 1))
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the stage
                     // chunks 0-3: low nibbles of bytes 8c..8c+7; chunks 4-7: high nibbles of bytes 8(c-4)..
@@ -367,7 +404,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             if (!ok) break;
             // min tile: m_j duplicated against the two 16-element bsums of sub-block j
             const int buf = b & 1;
-            if (b >= 2) ok = mbar_wait_abortable(&mina_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+            if (b >= 2) ok = mbar_wait_abortable<96>(&mina_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
             if (!ok) break;
             uint8_t *md = smem + kOffMinA + buf * kGemmMinBytes;
 #pragma unroll
@@ -384,65 +421,107 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&mina_full[buf]);
+            if (threadIdx.x == 256) LLOOM_GTRACE(2, b, 4);
         }
     } else if (warp == 12) {
         // ------------------------------ activation tiles: bulk copies ------------------------------
-        if (lane == 0) {
-            const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmStageBytes;
-            const uint8_t *minb = p.scratch + lay.minb + (int64_t)mt * nb * kGemmMinBytes;
-            const uint8_t *dat = p.scratch + lay.dat + (int64_t)mt * nb * kGemmDaBytes;
-            bool ok = true;
-            for (int b = 0; b < nb && ok; ++b) {
-                for (int g = 0; g < 4 && ok; ++g) {
-                    const int it = b * 4 + g, s = it % kGemmStages;
-                    if (it >= kGemmStages) ok = mbar_wait_abortable(&b_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(&b_full[s], kGemmStageBytes);
-                    bulk_g2s(smem + kOffB + s * kGemmStageBytes, bimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &b_full[s]);
+        // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
+        const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmStageBytes;
+        const uint8_t *minb = p.scratch + lay.minb + (int64_t)mt * nb * kGemmMinBytes;
+        const uint8_t *dat = p.scratch + lay.dat + (int64_t)mt * nb * kGemmDaBytes;
+        bool ok = true;
+        for (int b = 0; b < nb && ok; ++b) {
+            for (int g = 0; g < 4 && ok; ++g) {
+                const int it = b * 4 + g, s = it % kGemmStages;
+                if (it >= kGemmStages) ok = mbar_wait_abortable<96>(&b_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+                if (!ok) break;
+                if (lane == 0) {
+                    LLOOM_GTRACE(3, b, g);
+                    if (p.dbg & 4) {
+                        mbar_arrive(&b_full[s]);
+                    } else {
+                        mbar_arrive_expect_tx(&b_full[s], kGemmStageBytes);
+                        bulk_g2s(smem + kOffB + s * kGemmStageBytes, bimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &b_full[s]);
+                    }
                 }
-                if (!ok) break;
-                const int buf = b & 1;
-                if (b >= 2) ok = mbar_wait_abortable(&minb_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
-                if (!ok) break;
+                __syncwarp();
+            }
+            if (!ok) break;
+            const int buf = b & 1;
+            if (b >= 2) ok = mbar_wait_abortable<96>(&minb_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+            if (!ok) break;
+            if (lane == 0) {
                 mbar_arrive_expect_tx(&minb_full[buf], kGemmMinBytes + kGemmDaBytes);
                 bulk_g2s(smem + kOffMinB + buf * kGemmMinBytes, minb + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &minb_full[buf]);
                 bulk_g2s(smem + kOffDa + buf * kGemmDaBytes, dat + (int64_t)b * kGemmDaBytes, kGemmDaBytes, &minb_full[buf]);
             }
+            __syncwarp();
         }
     } else if (warp == 13) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(kGemmBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
-            bool ok = true;
-            for (int b = 0; b < nb && ok; ++b) {
-                const int buf = b & 1;
-                const uint32_t par = (b >> 1) & 1;
-                if (b >= 2) ok = mbar_wait_abortable(&acc_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+        // The whole warp walks the loop; lane 0 issues the MMAs and commits.
+        // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(kGemmBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
+        bool ok = true;
+        for (int b = 0; b < nb && ok; ++b) {
+            const int buf = b & 1;
+            const uint32_t par = (b >> 1) & 1;
+            if (b >= 2) ok = mbar_wait_abortable<0>(&acc_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) LLOOM_GTRACE(0, b, 0);
+            const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
+            for (int g = 0; g < 4 && ok; ++g) {
+                const int it = b * 4 + g, s = it % kGemmStages;
+                const uint32_t sp = (it / kGemmStages) & 1;
+#ifdef LLOOM_TRACE
+                const bool micro = blockIdx.x == 0 && g == 1 && b < 64 && lane == 0;
+                if (micro) g_mma_micro[b][0] = clock64();
+                ok = mbar_wait_abortable<0>(&a_full[s], sp, abort_flag);
+                if (micro) g_mma_micro[b][1] = clock64();
+                ok = ok && mbar_wait_abortable<0>(&b_full[s], sp, abort_flag);
+                if (micro) g_mma_micro[b][2] = clock64();
+#else
+                ok = mbar_wait_abortable<0>(&a_full[s], sp, abort_flag) && mbar_wait_abortable<0>(&b_full[s], sp, abort_flag);
+#endif
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
-                for (int g = 0; g < 4 && ok; ++g) {
-                    const int it = b * 4 + g, s = it % kGemmStages;
-                    const uint32_t sp = (it / kGemmStages) & 1;
-                    ok = mbar_wait_abortable(&a_full[s], sp, abort_flag) && mbar_wait_abortable(&b_full[s], sp, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
+#ifdef LLOOM_TRACE
+                if (micro) g_mma_micro[b][3] = clock64();
+#endif
+                if (lane == 0) {
+                    LLOOM_GTRACE(0, b, 1 + g);
                     const uint32_t a_addr = smem_u32(smem + kOffA + s * kGemmStageBytes);
                     const uint32_t b_addr = smem_u32(smem + kOffB + s * kGemmStageBytes);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {  // K = 16 per instruction: 32 bytes along the swizzled row
                         const uint64_t ad = umma_desc(a_addr + kk * 32, 16, 1024, 2);
                         const uint64_t bd = umma_desc(b_addr + kk * 32, 16, 1024, 2);
-                        umma_f16(d_main, ad, bd, idesc, (g | kk) != 0 ? 1u : 0u);
+                        if (!(p.dbg & 8)) umma_f16(d_main, ad, bd, idesc, (g | kk) != 0 ? 1u : 0u);
                     }
+#ifdef LLOOM_TRACE
+                    if (micro) g_mma_micro[b][4] = clock64();
+#endif
                     umma_commit(&a_empty[s]);
+#ifdef LLOOM_TRACE
+                    if (micro) g_mma_micro[b][5] = clock64();
+#endif
                     umma_commit(&b_empty[s]);
+#ifdef LLOOM_TRACE
+                    if (micro) g_mma_micro[b][6] = clock64();
+#endif
                 }
-                if (!ok) break;
-                ok = mbar_wait_abortable(&mina_full[buf], par, abort_flag) && mbar_wait_abortable(&minb_full[buf], par, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
+                __syncwarp();
+#ifdef LLOOM_TRACE
+                if (micro) g_mma_micro[b][7] = clock64();
+#endif
+            }
+            if (!ok) break;
+            ok = mbar_wait_abortable<0>(&mina_full[buf], par, abort_flag) && mbar_wait_abortable<0>(&minb_full[buf], par, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                LLOOM_GTRACE(0, b, 5);
                 const uint64_t mad = umma_desc(smem_u32(smem + kOffMinA + buf * kGemmMinBytes), 128, 256, 0);
                 const uint64_t mbd = umma_desc(smem_u32(smem + kOffMinB + buf * kGemmMinBytes), 128, 256, 0);
                 umma_f16(d_min, mad, mbd, idesc, 0u);
@@ -450,6 +529,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
                 umma_commit(&minb_empty[buf]);
                 umma_commit(&acc_full[buf]);
             }
+            __syncwarp();
         }
     }
     // ------------------------------ teardown ------------------------------
@@ -488,6 +568,10 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
     p.n = (int)n;
     p.k = (int)k;
     p.n_tiles = (int)((n + kGemmBN - 1) / kGemmBN);
+    p.dbg = 0;
+#ifdef LLOOM_TRACE
+    if (const char *e = getenv("LLOOM_GEMM_DBG")) p.dbg = atoi(e);
+#endif
     gemm_q4k_kernel<<<(unsigned)(p.n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }

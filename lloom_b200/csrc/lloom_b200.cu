@@ -394,6 +394,12 @@ int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float
 int lloom_b200_read_trace(unsigned long long *out) {  // development build only
     return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
 }
+int lloom_b200_read_gemm_trace(unsigned long long *out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(g_gemm_trace));
+}
+int lloom_b200_read_mma_micro(unsigned long long *out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, g_mma_micro, sizeof(g_mma_micro));
+}
 #endif
 
 int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,

@@ -192,6 +192,43 @@ def test_full_size_properties_q4k(dev, oracle):
         assert run_fwd(dev, 12, wq, n, k, x[:m]).tobytes() == got[:m].tobytes()
 
 
+@pytest.mark.parametrize("n,k,m", [(128, 256, 128), (130, 512, 70), (256, 1024, 96), (384, 2048, 9), (1000, 4096, 200),
+                                   (64, 768, 129)])
+def test_gemm_q4k_tensor_core_path(dev, oracle, n, k, m):
+    """Prefill GEMM (m > 8, Q4_K) on the tcgen05 kernel: ragged tiles in both directions, 1..16 superblocks."""
+    _, x, wq = make_case(oracle, 12, n, k, m, seed=n + k + m)
+    ref = oracle.matmul(12, x, wq, n, nthreads=8)
+    absum = oracle.matmul_absum(12, x, wq, n, nthreads=8)
+    got = run_fwd(dev, 12, wq, n, k, x)
+    assert_matmul_close(got, ref, absum, f"Q4K gemm n={n} k={k} m={m}")
+    assert run_fwd(dev, 12, wq, n, k, x).tobytes() == got.tobytes()  # run-to-run bit-stable
+
+
+def test_gemm_q4k_prefill_config(dev, oracle):
+    """C4 shape [14336, 4096] at M = 512: oracle parity on a sample of rows and columns (the CPU needs minutes for
+    all of it), agreement with the decode GEMV on the same tokens, and every output finite."""
+    from lloom_b200 import quantized as Q
+
+    n, k, m = 14336, 4096, 512
+    w = np.random.default_rng(6).standard_normal((n, k)).astype(np.float32) * np.float32(0.02)
+    wq = oracle.quantize(12, w, nthreads=8)
+    x = np.random.default_rng(7).standard_normal((m, k)).astype(np.float32)
+    got = run_fwd(dev, 12, wq, n, k, x)
+    assert np.isfinite(got).all()
+    rng = np.random.default_rng(1)
+    rows = np.sort(rng.choice(m, 24, replace=False))
+    cols = np.sort(rng.choice(n, 1536, replace=False))
+    wsub = np.ascontiguousarray(wq[cols])
+    ref = oracle.matmul(12, x[rows], wsub, len(cols), nthreads=8)
+    absum = oracle.matmul_absum(12, x[rows], wsub, len(cols), nthreads=8)
+    assert_matmul_close(got[np.ix_(rows, cols)], ref, absum, "C4 sample")
+    gemv = run_fwd(dev, 12, wq, n, k, x[:8])  # the same first eight tokens through the decode kernel
+    absum8 = oracle.matmul_absum(12, x[:8], np.ascontiguousarray(wq[:4096]), 4096, nthreads=8)
+    err = np.abs(gemv[:, :4096].astype(np.float64) - got[:8, :4096]) / np.maximum(absum8, 1e-30)
+    assert err.max() <= REL_TOL
+    assert Q.device_status() == 0
+
+
 @pytest.mark.parametrize("dt", [8, 12, 14])
 def test_dequantize_and_embedding_bit_exact(dev, oracle, dt):
     """T::to_float parity (f32 and f16) and the embedding gather (run_quantized_embedding, :304-315)."""
