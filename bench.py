@@ -366,6 +366,84 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_lm_head(args):
+    """`--workload lm_head`: the Q6_K lm_head [128256, 4096] at M = 1, output rows sharded over the ranks and the
+    logits all-gathered with NCCL (strong scaling: the matrix is fixed, each rank streams 1/G of it)."""
+    import torch
+    import torch.distributed as dist
+
+    import lloom_b200 as lb
+    from lloom_b200 import _lib
+    from lloom_b200 import quantized as Q
+    from lloom_b200.sharded import ShardPlan, gather_rows
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    n_total, k, dtype = 128256, 4096, lb.GgmlDType.Q6K
+    row_bytes = k // 256 * 210
+    plan = ShardPlan(n_total, world)
+    lo, hi = plan.range_of(rank)
+    rows = hi - lo
+    chunks = []
+    c0 = lo
+    while c0 < hi:  # rows are drawn per 4096-row chunk so that any sharding sees the same matrix
+        c1 = min(hi, (c0 // 4096 + 1) * 4096)
+        blk = np.random.default_rng([4, c0 // 4096]).standard_normal((4096, k)).astype(np.float32) * np.float32(0.02)
+        chunks.append(Q.quantize_weights_host(blk[c0 % 4096: c0 % 4096 + (c1 - c0)], dtype))
+        c0 = c1
+    shard = np.concatenate(chunks)
+    copies = max(1, -(-int(2.2 * 126e6) // (rows * row_bytes)))
+    pool = [lb.QTensor.from_data(shard, dtype, (rows, k), dev) for _ in range(copies)]
+    _lib.lib().lloom_b200_set_launch_overlap(1)
+    x = torch.from_numpy(np.random.default_rng(5).standard_normal((1, k)).astype(np.float32)).to(dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def step():
+        out = None
+        for q in pool:
+            y_local = q.fwd(x)
+            out = gather_rows(y_local, plan) if world > 1 else y_local
+        return out
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    per_matmul_us = ms / steps / copies * 1e3
+    value = n_total * row_bytes / (per_matmul_us * 1e-6) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "q6k_lm_head_gemv_weight_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "config": {"workload": "C3 Q6_K lm_head GEMV [128256x4096], M=1, rows sharded over ranks + NCCL all-gather",
+                       "copies_per_rank": copies, "us_per_sharded_matmul": round(per_matmul_us, 2),
+                       "per_gpu_GBps": round(value / world, 1), "timing": "CUDA events, eager launches (no graph)"},
+            "gpu_launches": steps * copies}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one M=1 GEMV launch on the full [14336,4096] matrix,
 # from the ncu capture summarised in profiles/gemv_q4k_m1.md (None until captured).
 GEMV_DRAM_TRAFFIC_BYTES = None
@@ -378,9 +456,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--workload", default="c2", choices=["c2", "lm_head"],
+                    help="c2: the headline Q4_K decode GEMV; lm_head: the row-sharded Q6_K lm_head with all-gather")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "lm_head":
+        run_lm_head(args)
     else:
         run_gpu(args)
 
