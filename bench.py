@@ -445,8 +445,8 @@ def run_lm_head(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one M=1 GEMV launch on the full [14336,4096] matrix,
-# from the ncu capture summarised in profiles/gemv_q4k_m1.md (None until captured).
-GEMV_DRAM_TRAFFIC_BYTES = None
+# from the ncu capture summarised in profiles/gemv_q4k_m1.md.
+GEMV_DRAM_TRAFFIC_BYTES = 33089280
 
 
 def main():
