@@ -28,18 +28,17 @@
 
 #include <cuda_fp16.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace lloom {
 
 constexpr int kGemmBN = 128;          // weight rows per tile (UMMA M)
 constexpr int kGemmBM = 128;          // activation rows per tile (UMMA N)
-constexpr int kGemmStageBytes = 128 * 64 * 2;  // one k-stage (64 of K) of either operand, f16
+constexpr int kGemmAtomBytes = 128 * 64 * 2;   // one swizzle atom: 128 rows x 64 of K, f16
+constexpr int kGemmStageBytes = 2 * kGemmAtomBytes;  // a pipeline stage covers 128 of K: two atoms per operand
 constexpr int kGemmMinBytes = 128 * 16 * 2;    // min-term operand tile (K = 16), f16
 constexpr int kGemmDaBytes = 128 * 4;
-constexpr int kGemmStages = 4;
+constexpr int kGemmStages = 3;
 constexpr int kGemmThreads = 512;
 
 // ---- shared memory map (offsets from a 1024-byte aligned base) ----
@@ -49,7 +48,7 @@ constexpr int kOffMinA = kOffB + kGemmStages * kGemmStageBytes;
 constexpr int kOffMinB = kOffMinA + 2 * kGemmMinBytes;
 constexpr int kOffDa = kOffMinB + 2 * kGemmMinBytes;
 constexpr int kOffBars = kOffDa + 2 * kGemmDaBytes;
-constexpr int kGemmNumBars = 4 * kGemmStages + 12;
+constexpr int kGemmNumBars = 2 * kGemmStages + 6;
 constexpr int kOffMisc = kOffBars + kGemmNumBars * 8;
 constexpr int kGemmSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 
@@ -63,7 +62,7 @@ __host__ __device__ inline GemmScratch gemm_scratch_layout(int64_t m, int64_t k)
     GemmScratch s;
     const int64_t mt = gemm_m_tiles(m), nb = k / 256;
     s.bimg = 0;
-    s.minb = s.bimg + mt * (k / 64) * kGemmStageBytes;
+    s.minb = s.bimg + mt * (k / 64) * kGemmAtomBytes;
     s.dat = s.minb + mt * nb * kGemmMinBytes;
     s.total = (s.dat + mt * nb * kGemmDaBytes + 255) / 256 * 256;
     return s;
@@ -92,7 +91,7 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
     const int nb = k / 256;
     const int mt = blockIdx.x / nb, b = blockIdx.x % nb;
     const GemmScratch lay = gemm_scratch_layout(m, k);
-    uint8_t *bimg = scratch + lay.bimg + ((int64_t)mt * (k / 64) + (int64_t)b * 4) * kGemmStageBytes;
+    uint8_t *bimg = scratch + lay.bimg + ((int64_t)mt * (k / 64) + (int64_t)b * 4) * kGemmAtomBytes;
     uint8_t *minb = scratch + lay.minb + ((int64_t)mt * nb + b) * kGemmMinBytes;
     float *dat = reinterpret_cast<float *>(scratch + lay.dat) + ((int64_t)mt * nb + b) * 128;
     for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
@@ -110,7 +109,7 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
             out = make_uint4(cvt2(q.x, 0), cvt2(q.x, 16), cvt2(q.y, 0), cvt2(q.y, 16));
         }
         const int ks = c >> 3, e = (c & 7) * 8;
-        *reinterpret_cast<uint4 *>(bimg + (int64_t)ks * kGemmStageBytes + sw128_offset(t, e)) = out;
+        *reinterpret_cast<uint4 *>(bimg + (int64_t)ks * kGemmAtomBytes + sw128_offset(t, e)) = out;
     }
     for (int i = threadIdx.x; i < 128 * 2; i += blockDim.x) {
         const int t = i >> 1, c = i & 1;
@@ -205,15 +204,6 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t pari
     return false;
 }
 
-#ifdef LLOOM_TRACE
-__device__ unsigned long long g_gemm_trace[4][64][8];
-__device__ unsigned long long g_mma_micro[64][8];  // per superblock (stage 1): clock64 after each step of the MMA loop  // development build: [role][superblock][event] of CTA 0, SM cycles
-#define LLOOM_GTRACE(role, b, ev) do { if (blockIdx.x == 0 && (b) < 64) { \
-    g_gemm_trace[role][b][ev] = (unsigned long long)clock64(); } } while (0)
-#else
-#define LLOOM_GTRACE(role, b, ev) do { } while (0)
-#endif
-
 struct GemmParams {
     const uint8_t *w;        // Q4_K blocks [n][k/256], 16-byte aligned
     const uint8_t *scratch;  // planes written by gemm_prep_kernel
@@ -222,17 +212,20 @@ struct GemmParams {
     int64_t row_bytes;
     int m, n, k;
     int n_tiles;  // tiles along the weight rows
-    int dbg;      // development switches (always 0 outside trace builds)
 };
 
+// Pipeline barriers.  A stage (128 of K of both operands) has one "full" barrier, completed by the four
+// weight-producer warps plus the bulk copy's transaction bytes, and one "empty" barrier, completed by a single
+// tcgen05.commit -- one commit and one wait per stage keep the issuing thread's serial overhead below the
+// tensor time of the stage.  Per superblock parity (two of each): min_full (min tiles + activation scales
+// landed), acc_full (commit after the superblock's last MMA: accumulators ready, min tiles free), acc_empty
+// (the eight epilogue warps have drained the accumulators and are done with the scales).
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
-    uint64_t *a_full = bars, *a_empty = bars + kGemmStages, *b_full = bars + 2 * kGemmStages, *b_empty = bars + 3 * kGemmStages;
-    uint64_t *mina_full = bars + 4 * kGemmStages, *mina_empty = mina_full + 2, *minb_full = mina_full + 4,
-             *minb_empty = mina_full + 6, *acc_full = mina_full + 8, *acc_empty = mina_full + 10;
-    // da tiles ride on the min-B barriers for "full"; their release needs the epilogue warps as well
+    uint64_t *full = bars, *empty = bars + kGemmStages;
+    uint64_t *min_full = bars + 2 * kGemmStages, *acc_full = min_full + 2, *acc_empty = min_full + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + kOffMisc + 4);
 
@@ -244,16 +237,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
-            mbar_init(&a_full[s], 4);
-            mbar_init(&a_empty[s], 1);
-            mbar_init(&b_full[s], 1);
-            mbar_init(&b_empty[s], 1);
+            mbar_init(&full[s], 4 + 1);
+            mbar_init(&empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&mina_full[i], 4);
-            mbar_init(&mina_empty[i], 1);
-            mbar_init(&minb_full[i], 1);
-            mbar_init(&minb_empty[i], 1 + 8);  // MMA commit + the eight epilogue warps (da scales)
+            mbar_init(&min_full[i], 4 + 1);
             mbar_init(&acc_full[i], 1);
             mbar_init(&acc_empty[i], 8);
         }
@@ -289,13 +277,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * Q4K_BYTES));
             const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
             const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
-            ok = mbar_wait_abortable<96>(&acc_full[buf], par, abort_flag) && mbar_wait_abortable<96>(&minb_full[buf], par, abort_flag);
+            ok = mbar_wait_abortable<96>(&min_full[buf], par, abort_flag) && mbar_wait_abortable<96>(&acc_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            if (threadIdx.x == 0) LLOOM_GTRACE(1, b, 0);
             const float *da = reinterpret_cast<const float *>(smem + kOffDa + buf * kGemmDaBytes) + half * 64;
             const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * 64);
-            if (!(p.dbg & 2))
 #pragma unroll
             for (int chunk = 0; chunk < 2; ++chunk) {
                 uint32_t v[32];
@@ -318,11 +304,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&acc_empty[buf]);
-                mbar_arrive(&minb_empty[buf]);
-            }
-            if (threadIdx.x == 0) LLOOM_GTRACE(1, b, 1);
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
         if (ok && row_ok) {
 #pragma unroll
@@ -364,22 +346,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             const uint32_t scw[2] = {hq.y & 0x3f3f3f3fu, (hq.w & 0x0f0f0f0fu) | (((hq.y >> 6) & 0x03030303u) << 4)};
             const uint32_t mnw[2] = {hq.z & 0x3f3f3f3fu, ((hq.w >> 4) & 0x0f0f0f0fu) | (((hq.z >> 6) & 0x03030303u) << 4)};
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int it = b * 4 + g, s = it % kGemmStages;
+            for (int g = 0; g < 4; ++g) {  // 64-element group g -> atom (g & 1) of stage (b*2 + g/2)
+                const int it = b * 2 + (g >> 1), s = it % kGemmStages;
                 const uint4 q0 = cur[1 + 2 * g], q1 = cur[2 + 2 * g];
-                if (it >= kGemmStages) ok = mbar_wait_abortable<96>(&a_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+                if ((g & 1) == 0 && it >= kGemmStages)
+                    ok = mbar_wait_abortable<96>(&empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
                 if (!ok) break;
-                if (threadIdx.x == 256) LLOOM_GTRACE(2, b, g);
                 const uint32_t sc_lo = (scw[g >> 1] >> (16 * (g & 1))) & 0xff, sc_hi = (scw[g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
                 // f16 value of sc*q without an int->float convert: (1024 + q) * sc - 1024 * sc, one exact FMA
                 const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo));
                 const __half2 s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
                 const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), c_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
                 const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                uint8_t *dst = a_base + s * kGemmStageBytes;
-                if (!(p.dbg & 1))
+                uint8_t *dst = a_base + s * kGemmStageBytes + (g & 1) * kGemmAtomBytes;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the stage
+                for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the atom
                     // chunks 0-3: low nibbles of bytes 8c..8c+7; chunks 4-7: high nibbles of bytes 8(c-4)..
                     const uint32_t w0 = qw[2 * (c & 3)], w1 = qw[2 * (c & 3) + 1];
                     const uint32_t n0w = (c < 4) ? (w0 & 0x0f0f0f0fu) : ((w0 >> 4) & 0x0f0f0f0fu);
@@ -397,14 +378,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
                     }
                     *reinterpret_cast<uint4 *>(dst + ((c ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
                 }
-                fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&a_full[s]);
+                if (g & 1) {
+                    fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[s]);
+                }
             }
             if (!ok) break;
-            // min tile: m_j duplicated against the two 16-element bsums of sub-block j
+            // min tile: m_j duplicated against the two 16-element bsums of sub-block j; free once the MMAs of
+            // superblock b-2 have completed (acc_full of that superblock)
             const int buf = b & 1;
-            if (b >= 2) ok = mbar_wait_abortable<96>(&mina_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+            if (b >= 2) ok = mbar_wait_abortable<96>(&acc_full[buf], ((b >> 1) - 1) & 1, abort_flag);
             if (!ok) break;
             uint8_t *md = smem + kOffMinA + buf * kGemmMinBytes;
 #pragma unroll
@@ -420,40 +404,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&mina_full[buf]);
-            if (threadIdx.x == 256) LLOOM_GTRACE(2, b, 4);
+            if (lane == 0) mbar_arrive(&min_full[buf]);
         }
     } else if (warp == 12) {
         // ------------------------------ activation tiles: bulk copies ------------------------------
         // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
-        const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmStageBytes;
+        const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmAtomBytes;
         const uint8_t *minb = p.scratch + lay.minb + (int64_t)mt * nb * kGemmMinBytes;
         const uint8_t *dat = p.scratch + lay.dat + (int64_t)mt * nb * kGemmDaBytes;
         bool ok = true;
         for (int b = 0; b < nb && ok; ++b) {
-            for (int g = 0; g < 4 && ok; ++g) {
-                const int it = b * 4 + g, s = it % kGemmStages;
-                if (it >= kGemmStages) ok = mbar_wait_abortable<96>(&b_empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+            for (int h = 0; h < 2 && ok; ++h) {
+                const int it = b * 2 + h, s = it % kGemmStages;
+                if (it >= kGemmStages) ok = mbar_wait_abortable<96>(&empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
                 if (!ok) break;
                 if (lane == 0) {
-                    LLOOM_GTRACE(3, b, g);
-                    if (p.dbg & 4) {
-                        mbar_arrive(&b_full[s]);
-                    } else {
-                        mbar_arrive_expect_tx(&b_full[s], kGemmStageBytes);
-                        bulk_g2s(smem + kOffB + s * kGemmStageBytes, bimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &b_full[s]);
-                    }
+                    mbar_arrive_expect_tx(&full[s], kGemmStageBytes);
+                    bulk_g2s(smem + kOffB + s * kGemmStageBytes, bimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &full[s]);
                 }
                 __syncwarp();
             }
             if (!ok) break;
             const int buf = b & 1;
-            if (b >= 2) ok = mbar_wait_abortable<96>(&minb_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
+            if (b >= 2) {  // min-B tile is free after the MMAs of b-2, the scales after the epilogue of b-2
+                const uint32_t pp = ((b >> 1) - 1) & 1;
+                ok = mbar_wait_abortable<96>(&acc_full[buf], pp, abort_flag) && mbar_wait_abortable<96>(&acc_empty[buf], pp, abort_flag);
+            }
             if (!ok) break;
             if (lane == 0) {
-                mbar_arrive_expect_tx(&minb_full[buf], kGemmMinBytes + kGemmDaBytes);
-                bulk_g2s(smem + kOffMinB + buf * kGemmMinBytes, minb + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &minb_full[buf]);
-                bulk_g2s(smem + kOffDa + buf * kGemmDaBytes, dat + (int64_t)b * kGemmDaBytes, kGemmDaBytes, &minb_full[buf]);
+                mbar_arrive_expect_tx(&min_full[buf], kGemmMinBytes + kGemmDaBytes);
+                bulk_g2s(smem + kOffMinB + buf * kGemmMinBytes, minb + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &min_full[buf]);
+                bulk_g2s(smem + kOffDa + buf * kGemmDaBytes, dat + (int64_t)b * kGemmDaBytes, kGemmDaBytes, &min_full[buf]);
             }
             __syncwarp();
         }
@@ -469,64 +450,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             if (b >= 2) ok = mbar_wait_abortable<0>(&acc_empty[buf], ((b >> 1) - 1) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            if (lane == 0) LLOOM_GTRACE(0, b, 0);
             const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
-            for (int g = 0; g < 4 && ok; ++g) {
-                const int it = b * 4 + g, s = it % kGemmStages;
-                const uint32_t sp = (it / kGemmStages) & 1;
-#ifdef LLOOM_TRACE
-                const bool micro = blockIdx.x == 0 && g == 1 && b < 64 && lane == 0;
-                if (micro) g_mma_micro[b][0] = clock64();
-                ok = mbar_wait_abortable<0>(&a_full[s], sp, abort_flag);
-                if (micro) g_mma_micro[b][1] = clock64();
-                ok = ok && mbar_wait_abortable<0>(&b_full[s], sp, abort_flag);
-                if (micro) g_mma_micro[b][2] = clock64();
-#else
-                ok = mbar_wait_abortable<0>(&a_full[s], sp, abort_flag) && mbar_wait_abortable<0>(&b_full[s], sp, abort_flag);
-#endif
+            for (int h = 0; h < 2 && ok; ++h) {
+                const int it = b * 2 + h, s = it % kGemmStages;
+                ok = mbar_wait_abortable<0>(&full[s], (it / kGemmStages) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-#ifdef LLOOM_TRACE
-                if (micro) g_mma_micro[b][3] = clock64();
-#endif
                 if (lane == 0) {
-                    LLOOM_GTRACE(0, b, 1 + g);
                     const uint32_t a_addr = smem_u32(smem + kOffA + s * kGemmStageBytes);
                     const uint32_t b_addr = smem_u32(smem + kOffB + s * kGemmStageBytes);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {  // K = 16 per instruction: 32 bytes along the swizzled row
-                        const uint64_t ad = umma_desc(a_addr + kk * 32, 16, 1024, 2);
-                        const uint64_t bd = umma_desc(b_addr + kk * 32, 16, 1024, 2);
-                        if (!(p.dbg & 8)) umma_f16(d_main, ad, bd, idesc, (g | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 8; ++kk) {  // K = 16 per instruction: atom kk/4, 32 bytes along its swizzled row
+                        const uint32_t off = (uint32_t)((kk >> 2) * kGemmAtomBytes + (kk & 3) * 32);
+                        umma_f16(d_main, umma_desc(a_addr + off, 16, 1024, 2), umma_desc(b_addr + off, 16, 1024, 2), idesc,
+                                 (h | kk) != 0 ? 1u : 0u);
                     }
-#ifdef LLOOM_TRACE
-                    if (micro) g_mma_micro[b][4] = clock64();
-#endif
-                    umma_commit(&a_empty[s]);
-#ifdef LLOOM_TRACE
-                    if (micro) g_mma_micro[b][5] = clock64();
-#endif
-                    umma_commit(&b_empty[s]);
-#ifdef LLOOM_TRACE
-                    if (micro) g_mma_micro[b][6] = clock64();
-#endif
+                    umma_commit(&empty[s]);
                 }
                 __syncwarp();
-#ifdef LLOOM_TRACE
-                if (micro) g_mma_micro[b][7] = clock64();
-#endif
             }
             if (!ok) break;
-            ok = mbar_wait_abortable<0>(&mina_full[buf], par, abort_flag) && mbar_wait_abortable<0>(&minb_full[buf], par, abort_flag);
+            ok = mbar_wait_abortable<0>(&min_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
-                LLOOM_GTRACE(0, b, 5);
                 const uint64_t mad = umma_desc(smem_u32(smem + kOffMinA + buf * kGemmMinBytes), 128, 256, 0);
                 const uint64_t mbd = umma_desc(smem_u32(smem + kOffMinB + buf * kGemmMinBytes), 128, 256, 0);
                 umma_f16(d_min, mad, mbd, idesc, 0u);
-                umma_commit(&mina_empty[buf]);
-                umma_commit(&minb_empty[buf]);
                 umma_commit(&acc_full[buf]);
             }
             __syncwarp();
@@ -568,10 +518,6 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
     p.n = (int)n;
     p.k = (int)k;
     p.n_tiles = (int)((n + kGemmBN - 1) / kGemmBN);
-    p.dbg = 0;
-#ifdef LLOOM_TRACE
-    if (const char *e = getenv("LLOOM_GEMM_DBG")) p.dbg = atoi(e);
-#endif
     gemm_q4k_kernel<<<(unsigned)(p.n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }

@@ -67,6 +67,19 @@ __device__ __forceinline__ int dot16(const uint4 &a, const uint4 &b, int c) {
     return __dp4a((int)a.w, (int)b.w, c);
 }
 
+// unsigned bytes of a times signed bytes of b (dp4a.u32.s32)
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dot16_us(const uint4 &a, const uint4 &b, int c) {
+    c = dp4a_us(a.x, b.x, c);
+    c = dp4a_us(a.y, b.y, c);
+    c = dp4a_us(a.z, b.z, c);
+    return dp4a_us(a.w, b.w, c);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Per-format units.  A unit is the span of one weight row that a single lane owns: one 256-element
 // superblock for the k-quants, two 32-element blocks for Q8_0.  The lane loads the matching
@@ -122,16 +135,15 @@ struct FmtQ4K {
                 uint4 l0, l1, h0, h1;
                 l0.x = q0.x & 0x0f0f0f0fu; l0.y = q0.y & 0x0f0f0f0fu; l0.z = q0.z & 0x0f0f0f0fu; l0.w = q0.w & 0x0f0f0f0fu;
                 l1.x = q1.x & 0x0f0f0f0fu; l1.y = q1.y & 0x0f0f0f0fu; l1.z = q1.z & 0x0f0f0f0fu; l1.w = q1.w & 0x0f0f0f0fu;
-                h0.x = (q0.x >> 4) & 0x0f0f0f0fu; h0.y = (q0.y >> 4) & 0x0f0f0f0fu;
-                h0.z = (q0.z >> 4) & 0x0f0f0f0fu; h0.w = (q0.w >> 4) & 0x0f0f0f0fu;
-                h1.x = (q1.x >> 4) & 0x0f0f0f0fu; h1.y = (q1.y >> 4) & 0x0f0f0f0fu;
-                h1.z = (q1.z >> 4) & 0x0f0f0f0fu; h1.w = (q1.w >> 4) & 0x0f0f0f0fu;
+                // high nibbles stay in place (16*q as unsigned bytes); the exact factor 16 comes out of the sum below
+                h0.x = q0.x & 0xf0f0f0f0u; h0.y = q0.y & 0xf0f0f0f0u; h0.z = q0.z & 0xf0f0f0f0u; h0.w = q0.w & 0xf0f0f0f0u;
+                h1.x = q1.x & 0xf0f0f0f0u; h1.y = q1.y & 0xf0f0f0f0u; h1.z = q1.z & 0xf0f0f0f0u; h1.w = q1.w & 0xf0f0f0f0u;
                 const int sc_lo = (scw[r][g >> 1] >> (16 * (g & 1))) & 0xff;
                 const int sc_hi = (scw[r][g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
 #pragma unroll
                 for (int m = 0; m < MC; ++m) {
                     const int pl = dot16(l1, alo[m][1], dot16(l0, alo[m][0], 0));
-                    const int ph = dot16(h1, ahi[m][1], dot16(h0, ahi[m][0], 0));
+                    const int ph = dot16_us(h1, ahi[m][1], dot16_us(h0, ahi[m][0], 0)) >> 4;  // a multiple of 16: exact
                     S[r][m] += sc_lo * pl + sc_hi * ph;
                 }
             }
@@ -296,13 +308,15 @@ constexpr int kMaxStages = 8;
 
 #ifdef LLOOM_TRACE
 // Development build only: per-CTA timestamps (ns) of the GEMV's phases.
-__device__ unsigned long long g_trace[256][16];
+__device__ unsigned long long g_trace[16][160][16];  // [launch ring][CTA][event]
+__device__ unsigned int g_trace_cnt[160];
+__shared__ unsigned int s_trace_slot;
 __device__ __forceinline__ unsigned long long trace_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-#define LLOOM_TRACE_MARK(slot) do { if ((threadIdx.x & 31) == 0) g_trace[blockIdx.x][slot] = trace_now(); } while (0)
+#define LLOOM_TRACE_MARK(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 160) g_trace[s_trace_slot & 15][blockIdx.x][slot] = trace_now(); } while (0)
 #else
 #define LLOOM_TRACE_MARK(slot) do { } while (0)
 #endif
@@ -409,22 +423,30 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
         const int nb = p.k / 256;
         short *sums = reinterpret_cast<short *>(act_smem + qs_bytes + round16((int64_t)p.m * nb * 4));
         const int total = p.m * nb;
-        for (int blk = warp; blk < total; blk += p.n_cwarps) {
-            float v[8];
-            load8(p.x + (size_t)blk * 256 + lane * 8, v);
-            uint32_t q_lo, q_hi;
-            float d;
-            int sum16;
-            q8k_quantize_warp(v, lane, q_lo, q_hi, d, sum16);
-            q32[blk * (kQ8KUnitStride / 4) + lane * 2] = q_lo;
-            q32[blk * (kQ8KUnitStride / 4) + lane * 2 + 1] = q_hi;
-            if (lane == 0) dpl[blk] = d;
-            if (p.w_dtype == LLOOM_Q4_K) {
-                const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
-                if ((lane & 3) == 0) sums[blk * 8 + (lane >> 2)] = (short)sum32;
-            } else if ((lane & 1) == 0) {
-                const int mrow = blk / nb, b = blk - mrow * nb, j = lane >> 1;
-                sums[((mrow * 2 + (j >> 3)) * nb + b) * 8 + (j & 7)] = (short)sum16;
+        // two blocks per warp in flight: both loads are issued before either is quantized (one L2 round trip)
+        for (int blk0 = warp; blk0 < total; blk0 += 2 * p.n_cwarps) {
+            const int blk1 = blk0 + p.n_cwarps;
+            float va[8], vb[8];
+            load8(p.x + (size_t)blk0 * 256 + lane * 8, va);
+            if (blk1 < total) load8(p.x + (size_t)blk1 * 256 + lane * 8, vb);
+#pragma unroll
+            for (int rep = 0; rep < 2; ++rep) {
+                const int blk = rep == 0 ? blk0 : blk1;
+                if (blk >= total) break;  // warp-uniform
+                uint32_t q_lo, q_hi;
+                float d;
+                int sum16;
+                q8k_quantize_warp(rep == 0 ? va : vb, lane, q_lo, q_hi, d, sum16);
+                q32[blk * (kQ8KUnitStride / 4) + lane * 2] = q_lo;
+                q32[blk * (kQ8KUnitStride / 4) + lane * 2 + 1] = q_hi;
+                if (lane == 0) dpl[blk] = d;
+                if (p.w_dtype == LLOOM_Q4_K) {
+                    const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+                    if ((lane & 3) == 0) sums[blk * 8 + (lane >> 2)] = (short)sum32;
+                } else if ((lane & 1) == 0) {
+                    const int mrow = blk / nb, b = blk - mrow * nb, j = lane >> 1;
+                    sums[((mrow * 2 + (j >> 3)) * nb + b) * 8 + (j & 7)] = (short)sum16;
+                }
             }
         }
         planes.sums = sums;
@@ -438,8 +460,9 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
 // away -- weights are read-only for the life of a QTensor.  Without the programmatic-serialization
 // launch attribute both instructions do nothing.  RW == 1 instances are built to fit two per SM, so
 // a successor's CTA can sit beside its predecessor's and keep the HBM stream going across launches.
-template <class Fmt, int M, int RW>
-__global__ void __launch_bounds__(288, RW == 1 ? 2 : 1) gemv_kernel(const GemvParams p) {
+// CW = most consumer warps the instance may be launched with (8, or 12 for the side-by-side m <= 2 shapes).
+template <class Fmt, int M, int RW, int CW = 8>
+__global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(const GemvParams p) {
     constexpr int MC = M > 4 ? (M + 1) / 2 : M;  // activation rows per pass
     constexpr int NPASS = (M + MC - 1) / MC;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -456,6 +479,10 @@ __global__ void __launch_bounds__(288, RW == 1 ? 2 : 1) gemv_kernel(const GemvPa
     const int r_begin = (int)(((int64_t)blockIdx.x * p.n) / gridDim.x);
     const int r_end = (int)(((int64_t)(blockIdx.x + 1) * p.n) / gridDim.x);
 
+#ifdef LLOOM_TRACE
+    if (threadIdx.x == 0) s_trace_slot = blockIdx.x < 160 ? g_trace_cnt[blockIdx.x]++ : 0;
+    __syncthreads();
+#endif
     if (threadIdx.x == 0) LLOOM_TRACE_MARK(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -507,6 +534,7 @@ __global__ void __launch_bounds__(288, RW == 1 ? 2 : 1) gemv_kernel(const GemvPa
     {
         const int nthreads = p.n_cwarps * 32;
         asm volatile("griddepcontrol.wait;" ::: "memory");  // predecessor's writes (x, act blocks) are visible
+        if (threadIdx.x == 0) LLOOM_TRACE_MARK(14);
         if (p.x) quantize_acts_to_planes(p, act_smem, warp, lane, planes);
         else stage_acts(p, act_smem, threadIdx.x, nthreads, planes);
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");

@@ -65,14 +65,17 @@ static int64_t weight_row_bytes(int dtype, int64_t k) {
 
 // ---- GEMV launch planning ----
 
-template <class Item, int M, int RW>
+template <class Item, int M, int RW, int CW = 8>
 static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_kernel<Item, M, RW>;
+    auto kern = gemv_kernel<Item, M, RW, CW>;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_smem[dev] < smem) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        // ask for the largest shared-memory carve-out, so that two half-size CTAs really fit side by side
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         configured_smem[dev] = smem;
     }
@@ -91,6 +94,11 @@ static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, boo
 
 template <class Fmt, int RW>
 static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    if (RW == 1 && p.n_cwarps > 8) {  // twelve-consumer-warp instances exist for m <= 2 only
+        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 12>(p, grid, smem, overlap, stream);
+        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 12>(p, grid, smem, overlap, stream);
+        return cudaErrorInvalidValue;
+    }
     switch (p.m) {
     case 1: return launch_gemv_inst<Fmt, 1, RW>(p, grid, smem, overlap, stream);
     case 2: return launch_gemv_inst<Fmt, 2, RW>(p, grid, smem, overlap, stream);
@@ -119,7 +127,10 @@ static bool gemv_shape_override(int &cw, int &rw) {
     static int cached = -1, ccw = 0, crw = 0;
     if (cached < 0) {
         const char *e = getenv("LLOOM_GEMV_SHAPE");
-        cached = (e && sscanf(e, "%d,%d", &ccw, &crw) == 2 && ccw >= 1 && ccw <= 8 && (crw == 1 || crw == 2)) ? 1 : 0;
+        cached = (e && sscanf(e, "%d,%d", &ccw, &crw) == 2 && ccw >= 1 && ccw <= 12 && (crw == 1 || crw == 2) &&
+                  (ccw <= 8 || crw == 1))
+                     ? 1
+                     : 0;
     }
     cw = ccw;
     rw = crw;
@@ -161,11 +172,13 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     // first that leaves room for at least two stages wins.  With launch overlap on, m <= 2 tries shapes
     // that fit two CTAs per SM first, so that consecutive launches can sit side by side.
     struct Shape { int cw, rw; bool half; };
-    Shape shapes[10];
+    Shape shapes[12];
     int ns = 0, ocw = 0, orw = 0;
     const bool overlap = g_launch_overlap.load(std::memory_order_relaxed) != 0;
     if (gemv_shape_override(ocw, orw)) shapes[ns++] = {ocw, orw, overlap && orw == 1};
     if (overlap && m <= 2) {  // HBM-bound batch sizes only: wider batches need the registers and the row tiling
+        // twelve consumer warps pay off for Q8_0 (cheap units, more of them per row); the k-quants are best at eight
+        if (w_dtype == LLOOM_Q8_0) shapes[ns++] = {12, 1, true};
         const int half_cw[4] = {8, 4, 2, 1};
         for (int c : half_cw) shapes[ns++] = {c, 1, true};
     }
@@ -391,15 +404,11 @@ int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float
 }
 
 #ifdef LLOOM_TRACE
-int lloom_b200_read_trace(unsigned long long *out) {  // development build only
+int lloom_b200_read_trace(unsigned long long *out, unsigned int *cnt) {  // development build only
+    cudaMemcpyFromSymbol(cnt, g_trace_cnt, sizeof(g_trace_cnt));
     return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
 }
-int lloom_b200_read_gemm_trace(unsigned long long *out) {  // development build only
-    return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(g_gemm_trace));
-}
-int lloom_b200_read_mma_micro(unsigned long long *out) {  // development build only
-    return (int)cudaMemcpyFromSymbol(out, g_mma_micro, sizeof(g_mma_micro));
-}
+
 #endif
 
 int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,
