@@ -15,13 +15,17 @@
 // accumulator pairs (2 x (128 + 128) = 512 columns), so the drain of superblock b overlaps the MMAs
 // of superblock b+1.
 //
-// CTA = one 128 (weight rows) x 128 (activation rows) output tile.  Warp roles:
-//   warps 0-7   epilogue: tcgen05.ld -> f32x2 FMAs; warp w reads TMEM lanes 32*(w%4).., columns 64*(w/4)..
-//   warps 8-11  weight producers: one thread per weight row, Q4_K block -> f16 (sc*q) written straight
-//               into the 128B-swizzled K-major UMMA layout (4 k-stages of 64 per superblock) + min tile
-//   warp 12     bulk-copy (TMA engine) producer of the activation tiles, which gemm_prep_kernel laid out
-//               in global memory as ready-made shared-memory images
-//   warp 13     MMA issuer (one elected thread): 4 x tcgen05.mma.kind::f16 (K = 16) per k-stage
+// Three launches per call:
+//   gemm_prep_kernel     canonical Q8_K activation blocks -> f16 operand images (B, B_min) + scale planes
+//   gemm_expand_kernel   Q4_K weight blocks -> f16 operand images (A = sc*q, A_min = m_j); a bandwidth pass
+//                        (33 MB in, 125 MB out for [14336, 4096]) that spares every output tile from
+//                        re-unpacking its 128 weight rows on CUDA cores beside the MMAs
+//   gemm_q4k_kernel      one CTA per 128 x 128 output tile; all operands arrive as ready-made shared-memory
+//                        images (128-byte-swizzled K-major UMMA layout) by bulk copies.  Warp roles:
+//                          warps 0-7  epilogue: tcgen05.ld -> f32x2 FMAs; warp w reads TMEM lanes 32*(w%4)..,
+//                                     columns 64*(w/4)..
+//                          warp 8     bulk-copy (TMA engine) producer
+//                          warp 9     MMA issuer (one elected lane): 8 x tcgen05.mma.kind::f16 (K = 16) per stage
 // All mbarrier waits are bounded and abortable; on a time-out the status word is set, every role
 // leaves its loop, and tensor memory is still released.
 #pragma once
@@ -39,7 +43,8 @@ constexpr int kGemmStageBytes = 2 * kGemmAtomBytes;  // a pipeline stage covers 
 constexpr int kGemmMinBytes = 128 * 16 * 2;    // min-term operand tile (K = 16), f16
 constexpr int kGemmDaBytes = 128 * 4;
 constexpr int kGemmStages = 3;
-constexpr int kGemmThreads = 512;
+constexpr int kGemmThreads = 320;  // 8 epilogue warps + bulk-copy warp + MMA warp
+constexpr int kGemmEpiWarps = 8;
 
 // ---- shared memory map (offsets from a 1024-byte aligned base) ----
 constexpr int kOffA = 0;
@@ -56,21 +61,23 @@ __host__ __device__ inline int64_t gemm_m_tiles(int64_t m) { return (m + kGemmBM
 
 // Workspace planes the GEMM reads (after the canonical activation blocks): B images, min-B images, scales.
 struct GemmScratch {
-    int64_t bimg, minb, dat, total;
+    int64_t bimg, minb, dat, aimg, mina, total;
 };
-__host__ __device__ inline GemmScratch gemm_scratch_layout(int64_t m, int64_t k) {
+__host__ __device__ inline GemmScratch gemm_scratch_layout(int64_t m, int64_t n, int64_t k) {
     GemmScratch s;
-    const int64_t mt = gemm_m_tiles(m), nb = k / 256;
+    const int64_t mt = gemm_m_tiles(m), nt = (n + kGemmBN - 1) / kGemmBN, nb = k / 256;
     s.bimg = 0;
     s.minb = s.bimg + mt * (k / 64) * kGemmAtomBytes;
     s.dat = s.minb + mt * nb * kGemmMinBytes;
-    s.total = (s.dat + mt * nb * kGemmDaBytes + 255) / 256 * 256;
+    s.aimg = (s.dat + mt * nb * kGemmDaBytes + 1023) / 1024 * 1024;
+    s.mina = s.aimg + nt * (k / 64) * kGemmAtomBytes;
+    s.total = (s.mina + nt * nb * kGemmMinBytes + 255) / 256 * 256;
     return s;
 }
 
-inline int64_t gemm_scratch_bytes(int w_dtype, int64_t m, int64_t /*n*/, int64_t k) {
+inline int64_t gemm_scratch_bytes(int w_dtype, int64_t m, int64_t n, int64_t k) {
     if (w_dtype != LLOOM_Q4_K || m <= 8) return 0;
-    return gemm_scratch_layout(m, k).total;
+    return gemm_scratch_layout(m, n, k).total;
 }
 
 // Byte offset of element (row r, k-element e in [0,64)) inside a 128-row k-stage image:
@@ -86,16 +93,17 @@ __host__ __device__ inline int min_tile_offset(int r, int e) {
 
 // Canonical Q8_K activation blocks -> the GEMM's operand images.  One CTA per (m-tile, superblock):
 // thread (t, c) converts 8 consecutive codes of token t to f16 and stores one 16-byte chunk.
-__global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restrict__ act, int m, int k,
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restrict__ act, int m, int n, int k,
                                                         uint8_t *__restrict__ scratch) {
     const int nb = k / 256;
-    const int mt = blockIdx.x / nb, b = blockIdx.x % nb;
-    const GemmScratch lay = gemm_scratch_layout(m, k);
+    const int quarter = blockIdx.x & 3;  // 32 tokens of the tile per CTA
+    const int mt = (blockIdx.x >> 2) / nb, b = (blockIdx.x >> 2) % nb;
+    const GemmScratch lay = gemm_scratch_layout(m, n, k);
     uint8_t *bimg = scratch + lay.bimg + ((int64_t)mt * (k / 64) + (int64_t)b * 4) * kGemmAtomBytes;
     uint8_t *minb = scratch + lay.minb + ((int64_t)mt * nb + b) * kGemmMinBytes;
     float *dat = reinterpret_cast<float *>(scratch + lay.dat) + ((int64_t)mt * nb + b) * 128;
-    for (int i = threadIdx.x; i < 128 * 32; i += blockDim.x) {
-        const int t = i >> 5, c = i & 31;  // token in tile, 8-element chunk of the superblock
+    for (int i = threadIdx.x; i < 32 * 32; i += blockDim.x) {
+        const int t = quarter * 32 + (i >> 5), c = i & 31;  // token in tile, 8-element chunk of the superblock
         const int row = mt * kGemmBM + t;
         uint4 out = make_uint4(0, 0, 0, 0);
         if (row < m) {
@@ -111,8 +119,8 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
         const int ks = c >> 3, e = (c & 7) * 8;
         *reinterpret_cast<uint4 *>(bimg + (int64_t)ks * kGemmAtomBytes + sw128_offset(t, e)) = out;
     }
-    for (int i = threadIdx.x; i < 128 * 2; i += blockDim.x) {
-        const int t = i >> 1, c = i & 1;
+    for (int i = threadIdx.x; i < 32 * 2; i += blockDim.x) {
+        const int t = quarter * 32 + (i >> 1), c = i & 1;
         const int row = mt * kGemmBM + t;
         uint4 out = make_uint4(0, 0, 0, 0);
         if (row < m) {
@@ -128,9 +136,92 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
         }
         *reinterpret_cast<uint4 *>(minb + min_tile_offset(t, c * 8)) = out;
     }
-    for (int t = threadIdx.x; t < 128; t += blockDim.x) {
+    for (int t = quarter * 32 + threadIdx.x; t < quarter * 32 + 32; t += blockDim.x) {
         const int row = mt * kGemmBM + t;
         dat[t] = row < m ? *reinterpret_cast<const float *>(act + ((int64_t)row * nb + b) * Q8K_BYTES) : 0.0f;
+    }
+}
+
+// Q4_K weight blocks -> the GEMM's A images.  One CTA per (n-tile, superblock), one thread per weight row:
+// the 144-byte block becomes four 128-byte rows of f16 (sc_j * q, exact) in the four swizzle atoms of the
+// superblock, plus the 32-byte min row (m_j duplicated against the two 16-element bsums of sub-block j).
+__global__ void __launch_bounds__(128) gemm_expand_kernel(const uint8_t *__restrict__ w, int m, int n, int k,
+                                                          uint8_t *__restrict__ scratch) {
+    // [4 atoms x 16 KB][min tile 4 KB]: assembled in shared memory, written out by two bulk stores
+    extern __shared__ __align__(1024) uint8_t ex_smem[];
+    const int nb = k / 256;
+    const int nt = blockIdx.x / nb, b = blockIdx.x % nb;
+    const GemmScratch lay = gemm_scratch_layout(m, n, k);
+    const int r = threadIdx.x, row = nt * kGemmBN + r;
+    uint4 blk[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) blk[i] = make_uint4(0, 0, 0, 0);
+    if (row < n) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(w + ((int64_t)row * nb + b) * Q4K_BYTES);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) blk[i] = __ldg(src + i);
+    }
+    const uint4 hq = blk[0];
+    // 6-bit scales / mins (utils.rs:50-60), four per word
+    const uint32_t scw[2] = {hq.y & 0x3f3f3f3fu, (hq.w & 0x0f0f0f0fu) | (((hq.y >> 6) & 0x03030303u) << 4)};
+    const uint32_t mnw[2] = {hq.z & 0x3f3f3f3fu, ((hq.w >> 4) & 0x0f0f0f0fu) | (((hq.z >> 6) & 0x03030303u) << 4)};
+    uint8_t *img = ex_smem + (r >> 3) * 1024 + (r & 7) * 128;
+    const int sw = r & 7;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint4 q0 = blk[1 + 2 * g], q1 = blk[2 + 2 * g];
+        const uint32_t sc_lo = (scw[g >> 1] >> (16 * (g & 1))) & 0xff, sc_hi = (scw[g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
+        // f16 value of sc*q without an int->float convert: (1024 + q) * sc - 1024 * sc, one exact FMA
+        const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo));
+        const __half2 s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
+        const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), c_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint8_t *dst = img + g * kGemmAtomBytes;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the atom
+            // chunks 0-3: low nibbles of bytes 8c..8c+7; chunks 4-7: high nibbles of bytes 8(c-4)..
+            const uint32_t w0 = qw[2 * (c & 3)], w1 = qw[2 * (c & 3) + 1];
+            const uint32_t n0w = (c < 4) ? (w0 & 0x0f0f0f0fu) : ((w0 >> 4) & 0x0f0f0f0fu);
+            const uint32_t n1w = (c < 4) ? (w1 & 0x0f0f0f0fu) : ((w1 >> 4) & 0x0f0f0f0fu);
+            const __half2 sc2 = (c < 4) ? s_lo : s_hi, cc2 = (c < 4) ? c_lo : c_hi;
+            uint32_t h[4];
+            h[0] = __byte_perm(n0w, 0x64646464u, 0x4140);
+            h[1] = __byte_perm(n0w, 0x64646464u, 0x4342);
+            h[2] = __byte_perm(n1w, 0x64646464u, 0x4140);
+            h[3] = __byte_perm(n1w, 0x64646464u, 0x4342);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 v = __hfma2(*reinterpret_cast<const __half2 *>(&h[j]), sc2, cc2);
+                h[j] = *reinterpret_cast<const uint32_t *>(&v);
+            }
+            *reinterpret_cast<uint4 *>(dst + ((c ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+    }
+    uint8_t *md = ex_smem + 4 * kGemmAtomBytes;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint32_t h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned short mv = (unsigned short)((mnw[c] >> (8 * j)) & 0xff);
+            const __half2 v = __half2half2(__ushort2half_rn(mv));
+            h[j] = *reinterpret_cast<const uint32_t *>(&v);
+        }
+        *reinterpret_cast<uint4 *>(md + min_tile_offset(r, c * 8)) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+    fence_proxy_async();  // generic-proxy stores -> visible to the bulk-copy engine
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint8_t *ga = scratch + lay.aimg + ((int64_t)nt * (k / 64) + (int64_t)b * 4) * kGemmAtomBytes;
+        uint8_t *gm = scratch + lay.mina + ((int64_t)nt * nb + b) * kGemmMinBytes;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(ga), "r"(smem_u32(ex_smem)),
+                     "r"(4 * kGemmAtomBytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gm), "r"(smem_u32(md)),
+                     "r"(kGemmMinBytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // shared memory must outlive the copies
     }
 }
 
@@ -212,14 +303,15 @@ struct GemmParams {
     int64_t row_bytes;
     int m, n, k;
     int n_tiles;  // tiles along the weight rows
+    int m_tiles;  // tiles along the activation rows
 };
 
-// Pipeline barriers.  A stage (128 of K of both operands) has one "full" barrier, completed by the four
-// weight-producer warps plus the bulk copy's transaction bytes, and one "empty" barrier, completed by a single
-// tcgen05.commit -- one commit and one wait per stage keep the issuing thread's serial overhead below the
-// tensor time of the stage.  Per superblock parity (two of each): min_full (min tiles + activation scales
-// landed), acc_full (commit after the superblock's last MMA: accumulators ready, min tiles free), acc_empty
-// (the eight epilogue warps have drained the accumulators and are done with the scales).
+// Pipeline barriers.  A stage (128 of K of both operands, 64 KB) has one "full" barrier, completed by the
+// bulk copies' transaction bytes, and one "empty" barrier, completed by a single tcgen05.commit -- one
+// commit and one wait per stage keep the issuing thread's serial overhead below the tensor time of the
+// stage.  Per superblock parity (two of each): min_full (min tiles + activation scales landed), acc_full
+// (commit after the superblock's last MMA: accumulators ready, min tiles free), acc_empty (the eight
+// epilogue warps have read the accumulators out of tensor memory and hold the scales in registers).
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -230,25 +322,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + kOffMisc + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nt = blockIdx.x % p.n_tiles, mt = blockIdx.x / p.n_tiles;
+    // m-tiles of one n-tile are neighbours in launch order, so the n-tile's A images are shared through L2
+    const int mt = blockIdx.x % p.m_tiles, nt = blockIdx.x / p.m_tiles;
     const int n0 = nt * kGemmBN, m0 = mt * kGemmBM;
     const int nb = p.k / 256;
-    const GemmScratch lay = gemm_scratch_layout(p.m, p.k);
+    const GemmScratch lay = gemm_scratch_layout(p.m, p.n, p.k);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
-            mbar_init(&full[s], 4 + 1);
+            mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&min_full[i], 4 + 1);
+            mbar_init(&min_full[i], 1);
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 8);
+            mbar_init(&acc_empty[i], kGemmEpiWarps);
         }
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 13) {  // tensor memory: all 512 columns, two (S, Mn) accumulator pairs
+    if (warp == kGemmEpiWarps + 1) {  // tensor memory: all 512 columns, two (S, Mn) accumulator pairs
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -258,8 +351,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 8) {
+    if (warp < kGemmEpiWarps) {
         // ------------------------------ epilogue ------------------------------
+        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 64*(w/4)..
         const int q = warp & 3, half = warp >> 2;
         const int r = q * 32 + lane;  // row of the tile == TMEM lane
         const int n = n0 + r;
@@ -277,34 +371,49 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * Q4K_BYTES));
             const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
             const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
-            ok = mbar_wait_abortable<96>(&min_full[buf], par, abort_flag) && mbar_wait_abortable<96>(&acc_full[buf], par, abort_flag);
+            ok = mbar_wait_abortable<64>(&min_full[buf], par, abort_flag);
             if (!ok) break;
-            tc_fence_after();
-            const float *da = reinterpret_cast<const float *>(smem + kOffDa + buf * kGemmDaBytes) + half * 64;
-            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * 64);
-#pragma unroll
-            for (int chunk = 0; chunk < 2; ++chunk) {
-                uint32_t v[32];
-                tmem_ld32(t_main + chunk * 32, v);  // S
-                tmem_ld_wait();
+            // the 64 activation scales of this warp's columns, as f32 pairs
+            uint64_t da2[32];
+            {
+                const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + kOffDa + buf * kGemmDaBytes + half * 256);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float2 d2 = *reinterpret_cast<const float2 *>(da + chunk * 32 + 2 * j);
-                    const uint64_t t = mul_f32x2(pack2f(d2.x, d2.y), dw2);
-                    out2[chunk * 16 + j] = fma_f32x2(t, (uint64_t)v[2 * j] | ((uint64_t)v[2 * j + 1] << 32), out2[chunk * 16 + j]);
-                }
-                tmem_ld32(t_main + 128 + chunk * 32, v);  // Mn
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float2 d2 = *reinterpret_cast<const float2 *>(da + chunk * 32 + 2 * j);
-                    const uint64_t t = mul_f32x2(pack2f(d2.x, d2.y), ndmin2);
-                    out2[chunk * 16 + j] = fma_f32x2(t, (uint64_t)v[2 * j] | ((uint64_t)v[2 * j + 1] << 32), out2[chunk * 16 + j]);
+                    const ulonglong2 t = dap[j];
+                    da2[2 * j] = t.x;
+                    da2[2 * j + 1] = t.y;
                 }
             }
+            ok = mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * 64);
+            uint32_t va[32], vb[32];
+            // loads run one chunk ahead of the FMAs: S0 | Mn0 | S1 | Mn1
+            tmem_ld32(t_main, va);
+            tmem_ld_wait();
+            tmem_ld32(t_main + 128, vb);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                out2[j] = fma_f32x2(mul_f32x2(da2[j], dw2), (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[j]);
+            tmem_ld_wait();
+            tmem_ld32(t_main + 32, va);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                out2[j] = fma_f32x2(mul_f32x2(da2[j], ndmin2), (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[j]);
+            tmem_ld_wait();
+            tmem_ld32(t_main + 128 + 32, vb);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                out2[16 + j] = fma_f32x2(mul_f32x2(da2[16 + j], dw2), (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[16 + j]);
+            tmem_ld_wait();
+            // everything this warp needs from tensor memory and from the scale tile is in registers now
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                out2[16 + j] = fma_f32x2(mul_f32x2(da2[16 + j], ndmin2), (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[16 + j]);
         }
         if (ok && row_ok) {
 #pragma unroll
@@ -314,101 +423,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
                 if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
             }
         }
-    } else if (warp < 12) {
-        // ------------------------------ weight producers ------------------------------
-        const int r = threadIdx.x - 256;  // row of the tile
-        const int n = n0 + r;
-        const bool row_ok = n < p.n;
-        const uint8_t *wrow = p.w + (int64_t)(row_ok ? n : 0) * p.row_bytes;
-        uint8_t *a_base = smem + kOffA + (r >> 3) * 1024 + (r & 7) * 128;
-        const int sw = r & 7;
-        bool ok = true;
-        // the row's 144-byte block, fetched one superblock ahead so that the L2/HBM latency is off the stage loop
-        uint4 nxt[9];
-#pragma unroll
-        for (int i = 0; i < 9; ++i) nxt[i] = make_uint4(0, 0, 0, 0);
-        if (row_ok) {
-            const uint4 *blk0 = reinterpret_cast<const uint4 *>(wrow);
-#pragma unroll
-            for (int i = 0; i < 9; ++i) nxt[i] = __ldg(blk0 + i);
-        }
-        for (int b = 0; b < nb && ok; ++b) {
-            uint4 cur[9];
-#pragma unroll
-            for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
-            if (row_ok && b + 1 < nb) {
-                const uint4 *blk1 = reinterpret_cast<const uint4 *>(wrow + (int64_t)(b + 1) * Q4K_BYTES);
-#pragma unroll
-                for (int i = 0; i < 9; ++i) nxt[i] = __ldg(blk1 + i);
-            }
-            const uint4 hq = cur[0];
-            // 6-bit scales / mins (utils.rs:50-60), four per word
-            const uint32_t scw[2] = {hq.y & 0x3f3f3f3fu, (hq.w & 0x0f0f0f0fu) | (((hq.y >> 6) & 0x03030303u) << 4)};
-            const uint32_t mnw[2] = {hq.z & 0x3f3f3f3fu, ((hq.w >> 4) & 0x0f0f0f0fu) | (((hq.z >> 6) & 0x03030303u) << 4)};
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {  // 64-element group g -> atom (g & 1) of stage (b*2 + g/2)
-                const int it = b * 2 + (g >> 1), s = it % kGemmStages;
-                const uint4 q0 = cur[1 + 2 * g], q1 = cur[2 + 2 * g];
-                if ((g & 1) == 0 && it >= kGemmStages)
-                    ok = mbar_wait_abortable<96>(&empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
-                if (!ok) break;
-                const uint32_t sc_lo = (scw[g >> 1] >> (16 * (g & 1))) & 0xff, sc_hi = (scw[g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
-                // f16 value of sc*q without an int->float convert: (1024 + q) * sc - 1024 * sc, one exact FMA
-                const __half2 s_lo = __half2half2(__ushort2half_rn((unsigned short)sc_lo));
-                const __half2 s_hi = __half2half2(__ushort2half_rn((unsigned short)sc_hi));
-                const __half2 c_lo = __hmul2(s_lo, __float2half2_rn(-1024.0f)), c_hi = __hmul2(s_hi, __float2half2_rn(-1024.0f));
-                const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                uint8_t *dst = a_base + s * kGemmStageBytes + (g & 1) * kGemmAtomBytes;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the atom
-                    // chunks 0-3: low nibbles of bytes 8c..8c+7; chunks 4-7: high nibbles of bytes 8(c-4)..
-                    const uint32_t w0 = qw[2 * (c & 3)], w1 = qw[2 * (c & 3) + 1];
-                    const uint32_t n0w = (c < 4) ? (w0 & 0x0f0f0f0fu) : ((w0 >> 4) & 0x0f0f0f0fu);
-                    const uint32_t n1w = (c < 4) ? (w1 & 0x0f0f0f0fu) : ((w1 >> 4) & 0x0f0f0f0fu);
-                    const __half2 sc2 = (c < 4) ? s_lo : s_hi, cc2 = (c < 4) ? c_lo : c_hi;
-                    uint32_t h[4];
-                    h[0] = __byte_perm(n0w, 0x64646464u, 0x4140);
-                    h[1] = __byte_perm(n0w, 0x64646464u, 0x4342);
-                    h[2] = __byte_perm(n1w, 0x64646464u, 0x4140);
-                    h[3] = __byte_perm(n1w, 0x64646464u, 0x4342);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const __half2 v = __hfma2(*reinterpret_cast<const __half2 *>(&h[j]), sc2, cc2);
-                        h[j] = *reinterpret_cast<const uint32_t *>(&v);
-                    }
-                    *reinterpret_cast<uint4 *>(dst + ((c ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                }
-                if (g & 1) {
-                    fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full[s]);
-                }
-            }
-            if (!ok) break;
-            // min tile: m_j duplicated against the two 16-element bsums of sub-block j; free once the MMAs of
-            // superblock b-2 have completed (acc_full of that superblock)
-            const int buf = b & 1;
-            if (b >= 2) ok = mbar_wait_abortable<96>(&acc_full[buf], ((b >> 1) - 1) & 1, abort_flag);
-            if (!ok) break;
-            uint8_t *md = smem + kOffMinA + buf * kGemmMinBytes;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t h[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const unsigned short mv = (unsigned short)((mnw[c] >> (8 * j)) & 0xff);
-                    const __half2 v = __half2half2(__ushort2half_rn(mv));
-                    h[j] = *reinterpret_cast<const uint32_t *>(&v);
-                }
-                *reinterpret_cast<uint4 *>(md + min_tile_offset(r, c * 8)) = make_uint4(h[0], h[1], h[2], h[3]);
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&min_full[buf]);
-        }
-    } else if (warp == 12) {
-        // ------------------------------ activation tiles: bulk copies ------------------------------
+    } else if (warp == kGemmEpiWarps) {
+        // ------------------------------ operand tiles: bulk copies ------------------------------
         // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
+        const uint8_t *aimg = p.scratch + lay.aimg + (int64_t)nt * (p.k / 64) * kGemmAtomBytes;
+        const uint8_t *mina = p.scratch + lay.mina + (int64_t)nt * nb * kGemmMinBytes;
         const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmAtomBytes;
         const uint8_t *minb = p.scratch + lay.minb + (int64_t)mt * nb * kGemmMinBytes;
         const uint8_t *dat = p.scratch + lay.dat + (int64_t)mt * nb * kGemmDaBytes;
@@ -416,29 +435,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
         for (int b = 0; b < nb && ok; ++b) {
             for (int h = 0; h < 2 && ok; ++h) {
                 const int it = b * 2 + h, s = it % kGemmStages;
-                if (it >= kGemmStages) ok = mbar_wait_abortable<96>(&empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
+                if (it >= kGemmStages) ok = mbar_wait_abortable<32>(&empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
                 if (!ok) break;
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(&full[s], kGemmStageBytes);
+                    mbar_arrive_expect_tx(&full[s], 2 * kGemmStageBytes);
+                    bulk_g2s(smem + kOffA + s * kGemmStageBytes, aimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &full[s]);
                     bulk_g2s(smem + kOffB + s * kGemmStageBytes, bimg + (int64_t)it * kGemmStageBytes, kGemmStageBytes, &full[s]);
                 }
                 __syncwarp();
             }
             if (!ok) break;
             const int buf = b & 1;
-            if (b >= 2) {  // min-B tile is free after the MMAs of b-2, the scales after the epilogue of b-2
+            if (b >= 2) {  // min tiles are free after the MMAs of b-2, the scales after the epilogue of b-2
                 const uint32_t pp = ((b >> 1) - 1) & 1;
-                ok = mbar_wait_abortable<96>(&acc_full[buf], pp, abort_flag) && mbar_wait_abortable<96>(&acc_empty[buf], pp, abort_flag);
+                ok = mbar_wait_abortable<32>(&acc_full[buf], pp, abort_flag) && mbar_wait_abortable<32>(&acc_empty[buf], pp, abort_flag);
             }
             if (!ok) break;
             if (lane == 0) {
-                mbar_arrive_expect_tx(&min_full[buf], kGemmMinBytes + kGemmDaBytes);
+                mbar_arrive_expect_tx(&min_full[buf], 2 * kGemmMinBytes + kGemmDaBytes);
+                bulk_g2s(smem + kOffMinA + buf * kGemmMinBytes, mina + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &min_full[buf]);
                 bulk_g2s(smem + kOffMinB + buf * kGemmMinBytes, minb + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &min_full[buf]);
                 bulk_g2s(smem + kOffDa + buf * kGemmDaBytes, dat + (int64_t)b * kGemmDaBytes, kGemmDaBytes, &min_full[buf]);
             }
             __syncwarp();
         }
-    } else if (warp == 13) {
+    } else if (warp == kGemmEpiWarps + 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp walks the loop; lane 0 issues the MMAs and commits.
         // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
@@ -485,7 +506,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     // ------------------------------ teardown ------------------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == kGemmEpiWarps + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
@@ -505,8 +526,19 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
         configured = true;
     }
     const int64_t mt = gemm_m_tiles(m), nb = k / 256;
-    gemm_prep_kernel<<<(unsigned)(mt * nb), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, (uint8_t *)workspace);
+    const int64_t ntiles = (n + kGemmBN - 1) / kGemmBN;
+    gemm_prep_kernel<<<(unsigned)(mt * nb * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)n, (int)k, (uint8_t *)workspace);
     cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
+    constexpr int kExpandSmem = 4 * kGemmAtomBytes + kGemmMinBytes;
+    static bool expand_configured = false;
+    if (!expand_configured) {
+        e = cudaFuncSetAttribute(gemm_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpandSmem);
+        if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
+        expand_configured = true;
+    }
+    gemm_expand_kernel<<<(unsigned)(ntiles * nb), 128, kExpandSmem, stream>>>((const uint8_t *)w, (int)m, (int)n, (int)k, (uint8_t *)workspace);
+    e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
     GemmParams p;
     p.w = (const uint8_t *)w;
@@ -517,7 +549,8 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
     p.m = (int)m;
     p.n = (int)n;
     p.k = (int)k;
-    p.n_tiles = (int)((n + kGemmBN - 1) / kGemmBN);
+    p.n_tiles = (int)ntiles;
+    p.m_tiles = (int)mt;
     gemm_q4k_kernel<<<(unsigned)(p.n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
