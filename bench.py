@@ -282,10 +282,9 @@ def run_gpu(args):
         for m in SWEEP_M:
             graphs[m] = capture(lambda m=m: fwd_pass(m, outs[m]))
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank)  # runs across every device-timed leg below (headline, sweep, roofline, prefill)
     sampler.start()
     ms_total = time_graph(graphs[1], steps, warmup)
-    clocks = sampler.stop()
     ms_per_step = ms_total / steps
     value = world * POOL * WEIGHT_BYTES / (ms_per_step * 1e-3) / 1e9
 
@@ -307,6 +306,34 @@ def run_gpu(args):
                 "frac": round(achieved / peak, 4), "traffic": GEMV_DRAM_TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}",
                 "kernel": "gemv_kernel<ItemQ4K<1>,1,RW>", "algorithmic_bytes_per_launch": WEIGHT_BYTES,
                 "us_per_launch": round(ms_gemv * 1e3, 3)}
+
+    # prefill leg (the metric's second half): whole QMatMul::forward at M = 512 and 2048 on the C4 matrix
+    # (activation quantizer + operand preparation + tcgen05 GEMM), CUDA events, output and operands larger than L2
+    gemm = {}
+    bf16_peak = 1627.9
+    try:
+        bf16_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    for m in (512, 2048):
+        xg = torch.from_numpy(np.random.default_rng(7).standard_normal((m, K)).astype(np.float32)).to(dev)
+        yg = torch.empty(m, N, dtype=torch.float32, device=dev)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                pool[1].storage.fwd((N, K), xg, out=yg)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            reps = 10
+            e0.record(stream)
+            for i in range(reps):
+                pool[(2 * i + 1) % POOL].storage.fwd((N, K), xg, out=yg)
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        tf = 2.0 * m * N * K / (ms * 1e-3) / 1e12
+        gemm[f"M={m}"] = {"us": round(ms * 1e3, 1), "tflops": round(tf, 1), "frac_of_bf16_burst": round(tf / bf16_peak, 3)}
+        del xg, yg
+    clocks = sampler.stop()
 
     # e2e leg: public API, host buffers in, host buffers out, every step
     y_host = torch.empty(POOL, 1, N, dtype=torch.float32).pin_memory()
@@ -353,6 +380,7 @@ def run_gpu(args):
         "gpu_launches": steps * POOL,  # one fused quantize+GEMV launch per matrix
         "roofline": roofline,
         "sweep_GBps": sweep,
+        "prefill_gemm_q4k": gemm,
         "device_status": status,
     }
     if rank == 0:
