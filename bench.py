@@ -472,6 +472,132 @@ def run_lm_head(args):
         dist.destroy_process_group()
 
 
+def run_stack(args):
+    """`--workload stack`: the synthetic Llama-8B-shaped decode matmul stack (C5): 32 layers of q/o [4096,4096],
+    k/v [1024,4096], gate/up [14336,4096], down [4096,14336] in Q4_K plus a Q6_K lm_head [128256,4096]; a chain of
+    225 independent forwards on fixed inputs of the right K (no attention / norms), M = 1 and M = 8.  FFN and lm_head
+    rows are sharded over the ranks (all-gather of their outputs); q/k/v/o are replicated.  One matrix per shape is
+    quantized on the host and copied into distinct device buffers per layer: distinct memory is what the step
+    streams, the values repeat."""
+    import torch
+    import torch.distributed as dist
+
+    import lloom_b200 as lb
+    from lloom_b200 import _lib
+    from lloom_b200 import quantized as Q
+    from lloom_b200.sharded import ShardPlan, gather_rows
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    layers = args.layers
+    H, FF, KV, V = 4096, 14336, 1024, 128256
+    q4, q6 = lb.GgmlDType.Q4K, lb.GgmlDType.Q6K
+
+    def host_matrix(seed, n, k, dtype, lo, hi):
+        out = []
+        c0 = lo
+        while c0 < hi:
+            c1 = min(hi, (c0 // 4096 + 1) * 4096)
+            blk = np.random.default_rng([seed, c0 // 4096]).standard_normal((4096, k)).astype(np.float32) * np.float32(0.02)
+            out.append(Q.quantize_weights_host(blk[c0 % 4096: c0 % 4096 + (c1 - c0)], dtype))
+            c0 = c1
+        return np.concatenate(out)
+
+    def shard(n):
+        plan = ShardPlan(n, world)
+        lo, hi = plan.range_of(rank)
+        return plan, lo, hi
+
+    specs = [("q", H, H, False), ("k", KV, H, False), ("v", KV, H, False), ("o", H, H, False),
+             ("gate", FF, H, True), ("up", FF, H, True), ("down", H, FF, True)]
+    protos = {}
+    for i, (name, n, k, sharded) in enumerate(specs):
+        plan, lo, hi = shard(n) if sharded else (None, 0, n)
+        protos[name] = (host_matrix(1000 + i, n, k, q4, lo, hi), hi - lo, k, plan)
+    plan_v, lo, hi = shard(V)
+    lm_host = host_matrix(9000, V, H, q6, lo, hi)
+    weights = []  # (QTensor, plan or None)
+    bytes_local = 0
+    for _ in range(layers):
+        for name, _, _, _ in specs:
+            host, rows, k, plan = protos[name]
+            weights.append((lb.QTensor.from_data(host, q4, (rows, k), dev), plan, k))
+            bytes_local += host.size
+    weights.append((lb.QTensor.from_data(lm_host, q6, (hi - lo, H), dev), plan_v if world > 1 else None, H))
+    bytes_local += lm_host.size
+    _lib.lib().lloom_b200_set_launch_overlap(1)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    results = {}
+    for m in (1, 8):
+        xs = {k: torch.from_numpy(np.random.default_rng(9001).standard_normal((m, k)).astype(np.float32)).to(dev)
+              for k in (H, FF)}
+        outs = [torch.empty(m, w.shape[0], dtype=torch.float32, device=dev) for w, _, _ in weights]
+
+        def step():
+            for (w, plan, k), y in zip(weights, outs):
+                w.storage.fwd(w.shape, xs[k], out=y)
+                if plan is not None and world > 1:
+                    gather_rows(y, plan)
+
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            step()
+            stream.synchronize()
+            use_graph = world == 1
+            if use_graph:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    step()
+                run = g.replay
+            else:
+                run = step
+            for _ in range(warmup):
+                run()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                run()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        tot = torch.tensor([ms, float(bytes_local)], device=dev, dtype=torch.float64)
+        if world > 1:
+            t_ms = tot[:1].clone()
+            dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+            t_b = tot[1:].clone()
+            dist.all_reduce(t_b, op=dist.ReduceOp.SUM)
+            ms, total_bytes = float(t_ms.item()), float(t_b.item())
+        else:
+            total_bytes = float(bytes_local)
+        results[m] = (ms, total_bytes)
+    if rank == 0:
+        ms1, tb = results[1]
+        peak, kind = measured_peaks()
+        print(json.dumps({
+            "metric": "llama8b_decode_stack_weight_GBps", "value": round(tb / (ms1 * 1e-3) / 1e9, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": round(ms1, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "config": {"workload": f"C5 decode matmul stack, {layers} layers + lm_head, M=1; FFN/lm_head row-sharded",
+                       "launches_per_step": len(weights), "bytes_read_per_step_all_gpus": int(tb),
+                       "per_gpu_frac_of_hbm": round(tb / world / (ms1 * 1e-3) / 1e9 / peak, 3), "peak_kind": f"of {kind}",
+                       "M=8": {"ms_per_step": round(results[8][0], 4),
+                               "GBps": round(results[8][1] / (results[8][0] * 1e-3) / 1e9, 1)},
+                       "timing": "CUDA events; one CUDA graph per step" if world == 1 else "CUDA events; eager launches + NCCL all-gathers"},
+            "gpu_launches": steps * len(weights)}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one M=1 GEMV launch on the full [14336,4096] matrix,
 # from the ncu capture summarised in profiles/gemv_q4k_m1.md.
 GEMV_DRAM_TRAFFIC_BYTES = 33089280
@@ -484,13 +610,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--workload", default="c2", choices=["c2", "lm_head"],
-                    help="c2: the headline Q4_K decode GEMV; lm_head: the row-sharded Q6_K lm_head with all-gather")
+    ap.add_argument("--workload", default="c2", choices=["c2", "lm_head", "stack"],
+                    help="c2: the headline Q4_K decode GEMV; lm_head: the row-sharded Q6_K lm_head with all-gather; "
+                         "stack: the 32-layer Llama-8B-shaped decode matmul stack")
+    ap.add_argument("--layers", type=int, default=32, help="layers of the stack workload")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "lm_head":
         run_lm_head(args)
+    elif args.workload == "stack":
+        run_stack(args)
     else:
         run_gpu(args)
 

@@ -375,10 +375,12 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
     if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
     if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
-    // decode: one launch, the activation quantizer is the GEMV's prologue (the workspace stays unused)
-    if (m <= 8) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
+    // single-token decode: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
+    // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
+    if (m <= 2) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
     rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
     if (rc != LLOOM_OK) return rc;
+    if (m <= 8) return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream);
     const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
     return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
                            workspace_bytes - act, stream);
