@@ -34,12 +34,14 @@ constexpr int kQ8_0UnitStride = 64 + 16;
 
 __host__ __device__ inline int64_t round16(int64_t v) { return (v + 15) / 16 * 16; }
 
-__host__ __device__ inline int64_t act_qs_bytes(int w_dtype, int64_t m, int64_t k) {
-    return (w_dtype == LLOOM_Q8_0) ? m * (k / 64) * kQ8_0UnitStride : m * (k / 256) * kQ8KUnitStride;
+// row_pad: extra bytes after each activation row of the qs plane (the tensor-core kernel, whose lanes read
+// eight activation rows at once, pads by 16 so that those rows fall on different banks).
+__host__ __device__ inline int64_t act_qs_bytes(int w_dtype, int64_t m, int64_t k, int row_pad = 0) {
+    return ((w_dtype == LLOOM_Q8_0) ? m * (k / 64) * kQ8_0UnitStride : m * (k / 256) * kQ8KUnitStride) + m * row_pad;
 }
 
-__host__ __device__ inline int64_t act_plane_bytes(int w_dtype, int64_t m, int64_t k) {
-    const int64_t qs = act_qs_bytes(w_dtype, m, k);
+__host__ __device__ inline int64_t act_plane_bytes(int w_dtype, int64_t m, int64_t k, int row_pad = 0) {
+    const int64_t qs = act_qs_bytes(w_dtype, m, k, row_pad);
     const int64_t d = (w_dtype == LLOOM_Q8_0) ? m * (k / 32) * 4 : m * (k / 256) * 4;
     const int64_t sums = (w_dtype == LLOOM_Q8_0) ? 0 : (w_dtype == LLOOM_Q4_K ? m * (k / 32) * 2 : m * (k / 16) * 2);
     return round16(qs) + round16(d) + round16(sums);
@@ -302,6 +304,7 @@ struct GemvParams {
     int stages;
     int stage_bytes;   // multiple of 128
     int act_bytes;     // multiple of 16
+    int act_row_pad;   // extra bytes after each activation row of the qs plane (0, or 16 for the tensor-core kernel)
 };
 
 constexpr int kMaxStages = 8;
@@ -324,7 +327,7 @@ __device__ __forceinline__ unsigned long long trace_now() {
 // Canonical activation blocks (global) -> planes (shared); all `nthreads` consumer threads take part.
 __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_smem, int tid, int nthreads,
                                            ActPlanes &planes) {
-    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k));
+    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k, p.act_row_pad));
     float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
     planes.qs = reinterpret_cast<const int8_t *>(act_smem);
     planes.d = dpl;
@@ -374,7 +377,7 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
                 if (i < total) {
                     const int blk = i / 73, w = i - blk * 73;
                     if (w == 0) dpl[blk] = __uint_as_float(v[j]);
-                    else if (w <= 64) q32[blk * (kQ8KUnitStride / 4) + w - 1] = v[j];
+                    else if (w <= 64) q32[blk * (kQ8KUnitStride / 4) + (blk / nb) * (p.act_row_pad / 4) + w - 1] = v[j];
                     else if (pair) sums[blk * 8 + w - 65] = (short)((int)(short)(v[j] & 0xffffu) + (int)(short)(v[j] >> 16));
                     else {
                         const int mrow = blk / nb, b = blk - mrow * nb, jj = w - 65;  // word jj: bsums 2jj, 2jj+1
@@ -391,7 +394,7 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
 // arithmetic as the stand-alone quantizer kernels (bit-identical codes, scales and sums).
 __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uint8_t *act_smem, int warp, int lane,
                                                         ActPlanes &planes) {
-    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k));
+    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k, p.act_row_pad));
     float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
     uint32_t *q32 = reinterpret_cast<uint32_t *>(act_smem);
     planes.qs = reinterpret_cast<const int8_t *>(act_smem);
@@ -437,8 +440,9 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
                 float d;
                 int sum16;
                 q8k_quantize_warp(rep == 0 ? va : vb, lane, q_lo, q_hi, d, sum16);
-                q32[blk * (kQ8KUnitStride / 4) + lane * 2] = q_lo;
-                q32[blk * (kQ8KUnitStride / 4) + lane * 2 + 1] = q_hi;
+                uint32_t *qdst = q32 + blk * (kQ8KUnitStride / 4) + (blk / nb) * (p.act_row_pad / 4) + lane * 2;
+                qdst[0] = q_lo;
+                qdst[1] = q_hi;
                 if (lane == 0) dpl[blk] = d;
                 if (p.w_dtype == LLOOM_Q4_K) {
                     const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
@@ -450,6 +454,60 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
             }
         }
         planes.sums = sums;
+    }
+}
+
+// The producer warp's loop: streams tiles of `tile_rows` consecutive rows of [r_begin, r_end) into the stage ring.
+__device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *full, uint64_t *empty, uint8_t *stage0,
+                                              int tile_rows, int r_begin, int r_end, int lane) {
+    int it = 0;
+    for (int row0 = r_begin; row0 < r_end; row0 += tile_rows, ++it) {
+        const int s = it % p.stages;
+        if (it >= p.stages) {
+            if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
+        }
+        const int rows = min(tile_rows, r_end - row0);
+        const int64_t start = (int64_t)row0 * p.row_bytes;
+        const int64_t end = start + (int64_t)rows * p.row_bytes;
+        const int64_t a_start = start & ~(int64_t)15;
+        int64_t a_end = (end + 15) & ~(int64_t)15;
+        const int64_t bulk_limit = p.w_bytes & ~(int64_t)15;  // bytes the bulk engine may touch
+        if (a_end > bulk_limit) a_end = bulk_limit;
+        uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
+        // ragged end of the weight stream (< 16 bytes): plain loads
+        if (end > a_end) {
+            const int64_t from = a_end > a_start ? a_end : a_start;
+            for (int64_t i = from + lane; i < end; i += 32) dst[i - a_start] = __ldg(p.w + i);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            if (a_end > a_start) {
+                const uint32_t bytes = (uint32_t)(a_end - a_start);
+                mbar_arrive_expect_tx(&full[s], bytes);
+                bulk_g2s(dst, p.w + a_start, bytes, &full[s]);
+            } else {
+                mbar_arrive(&full[s]);
+            }
+        }
+    }
+}
+
+// Row-wise variant for row sizes that are multiples of 16 bytes: one bulk copy per row, rows `row_pitch` bytes
+// apart in the stage (a pitch of row_bytes + 16 puts consecutive rows four banks apart).
+__device__ __forceinline__ void gemv_producer_rows(const GemvParams &p, uint64_t *full, uint64_t *empty, uint8_t *stage0,
+                                                   int tile_rows, int row_pitch, int r_begin, int r_end, int lane) {
+    int it = 0;
+    for (int row0 = r_begin; row0 < r_end; row0 += tile_rows, ++it) {
+        const int s = it % p.stages;
+        if (it >= p.stages) {
+            if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
+        }
+        const int rows = min(tile_rows, r_end - row0);
+        uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
+        if (lane == 0) mbar_arrive_expect_tx(&full[s], (uint32_t)(rows * p.row_bytes));
+        __syncwarp();
+        for (int r = lane; r < rows; r += 32)
+            bulk_g2s(dst + (size_t)r * row_pitch, p.w + (int64_t)(row0 + r) * p.row_bytes, (uint32_t)p.row_bytes, &full[s]);
     }
 }
 
@@ -496,36 +554,7 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
 
     if (warp == p.n_cwarps) {
         // ---------------- producer warp ----------------
-        int it = 0;
-        for (int row0 = r_begin; row0 < r_end; row0 += tile_rows, ++it) {
-            const int s = it % p.stages;
-            if (it >= p.stages) {
-                if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
-            }
-            const int rows = min(tile_rows, r_end - row0);
-            const int64_t start = (int64_t)row0 * p.row_bytes;
-            const int64_t end = start + (int64_t)rows * p.row_bytes;
-            const int64_t a_start = start & ~(int64_t)15;
-            int64_t a_end = (end + 15) & ~(int64_t)15;
-            const int64_t bulk_limit = p.w_bytes & ~(int64_t)15;  // bytes the bulk engine may touch
-            if (a_end > bulk_limit) a_end = bulk_limit;
-            uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
-            // ragged end of the weight stream (< 16 bytes): plain loads
-            if (end > a_end) {
-                const int64_t from = a_end > a_start ? a_end : a_start;
-                for (int64_t i = from + lane; i < end; i += 32) dst[i - a_start] = __ldg(p.w + i);
-            }
-            __syncwarp();
-            if (lane == 0) {
-                if (a_end > a_start) {
-                    const uint32_t bytes = (uint32_t)(a_end - a_start);
-                    mbar_arrive_expect_tx(&full[s], bytes);
-                    bulk_g2s(dst, p.w + a_start, bytes, &full[s]);
-                } else {
-                    mbar_arrive(&full[s]);
-                }
-            }
-        }
+        gemv_producer(p, full, empty, stage0, tile_rows, r_begin, r_end, lane);
         return;
     }
 

@@ -4,6 +4,7 @@
 #include "dequant.cuh"
 #include "gemm_q4k.cuh"
 #include "gemv.cuh"
+#include "gemv_mma.cuh"
 #include "quantize_act.cuh"
 
 #include <atomic>
@@ -137,6 +138,40 @@ static bool gemv_shape_override(int &cw, int &rw) {
     return cached == 1;
 }
 
+template <int M>
+static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    auto kern = gemv_mma_q4k_kernel<M>;
+    static int configured_smem[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_smem[dev] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured_smem[dev] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(32u * (kMmaWarps + 1));
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// Development knob: LLOOM_GEMV_MMA=0 keeps 3 <= m <= 8 on the dp4a kernel.
+static bool gemv_mma_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char *e = getenv("LLOOM_GEMV_MMA");
+        cached = (e && e[0] == '0') ? 0 : 1;
+    }
+    return cached == 1;
+}
+
 // Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
 // quantized in the kernel's prologue) is non-null.
 static int gemv_launch(int w_dtype, const void *w, const void *act, const float *x, float *y, int64_t m, int64_t n,
@@ -157,6 +192,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.m = (int)m;
     p.w_dtype = w_dtype;
     p.act_bytes = (int)act_plane_bytes(w_dtype, m, k);
+    p.act_row_pad = 0;
     // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
     const int64_t units = k / (w_dtype == LLOOM_Q8_0 ? 64 : 256);
     int lpr_log2 = 0;
@@ -168,6 +204,33 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     const int64_t pad = (p.row_bytes % 16 == 0) ? 16 : 48;
     int grid = di.sm_count;
     if ((int64_t)grid > n) grid = (int)n;
+    const bool overlap_on = g_launch_overlap.load(std::memory_order_relaxed) != 0;
+    // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
+    if (w_dtype == LLOOM_Q4_K && m >= 3 && gemv_mma_enabled()) {
+        const int64_t stage = (int64_t)kMmaTileRows * (p.row_bytes + 16);
+        const int act_bytes_mma = (int)act_plane_bytes(w_dtype, m, k, 16);
+        const int64_t budget = (int64_t)di.max_smem_optin - 128 - kMmaRedBytes - act_bytes_mma;
+        if (budget >= 2 * stage) {
+            p.act_bytes = act_bytes_mma;
+            p.act_row_pad = 16;
+            int64_t stages = budget / stage;
+            if (stages > kMaxStages) stages = kMaxStages;
+            p.n_cwarps = kMmaWarps;
+            p.stages = (int)stages;
+            p.stage_bytes = (int)stage;
+            const int smem = 128 + kMmaRedBytes + p.act_bytes + (int)(stages * stage);
+            cudaError_t e = cudaErrorInvalidValue;
+            switch (m) {
+            case 3: e = launch_gemv_mma_inst<3>(p, grid, smem, overlap_on, stream); break;
+            case 4: e = launch_gemv_mma_inst<4>(p, grid, smem, overlap_on, stream); break;
+            case 5: e = launch_gemv_mma_inst<5>(p, grid, smem, overlap_on, stream); break;
+            case 6: e = launch_gemv_mma_inst<6>(p, grid, smem, overlap_on, stream); break;
+            case 7: e = launch_gemv_mma_inst<7>(p, grid, smem, overlap_on, stream); break;
+            case 8: e = launch_gemv_mma_inst<8>(p, grid, smem, overlap_on, stream); break;
+            }
+            return launch_status(e);
+        }
+    }
     // Tile shapes {consumer warps, rows per lane}, widest first (after an optional pinned shape); the
     // first that leaves room for at least two stages wins.  With launch overlap on, m <= 2 tries shapes
     // that fit two CTAs per SM first, so that consecutive launches can sit side by side.
