@@ -34,14 +34,12 @@ constexpr int kQ8_0UnitStride = 64 + 16;
 
 __host__ __device__ inline int64_t round16(int64_t v) { return (v + 15) / 16 * 16; }
 
-// row_pad: extra bytes after each activation row of the qs plane (the tensor-core kernel, whose lanes read
-// eight activation rows at once, pads by 16 so that those rows fall on different banks).
-__host__ __device__ inline int64_t act_qs_bytes(int w_dtype, int64_t m, int64_t k, int row_pad = 0) {
-    return ((w_dtype == LLOOM_Q8_0) ? m * (k / 64) * kQ8_0UnitStride : m * (k / 256) * kQ8KUnitStride) + m * row_pad;
+__host__ __device__ inline int64_t act_qs_bytes(int w_dtype, int64_t m, int64_t k) {
+    return (w_dtype == LLOOM_Q8_0) ? m * (k / 64) * kQ8_0UnitStride : m * (k / 256) * kQ8KUnitStride;
 }
 
-__host__ __device__ inline int64_t act_plane_bytes(int w_dtype, int64_t m, int64_t k, int row_pad = 0) {
-    const int64_t qs = act_qs_bytes(w_dtype, m, k, row_pad);
+__host__ __device__ inline int64_t act_plane_bytes(int w_dtype, int64_t m, int64_t k) {
+    const int64_t qs = act_qs_bytes(w_dtype, m, k);
     const int64_t d = (w_dtype == LLOOM_Q8_0) ? m * (k / 32) * 4 : m * (k / 256) * 4;
     const int64_t sums = (w_dtype == LLOOM_Q8_0) ? 0 : (w_dtype == LLOOM_Q4_K ? m * (k / 32) * 2 : m * (k / 16) * 2);
     return round16(qs) + round16(d) + round16(sums);
@@ -304,7 +302,10 @@ struct GemvParams {
     int stages;
     int stage_bytes;   // multiple of 128
     int act_bytes;     // multiple of 16
-    int act_row_pad;   // extra bytes after each activation row of the qs plane (0, or 16 for the tensor-core kernel)
+    int row_pitch;     // tensor-core kernel only: bytes between weight rows inside a stage
+    int act_pitch;     // tensor-core kernel only: bytes between activation rows of the code plane
+    int act_planes;    // tensor-core kernel only: `act` already holds the plane image (else canonical blocks)
+    int tile_bar_bytes;  // tensor-core kernel only: bytes of the per-tile barrier array (multiple of 16)
 };
 
 constexpr int kMaxStages = 8;
@@ -327,7 +328,7 @@ __device__ __forceinline__ unsigned long long trace_now() {
 // Canonical activation blocks (global) -> planes (shared); all `nthreads` consumer threads take part.
 __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_smem, int tid, int nthreads,
                                            ActPlanes &planes) {
-    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k, p.act_row_pad));
+    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k));
     float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
     planes.qs = reinterpret_cast<const int8_t *>(act_smem);
     planes.d = dpl;
@@ -377,7 +378,7 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
                 if (i < total) {
                     const int blk = i / 73, w = i - blk * 73;
                     if (w == 0) dpl[blk] = __uint_as_float(v[j]);
-                    else if (w <= 64) q32[blk * (kQ8KUnitStride / 4) + (blk / nb) * (p.act_row_pad / 4) + w - 1] = v[j];
+                    else if (w <= 64) q32[blk * (kQ8KUnitStride / 4) + w - 1] = v[j];
                     else if (pair) sums[blk * 8 + w - 65] = (short)((int)(short)(v[j] & 0xffffu) + (int)(short)(v[j] >> 16));
                     else {
                         const int mrow = blk / nb, b = blk - mrow * nb, jj = w - 65;  // word jj: bsums 2jj, 2jj+1
@@ -394,7 +395,7 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
 // arithmetic as the stand-alone quantizer kernels (bit-identical codes, scales and sums).
 __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uint8_t *act_smem, int warp, int lane,
                                                         ActPlanes &planes) {
-    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k, p.act_row_pad));
+    const size_t qs_bytes = round16(act_qs_bytes(p.w_dtype, p.m, p.k));
     float *dpl = reinterpret_cast<float *>(act_smem + qs_bytes);
     uint32_t *q32 = reinterpret_cast<uint32_t *>(act_smem);
     planes.qs = reinterpret_cast<const int8_t *>(act_smem);
@@ -440,9 +441,8 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
                 float d;
                 int sum16;
                 q8k_quantize_warp(rep == 0 ? va : vb, lane, q_lo, q_hi, d, sum16);
-                uint32_t *qdst = q32 + blk * (kQ8KUnitStride / 4) + (blk / nb) * (p.act_row_pad / 4) + lane * 2;
-                qdst[0] = q_lo;
-                qdst[1] = q_hi;
+                q32[blk * (kQ8KUnitStride / 4) + lane * 2] = q_lo;
+                q32[blk * (kQ8KUnitStride / 4) + lane * 2 + 1] = q_hi;
                 if (lane == 0) dpl[blk] = d;
                 if (p.w_dtype == LLOOM_Q4_K) {
                     const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
@@ -493,8 +493,10 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
 }
 
 // Row-wise variant for row sizes that are multiples of 16 bytes: one bulk copy per row, rows `row_pitch` bytes
-// apart in the stage (a pitch of row_bytes + 16 puts consecutive rows four banks apart).
-__device__ __forceinline__ void gemv_producer_rows(const GemvParams &p, uint64_t *full, uint64_t *empty, uint8_t *stage0,
+// apart in the stage (the caller picks a pitch that spreads the rows a warp reads together over the banks).
+// Every tile completes a barrier of its own (tile_full[it], used once): the consumers of a stage are different
+// warps from one use to the next, and a phase parity cannot tell a late warp which use it is looking at.
+__device__ __forceinline__ void gemv_producer_rows(const GemvParams &p, uint64_t *tile_full, uint64_t *empty, uint8_t *stage0,
                                                    int tile_rows, int row_pitch, int r_begin, int r_end, int lane) {
     int it = 0;
     for (int row0 = r_begin; row0 < r_end; row0 += tile_rows, ++it) {
@@ -504,10 +506,10 @@ __device__ __forceinline__ void gemv_producer_rows(const GemvParams &p, uint64_t
         }
         const int rows = min(tile_rows, r_end - row0);
         uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
-        if (lane == 0) mbar_arrive_expect_tx(&full[s], (uint32_t)(rows * p.row_bytes));
+        if (lane == 0) mbar_arrive_expect_tx(&tile_full[it], (uint32_t)(rows * p.row_bytes));
         __syncwarp();
         for (int r = lane; r < rows; r += 32)
-            bulk_g2s(dst + (size_t)r * row_pitch, p.w + (int64_t)(row0 + r) * p.row_bytes, (uint32_t)p.row_bytes, &full[s]);
+            bulk_g2s(dst + (size_t)r * row_pitch, p.w + (int64_t)(row0 + r) * p.row_bytes, (uint32_t)p.row_bytes, &tile_full[it]);
     }
 }
 

@@ -3,15 +3,18 @@
 // With several activation rows the dp4a kernel (gemv.cuh) spends its time issuing dot-product
 // instructions, not waiting for HBM.  Here one warp-level `mma.sync.m16n8k32.s8` multiplies a
 // 16-row x 32-element weight sub-block (nibbles unpacked to int8 in registers) by the 32 x 8 block of
-// activation codes (8 = the activation rows, zero-padded), giving exact int32 sums for 16 rows x 8
-// rows of activations at once; the 6-bit sub-block scale is applied to the four accumulators of each
-// MMA as an integer multiply, so the superblock sum S stays an exact integer, and the f32 scales are
-// applied once per superblock in the reference's form (k_quants.rs:1540-1620, avx.rs:443-525).
+// activation codes (8 = the activation rows; columns past M compute on row 0's codes and are never
+// stored), giving exact int32 sums for 16 weight rows x 8 activation rows at once.  The 6-bit
+// sub-block scale is applied to the four accumulators of each MMA as an integer multiply, so the
+// superblock sum S stays an exact integer; the min term sum_j m_j * bsum_j is two more MMAs over the
+// sub-block sums split as 64*h + l (both halves fit int8); the f32 scales are applied once per
+// superblock in the reference's form (k_quants.rs:1540-1620, avx.rs:443-525).
 //
-// Same frame as the dp4a kernel: persistent CTA per SM over a contiguous row range, producer warp
-// streaming 16-row tiles through the bulk-copy ring, activation planes in shared memory.  The eight
-// consumer warps split the superblocks of a tile (warp w takes b = w, w+8, ...); their partial f32
-// tiles meet in shared memory and are summed in a fixed order, so results are run-to-run identical.
+// Frame: persistent CTA per SM over a contiguous row range; a producer warp streams 16-row tiles
+// through a bulk-copy ring, one copy per row so that rows sit `row_pitch` bytes apart (8 banks mod 32:
+// the 64-bit fragment loads of four rows are conflict-free).  Each of the eight consumer warps owns whole
+// tiles (tile i goes to warp i mod 8) and walks the superblocks of its tile in order, so a row's f32
+// sum has one fixed order whatever the batch, the shard or the launch; no CTA-wide barrier after start-up.
 #pragma once
 
 #include "gemv.cuh"
@@ -20,7 +23,25 @@ namespace lloom {
 
 constexpr int kMmaTileRows = 16;
 constexpr int kMmaWarps = 8;
-constexpr int kMmaRedBytes = 2 * kMmaWarps * 16 * 8 * 4;  // double-buffered partial tiles
+
+// Pitch in bytes (a multiple of 16, >= bytes) that is `want_words` 32-bit words modulo the 32 banks.
+__host__ __device__ inline int64_t bank_pitch(int64_t bytes, int want_words) {
+    const int64_t words = (bytes + 3) / 4;
+    int64_t pad = (want_words - words % 32 + 32) % 32;
+    while ((words + pad) % 4 != 0) pad += 32;  // never taken when bytes % 16 == 0 and want_words % 4 == 0
+    return (words + pad) * 4;
+}
+
+// Activation planes of the tensor-core kernel, per activation row t and superblock b:
+//   codes  [t][b][64 words]  the 256 int8 codes, words permuted so that lane (gid, tig) finds the four words of
+//                            group g it feeds to the MMAs -- low sub-block words 2tig, 2tig+1, high sub-block
+//                            words 2tig, 2tig+1 -- in one 16-byte load at word 16g + 4tig; rows act_pitch apart
+//   lh     [t][b][16 bytes]  l_j = bsum_j & 63 (j = 0..7, the 32-element sub-blocks), then h_j = bsum_j >> 6
+//   d      [t][b] f32
+__host__ __device__ inline int64_t mma_act_pitch(int64_t k) { return bank_pitch((k / 256) * 256, 16); }
+__host__ __device__ inline int64_t mma_act_bytes(int64_t m, int64_t k) {
+    return round16(m * mma_act_pitch(k) + m * (k / 256) * 16 + m * (k / 256) * 4);
+}
 
 __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile(
@@ -29,61 +50,142 @@ __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], const uint32_t (&a)[
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// Dynamic shared memory: [barriers 128 B][partial tiles 8 KB][act planes][stage 0][stage 1]...
-template <int M>
+// Where word c (0..63) of a block's codes goes inside the block's 64-word slot of the codes plane.
+__host__ __device__ inline int mma_code_pos(int c) {
+    const int g = c >> 4, r = c & 15;
+    return 16 * g + 4 * ((r & 7) >> 1) + 2 * (r >> 3) + (r & 1);
+}
+
+// Canonical Q8_K blocks (292 B: f32 d, 256 codes, 16 i16 sums of 16) -> the three planes above.
+__device__ __forceinline__ void stage_acts_mma(const GemvParams &p, uint8_t *act_smem, int tid, int nthreads) {
+    const int nb = p.k >> 8;
+    uint8_t *lh = act_smem + (size_t)p.m * p.act_pitch;
+    float *dpl = reinterpret_cast<float *>(lh + (size_t)p.m * nb * 16);
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(p.act);
+    const int total = p.m * nb * (Q8K_BYTES / 4);
+    constexpr int kUnroll = 8;  // loads of a batch in flight together: the latency is paid once per batch
+    for (int i0 = tid; i0 < total; i0 += nthreads * kUnroll) {
+        uint32_t v[kUnroll];
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int i = i0 + j * nthreads;
+            v[j] = i < total ? __ldg(src + i) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int i = i0 + j * nthreads;
+            if (i >= total) break;
+            const int blk = i / (Q8K_BYTES / 4), w = i - blk * (Q8K_BYTES / 4);
+            const int t = blk / nb, b = blk - t * nb;
+            if (w == 0) {
+                dpl[blk] = __uint_as_float(v[j]);
+            } else if (w <= 64) {
+                reinterpret_cast<uint32_t *>(act_smem + (size_t)t * p.act_pitch + (size_t)b * 256)[mma_code_pos(w - 1)] = v[j];
+            } else {
+                const int sb = w - 65;  // sub-block sb = i16 sums 2sb, 2sb+1
+                const int s = (int)(short)(v[j] & 0xffffu) + (int)(short)(v[j] >> 16);
+                lh[(size_t)blk * 16 + sb] = (uint8_t)(s & 63);
+                lh[(size_t)blk * 16 + 8 + sb] = (uint8_t)((s >> 6) & 0xff);
+            }
+        }
+    }
+}
+
+// f32 activations -> the plane image in global memory (the same bytes stage_acts_mma leaves in shared
+// memory), one warp per 256-element block; the GEMV then fetches the image with one bulk copy.
+// Block arithmetic: q8k_quantize_warp, shared with the canonical quantizer.
+__global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                                  int m, int nb, int act_pitch) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV may start streaming weights
+    const int lane = threadIdx.x & 31;
+    const int blk = (int)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    if (blk >= m * nb) return;  // whole warp leaves together
+    const int t = blk / nb, b = blk - t * nb;
+    float v[8];
+    load8(x + (int64_t)blk * QK_K + lane * 8, v);
+    uint32_t q_lo, q_hi;
+    float d;
+    int sum16;
+    q8k_quantize_warp(v, lane, q_lo, q_hi, d, sum16);
+    const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+    uint32_t *codes = reinterpret_cast<uint32_t *>(out + (size_t)t * act_pitch + (size_t)b * 256);
+    *reinterpret_cast<uint2 *>(codes + mma_code_pos(2 * lane)) = make_uint2(q_lo, q_hi);  // words 2l, 2l+1 stay adjacent
+    uint8_t *lh = out + (size_t)m * act_pitch + (size_t)blk * 16;
+    if ((lane & 3) == 0) {
+        lh[lane >> 2] = (uint8_t)(sum32 & 63);
+        lh[8 + (lane >> 2)] = (uint8_t)((sum32 >> 6) & 0xff);
+    }
+    if (lane == 0) reinterpret_cast<float *>(out + (size_t)m * act_pitch + (size_t)m * nb * 16)[blk] = d;
+}
+
+constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image
+constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
+
+// Dynamic shared memory: [barriers 128 B][per-tile barriers][act planes][stage 0][stage 1]...
 __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-    uint64_t *empty = full + kMaxStages;
-    float *red = reinterpret_cast<float *>(smem + 128);
-    uint8_t *act_smem = smem + 128 + kMmaRedBytes;
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *act_bar = empty + kMaxStages;
+    uint64_t *tile_full = reinterpret_cast<uint64_t *>(smem + kMmaBarBytes);
+    uint8_t *act_smem = smem + kMmaBarBytes + p.tile_bar_bytes;
     uint8_t *stage0 = act_smem + p.act_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r_begin = (int)(((int64_t)blockIdx.x * p.n) / gridDim.x);
     const int r_end = (int)(((int64_t)(blockIdx.x + 1) * p.n) / gridDim.x);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kMmaWarps);
-        }
-        fence_mbar_init();
-    }
+    const int ntiles = (r_end - r_begin + kMmaTileRows - 1) / kMmaTileRows;
+    for (int i = threadIdx.x; i < ntiles; i += blockDim.x) mbar_init(&tile_full[i], 1);
+    if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], 1);
+    if (threadIdx.x == 32) mbar_init(act_bar, 1);
+    fence_mbar_init();
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    const int row_pitch = (int)p.row_bytes + 16;  // consecutive rows four banks apart: conflict-free fragment loads
     if (warp == kMmaWarps) {
-        gemv_producer_rows(p, full, empty, stage0, kMmaTileRows, row_pitch, r_begin, r_end, lane);
+        gemv_producer_rows(p, tile_full, empty, stage0, kMmaTileRows, p.row_pitch, r_begin, r_end, lane);
         return;
     }
 
-    ActPlanes planes;
     constexpr int nthreads = kMmaWarps * 32;
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (p.x) quantize_acts_to_planes(p, act_smem, warp, lane, planes);
-    else stage_acts(p, act_smem, threadIdx.x, nthreads, planes);
-    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (p.act_planes) {
+        if (threadIdx.x == 0) {
+            mbar_arrive_expect_tx(act_bar, (uint32_t)p.act_bytes);
+            bulk_g2s(act_smem, p.act, (uint32_t)p.act_bytes, act_bar);
+        }
+        if (!mbar_wait(act_bar, 0)) return;
+    } else {
+        stage_acts_mma(p, act_smem, threadIdx.x, nthreads);
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    }
 
     const int nb = p.k >> 8;
     const int gid = lane >> 2, tig = lane & 3;  // MMA fragment coordinates
-    const bool tok_ok = gid < M;                // this lane's activation row (B-fragment column) exists
-    // activation rows this lane's accumulators belong to (C-fragment columns 2*tig, 2*tig + 1)
+    // B fragments come from activation row gid (rows past m read row 0; their columns are never stored)
+    const int tb = gid < p.m ? gid : 0;
+    const uint8_t *codes = act_smem + (size_t)tb * p.act_pitch + 16 * tig;
+    const uint8_t *lh_base = act_smem + (size_t)p.m * p.act_pitch;
+    const uint32_t *lh_b = reinterpret_cast<const uint32_t *>(lh_base + (size_t)tb * nb * 16) + (tig & 1);
+    const float *dpl = reinterpret_cast<const float *>(lh_base + (size_t)p.m * nb * 16);
+    // the accumulators of this lane belong to activation rows 2*tig and 2*tig + 1
     const int t0 = 2 * tig, t1 = 2 * tig + 1;
-    int it = 0;
-    bool alive = true;  // after a timed-out wait the warp keeps walking the tiles (the CTA barrier below needs it) but idles
-    for (int trow = r_begin; trow < r_end; trow += kMmaTileRows, ++it) {
+    const float *d0 = dpl + (t0 < p.m ? t0 : 0) * nb, *d1 = dpl + (t1 < p.m ? t1 : 0) * nb;
+    const bool min_lane = tig < 2;  // lanes that carry the eight mins / sub-block sums in the min-term MMAs
+
+    for (int it = warp; it < ntiles; it += kMmaWarps) {
         const int s = it % p.stages;
-        alive = alive && mbar_wait(&full[s], (it / p.stages) & 1);
+        if (!mbar_wait(&tile_full[it], 0)) return;
+        const int trow = r_begin + it * kMmaTileRows;
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
         const int rows = min(kMmaTileRows, r_end - trow);
         // rows of the A fragment held by this lane; rows past the end of the range read row 0 and are dropped later
         const int ra = gid < rows ? gid : 0, rb = gid + 8 < rows ? gid + 8 : 0;
-        const uint8_t *rowa = tile_base + (size_t)ra * row_pitch, *rowb = tile_base + (size_t)rb * row_pitch;
+        const uint8_t *rowa = tile_base + (size_t)ra * p.row_pitch, *rowb = tile_base + (size_t)rb * p.row_pitch;
 
         float out[4] = {0.f, 0.f, 0.f, 0.f};  // (row gid, t0), (gid, t1), (gid+8, t0), (gid+8, t1)
-        for (int b = warp; alive && b < nb; b += kMmaWarps) {
+#pragma unroll 2
+        for (int b = 0; b < nb; ++b) {
             const uint4 ha = *reinterpret_cast<const uint4 *>(rowa + (size_t)b * Q4K_BYTES);
             const uint4 hb = *reinterpret_cast<const uint4 *>(rowb + (size_t)b * Q4K_BYTES);
             // 6-bit scales / mins (utils.rs:50-60), four per word, for the two rows
@@ -91,25 +193,20 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             const uint32_t scb[2] = {hb.y & 0x3f3f3f3fu, (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4)};
             const uint32_t mna[2] = {ha.z & 0x3f3f3f3fu, ((ha.w >> 4) & 0x0f0f0f0fu) | (((ha.z >> 6) & 0x03030303u) << 4)};
             const uint32_t mnb[2] = {hb.z & 0x3f3f3f3fu, ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4)};
-            const uint32_t *qa = reinterpret_cast<const uint32_t *>(rowa + (size_t)b * Q4K_BYTES + 16);
-            const uint32_t *qb = reinterpret_cast<const uint32_t *>(rowb + (size_t)b * Q4K_BYTES + 16);
-            const uint32_t *act = reinterpret_cast<const uint32_t *>(
-                planes.qs + (size_t)(tok_ok ? gid : 0) * ((size_t)nb * kQ8KUnitStride + p.act_row_pad) + (size_t)b * kQ8KUnitStride);
+            const uint2 *qa = reinterpret_cast<const uint2 *>(rowa + (size_t)b * Q4K_BYTES + 16) + tig;
+            const uint2 *qb = reinterpret_cast<const uint2 *>(rowb + (size_t)b * Q4K_BYTES + 16) + tig;
+            const uint4 *act = reinterpret_cast<const uint4 *>(codes + (size_t)b * 256);
             int S[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-                // weight words of this lane: bytes 4*tig.. and 16+4*tig.. of the group's 32 bytes, rows gid / gid+8
-                const uint32_t wa0 = qa[8 * g + tig], wa1 = qa[8 * g + tig + 4];
-                const uint32_t wb0 = qb[8 * g + tig], wb1 = qb[8 * g + tig + 4];
-                // activation words: sub-block 2g at element 64g, sub-block 2g+1 at 64g + 32
-                uint32_t bl[2], bh[2];
-                bl[0] = tok_ok ? act[16 * g + tig] : 0u;
-                bl[1] = tok_ok ? act[16 * g + 4 + tig] : 0u;
-                bh[0] = tok_ok ? act[16 * g + 8 + tig] : 0u;
-                bh[1] = tok_ok ? act[16 * g + 12 + tig] : 0u;
-                const uint32_t alo[4] = {wa0 & 0x0f0f0f0fu, wb0 & 0x0f0f0f0fu, wa1 & 0x0f0f0f0fu, wb1 & 0x0f0f0f0fu};
-                const uint32_t ahi[4] = {(wa0 >> 4) & 0x0f0f0f0fu, (wb0 >> 4) & 0x0f0f0f0fu, (wa1 >> 4) & 0x0f0f0f0fu,
-                                         (wb1 >> 4) & 0x0f0f0f0fu};
+                // bytes 8*tig .. 8*tig+7 of the group's 32 nibble bytes, rows gid / gid+8; the same element
+                // positions of the low (2g) and high (2g+1) sub-blocks of the activations
+                const uint2 wa = qa[4 * g], wb = qb[4 * g];
+                const uint4 av = act[4 * g];
+                const uint32_t bl[2] = {av.x, av.y}, bh[2] = {av.z, av.w};
+                const uint32_t alo[4] = {wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu};
+                const uint32_t ahi[4] = {(wa.x >> 4) & 0x0f0f0f0fu, (wb.x >> 4) & 0x0f0f0f0fu, (wa.y >> 4) & 0x0f0f0f0fu,
+                                         (wb.y >> 4) & 0x0f0f0f0fu};
                 int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
                 mma_s8_16x8x32(cl, alo, bl);
                 mma_s8_16x8x32(ch, ahi, bh);
@@ -121,49 +218,37 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
                 S[2] += sb_lo * cl[2] + sb_hi * ch[2];
                 S[3] += sb_lo * cl[3] + sb_hi * ch[3];
             }
+            // min term: k = 0..7 of one MMA carry the eight mins against the eight l (then h) halves of the sums
+            const uint32_t am[4] = {min_lane ? (tig ? mna[1] : mna[0]) : 0u, min_lane ? (tig ? mnb[1] : mnb[0]) : 0u, 0u, 0u};
+            const uint32_t lv = lh_b[b * 4], hv = lh_b[b * 4 + 2];
+            const uint32_t bml[2] = {min_lane ? lv : 0u, 0u}, bmh[2] = {min_lane ? hv : 0u, 0u};
+            int ml[4] = {0, 0, 0, 0}, mh[4] = {0, 0, 0, 0};
+            mma_s8_16x8x32(ml, am, bml);
+            mma_s8_16x8x32(mh, am, bmh);
+
             const float dwa = f16_bits_to_f32(ha.x & 0xffffu), dma = f16_bits_to_f32(ha.x >> 16);
             const float dwb = f16_bits_to_f32(hb.x & 0xffffu), dmb = f16_bits_to_f32(hb.x >> 16);
-#pragma unroll
-            for (int tt = 0; tt < 2; ++tt) {
-                const int t = tt == 0 ? t0 : t1;
-                if (t < M) {
-                    const uint4 sp = *reinterpret_cast<const uint4 *>(planes.sums + ((size_t)t * nb + b) * 8);
-                    const float da = planes.d[t * nb + b];
-                    int ma = __dp2a_lo((int)sp.x, (int)mna[0], 0);
-                    ma = __dp2a_hi((int)sp.y, (int)mna[0], ma);
-                    ma = __dp2a_lo((int)sp.z, (int)mna[1], ma);
-                    ma = __dp2a_hi((int)sp.w, (int)mna[1], ma);
-                    int mb = __dp2a_lo((int)sp.x, (int)mnb[0], 0);
-                    mb = __dp2a_hi((int)sp.y, (int)mnb[0], mb);
-                    mb = __dp2a_lo((int)sp.z, (int)mnb[1], mb);
-                    mb = __dp2a_hi((int)sp.w, (int)mnb[1], mb);
-                    out[tt] = fmaf(__fmul_rn(da, dwa), (float)S[tt], out[tt]);
-                    out[tt] = fmaf(__fmul_rn(-da, dma), (float)ma, out[tt]);
-                    out[2 + tt] = fmaf(__fmul_rn(da, dwb), (float)S[2 + tt], out[2 + tt]);
-                    out[2 + tt] = fmaf(__fmul_rn(-da, dmb), (float)mb, out[2 + tt]);
-                }
-            }
+            const float da0 = d0[b], da1 = d1[b];
+            out[0] = fmaf(__fmul_rn(da0, dwa), (float)S[0], out[0]);
+            out[0] = fmaf(__fmul_rn(-da0, dma), (float)(ml[0] + 64 * mh[0]), out[0]);
+            out[1] = fmaf(__fmul_rn(da1, dwa), (float)S[1], out[1]);
+            out[1] = fmaf(__fmul_rn(-da1, dma), (float)(ml[1] + 64 * mh[1]), out[1]);
+            out[2] = fmaf(__fmul_rn(da0, dwb), (float)S[2], out[2]);
+            out[2] = fmaf(__fmul_rn(-da0, dmb), (float)(ml[2] + 64 * mh[2]), out[2]);
+            out[3] = fmaf(__fmul_rn(da1, dwb), (float)S[3], out[3]);
+            out[3] = fmaf(__fmul_rn(-da1, dmb), (float)(ml[3] + 64 * mh[3]), out[3]);
         }
         // this warp is done reading the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
 
-        // partial tiles of the eight warps meet in shared memory and are summed in warp order
-        float *mine = red + ((it & 1) * kMmaWarps + warp) * 128;
-        mine[gid * 8 + t0] = out[0];
-        mine[gid * 8 + t1] = out[1];
-        mine[(gid + 8) * 8 + t0] = out[2];
-        mine[(gid + 8) * 8 + t1] = out[3];
-        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-        if (threadIdx.x < 128) {
-            const int r = threadIdx.x >> 3, t = threadIdx.x & 7;
-            if (alive && r < rows && t < M) {
-                const float *src = red + (it & 1) * kMmaWarps * 128 + r * 8 + t;
-                float v = 0.0f;
-#pragma unroll
-                for (int w = 0; w < kMmaWarps; ++w) v += src[w * 128];
-                p.y[(int64_t)t * p.ldy + trow + r] = v;
-            }
+        if (t0 < p.m) {
+            if (gid < rows) p.y[(int64_t)t0 * p.ldy + trow + gid] = out[0];
+            if (gid + 8 < rows) p.y[(int64_t)t0 * p.ldy + trow + gid + 8] = out[2];
+        }
+        if (t1 < p.m) {
+            if (gid < rows) p.y[(int64_t)t1 * p.ldy + trow + gid] = out[1];
+            if (gid + 8 < rows) p.y[(int64_t)t1 * p.ldy + trow + gid + 8] = out[3];
         }
     }
 }

@@ -138,9 +138,8 @@ static bool gemv_shape_override(int &cw, int &rw) {
     return cached == 1;
 }
 
-template <int M>
-static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_mma_q4k_kernel<M>;
+static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    auto kern = gemv_mma_q4k_kernel;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -172,13 +171,30 @@ static bool gemv_mma_enabled() {
     return cached == 1;
 }
 
+// Whether the tensor-core GEMV takes this shape: Q4_K, 3..8 activation rows, two 16-row stages fit beside the
+// activation planes.
+static int64_t gemv_mma_tile_bar_bytes(const DeviceInfo &di, int64_t n) {
+    const int64_t grid = n < di.sm_count ? n : di.sm_count;
+    const int64_t tiles = ((n + grid - 1) / grid + kMmaTileRows - 1) / kMmaTileRows;
+    return round16(tiles * 8);
+}
+
+static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
+    if (w_dtype != LLOOM_Q4_K || m < 3 || m > 8 || !gemv_mma_enabled()) return false;
+    const int64_t bars = gemv_mma_tile_bar_bytes(di, n);
+    if (bars > kMmaMaxTiles * 8) return false;
+    const int64_t stage = (int64_t)kMmaTileRows * bank_pitch(weight_row_bytes(w_dtype, k), 8);
+    return (int64_t)di.max_smem_optin - kMmaBarBytes - bars - mma_act_bytes(m, k) >= 2 * stage;
+}
+
 // Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
 // quantized in the kernel's prologue) is non-null.
 static int gemv_launch(int w_dtype, const void *w, const void *act, const float *x, float *y, int64_t m, int64_t n,
-                       int64_t k, int64_t ldy, cudaStream_t stream) {
+                       int64_t k, int64_t ldy, cudaStream_t stream, bool act_planes = false) {
     DeviceInfo di;
     int rc = device_info(di);
     if (rc != LLOOM_OK) return rc;
+    if (act_planes && !gemv_mma_fits(di, w_dtype, m, n, k)) return LLOOM_ERR_SHAPE;
     GemvParams p;
     p.w = (const uint8_t *)w;
     p.act = (const uint8_t *)act;
@@ -192,7 +208,10 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.m = (int)m;
     p.w_dtype = w_dtype;
     p.act_bytes = (int)act_plane_bytes(w_dtype, m, k);
-    p.act_row_pad = 0;
+    p.row_pitch = 0;
+    p.act_pitch = 0;
+    p.act_planes = 0;
+    p.tile_bar_bytes = 0;
     // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
     const int64_t units = k / (w_dtype == LLOOM_Q8_0 ? 64 : 256);
     int lpr_log2 = 0;
@@ -206,30 +225,21 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     if ((int64_t)grid > n) grid = (int)n;
     const bool overlap_on = g_launch_overlap.load(std::memory_order_relaxed) != 0;
     // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
-    if (w_dtype == LLOOM_Q4_K && m >= 3 && gemv_mma_enabled()) {
-        const int64_t stage = (int64_t)kMmaTileRows * (p.row_bytes + 16);
-        const int act_bytes_mma = (int)act_plane_bytes(w_dtype, m, k, 16);
-        const int64_t budget = (int64_t)di.max_smem_optin - 128 - kMmaRedBytes - act_bytes_mma;
-        if (budget >= 2 * stage) {
-            p.act_bytes = act_bytes_mma;
-            p.act_row_pad = 16;
-            int64_t stages = budget / stage;
-            if (stages > kMaxStages) stages = kMaxStages;
-            p.n_cwarps = kMmaWarps;
-            p.stages = (int)stages;
-            p.stage_bytes = (int)stage;
-            const int smem = 128 + kMmaRedBytes + p.act_bytes + (int)(stages * stage);
-            cudaError_t e = cudaErrorInvalidValue;
-            switch (m) {
-            case 3: e = launch_gemv_mma_inst<3>(p, grid, smem, overlap_on, stream); break;
-            case 4: e = launch_gemv_mma_inst<4>(p, grid, smem, overlap_on, stream); break;
-            case 5: e = launch_gemv_mma_inst<5>(p, grid, smem, overlap_on, stream); break;
-            case 6: e = launch_gemv_mma_inst<6>(p, grid, smem, overlap_on, stream); break;
-            case 7: e = launch_gemv_mma_inst<7>(p, grid, smem, overlap_on, stream); break;
-            case 8: e = launch_gemv_mma_inst<8>(p, grid, smem, overlap_on, stream); break;
-            }
-            return launch_status(e);
-        }
+    if (gemv_mma_fits(di, w_dtype, m, n, k)) {
+        const int64_t row_pitch = bank_pitch(p.row_bytes, 8);
+        const int64_t stage = (int64_t)kMmaTileRows * row_pitch;
+        p.act_bytes = (int)mma_act_bytes(m, k);
+        p.act_pitch = (int)mma_act_pitch(k);
+        p.act_planes = act_planes ? 1 : 0;
+        p.row_pitch = (int)row_pitch;
+        p.tile_bar_bytes = (int)gemv_mma_tile_bar_bytes(di, n);
+        int64_t stages = ((int64_t)di.max_smem_optin - kMmaBarBytes - p.tile_bar_bytes - p.act_bytes) / stage;
+        if (stages > kMaxStages) stages = kMaxStages;
+        p.n_cwarps = kMmaWarps;
+        p.stages = (int)stages;
+        p.stage_bytes = (int)stage;
+        const int smem = kMmaBarBytes + p.tile_bar_bytes + p.act_bytes + (int)(stages * stage);
+        return launch_status(launch_gemv_mma(p, grid, smem, overlap_on, stream));
     }
     // Tile shapes {consumer warps, rows per lane}, widest first (after an optional pinned shape); the
     // first that leaves room for at least two stages wins.  With launch overlap on, m <= 2 tries shapes
@@ -441,6 +451,21 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     // single-token decode: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
     // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
     if (m <= 2) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
+    if (m <= 8) {
+        // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
+        // codes, scales and sums as the canonical blocks, laid out for its fragment loads)
+        DeviceInfo di;
+        rc = device_info(di);
+        if (rc != LLOOM_OK) return rc;
+        if (gemv_mma_fits(di, w_dtype, m, n, k) && mma_act_bytes(m, k) <= need) {
+            const int nb = (int)(k / QK_K);
+            quantize_q8k_planes_kernel<<<(unsigned)ceil_div64(m * nb * 32, 256), 256, 0, (cudaStream_t)stream>>>(
+                x, (uint8_t *)workspace, (int)m, nb, (int)mma_act_pitch(k));
+            rc = launch_status(cudaGetLastError());
+            if (rc != LLOOM_OK) return rc;
+            return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, true);
+        }
+    }
     rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
     if (rc != LLOOM_OK) return rc;
     if (m <= 8) return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream);
