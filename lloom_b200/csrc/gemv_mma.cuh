@@ -12,9 +12,11 @@
 //
 // Frame: persistent CTA per SM over a contiguous row range; a producer warp streams 16-row tiles
 // through a bulk-copy ring, one copy per row so that rows sit `row_pitch` bytes apart (8 banks mod 32:
-// the 64-bit fragment loads of four rows are conflict-free).  Each of the eight consumer warps owns whole
-// tiles (tile i goes to warp i mod 8) and walks the superblocks of its tile in order, so a row's f32
-// sum has one fixed order whatever the batch, the shard or the launch; no CTA-wide barrier after start-up.
+// the 64-bit fragment loads of four rows are conflict-free).  Tile i goes to consumer-warp pair i mod 8; the
+// even warp walks the first half of the tile's superblocks in order, the odd warp the second half, and the
+// even warp adds the two partial sums (first + second), so a row's f32 sum has one fixed order whatever the
+// batch, the shard or the launch.  Sixteen consumer warps, not eight: the per-superblock chain (loads, unpack,
+// MMA, integer scaling) is latency-bound, and four warps per scheduler hide it where two do not.
 #pragma once
 
 #include "gemv.cuh"
@@ -22,7 +24,9 @@
 namespace lloom {
 
 constexpr int kMmaTileRows = 16;
-constexpr int kMmaWarps = 8;
+constexpr int kMmaPairs = 8;              // tiles in flight per CTA
+constexpr int kMmaWarps = 2 * kMmaPairs;  // consumer warps: a pair shares a tile, each warp takes half of its superblocks
+constexpr int kMmaRedBytes = 2 * kMmaPairs * 32 * 16;  // double-buffered partial sums of the odd warps
 
 // Pitch in bytes (a multiple of 16, >= bytes) that is `want_words` 32-bit words modulo the 32 banks.
 __host__ __device__ inline int64_t bank_pitch(int64_t bytes, int want_words) {
@@ -121,13 +125,14 @@ __global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *_
 constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image
 constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
 
-// Dynamic shared memory: [barriers 128 B][per-tile barriers][act planes][stage 0][stage 1]...
+// Dynamic shared memory: [barriers 128 B][per-tile barriers][partial sums 8 KB][act planes][stage 0][stage 1]...
 __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem);
     uint64_t *act_bar = empty + kMaxStages;
     uint64_t *tile_full = reinterpret_cast<uint64_t *>(smem + kMmaBarBytes);
-    uint8_t *act_smem = smem + kMmaBarBytes + p.tile_bar_bytes;
+    float4 *red = reinterpret_cast<float4 *>(smem + kMmaBarBytes + p.tile_bar_bytes);
+    uint8_t *act_smem = smem + kMmaBarBytes + p.tile_bar_bytes + kMmaRedBytes;
     uint8_t *stage0 = act_smem + p.act_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -136,7 +141,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
 
     const int ntiles = (r_end - r_begin + kMmaTileRows - 1) / kMmaTileRows;
     for (int i = threadIdx.x; i < ntiles; i += blockDim.x) mbar_init(&tile_full[i], 1);
-    if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], 1);
+    if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], 2);
     if (threadIdx.x == 32) mbar_init(act_bar, 1);
     fence_mbar_init();
     __syncthreads();
@@ -148,16 +153,17 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     }
 
     constexpr int nthreads = kMmaWarps * 32;
+    bool alive = true;  // after a timed-out wait the warp keeps meeting its partner at the pair barrier but computes nothing
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.act_planes) {
         if (threadIdx.x == 0) {
             mbar_arrive_expect_tx(act_bar, (uint32_t)p.act_bytes);
             bulk_g2s(act_smem, p.act, (uint32_t)p.act_bytes, act_bar);
         }
-        if (!mbar_wait(act_bar, 0)) return;
+        alive = mbar_wait(act_bar, 0);
     } else {
         stage_acts_mma(p, act_smem, threadIdx.x, nthreads);
-        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
     }
 
     const int nb = p.k >> 8;
@@ -173,9 +179,13 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     const float *d0 = dpl + (t0 < p.m ? t0 : 0) * nb, *d1 = dpl + (t1 < p.m ? t1 : 0) * nb;
     const bool min_lane = tig < 2;  // lanes that carry the eight mins / sub-block sums in the min-term MMAs
 
-    for (int it = warp; it < ntiles; it += kMmaWarps) {
+    const int pair = warp >> 1, odd = warp & 1;
+    const int b_mid = (nb + 1) >> 1;
+    const int b_begin = odd ? b_mid : 0, b_end = odd ? nb : b_mid;
+    int round = 0;
+    for (int it = pair; it < ntiles; it += kMmaPairs, ++round) {
         const int s = it % p.stages;
-        if (!mbar_wait(&tile_full[it], 0)) return;
+        alive = alive && mbar_wait(&tile_full[it], 0);
         const int trow = r_begin + it * kMmaTileRows;
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
         const int rows = min(kMmaTileRows, r_end - trow);
@@ -185,7 +195,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
 
         float out[4] = {0.f, 0.f, 0.f, 0.f};  // (row gid, t0), (gid, t1), (gid+8, t0), (gid+8, t1)
 #pragma unroll 2
-        for (int b = 0; b < nb; ++b) {
+        for (int b = b_begin; alive && b < b_end; ++b) {
             const uint4 ha = *reinterpret_cast<const uint4 *>(rowa + (size_t)b * Q4K_BYTES);
             const uint4 hb = *reinterpret_cast<const uint4 *>(rowb + (size_t)b * Q4K_BYTES);
             // 6-bit scales / mins (utils.rs:50-60), four per word, for the two rows
@@ -242,6 +252,18 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
 
+        // odd warp -> shared memory -> even warp: first half + second half
+        float4 *slot = red + ((round & 1) * kMmaPairs + pair) * 32 + lane;
+        if (odd) *slot = make_float4(out[0], out[1], out[2], out[3]);
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+        if (odd || !alive) continue;
+        {
+            const float4 o = *slot;
+            out[0] += o.x;
+            out[1] += o.y;
+            out[2] += o.z;
+            out[3] += o.w;
+        }
         if (t0 < p.m) {
             if (gid < rows) p.y[(int64_t)t0 * p.ldy + trow + gid] = out[0];
             if (gid + 8 < rows) p.y[(int64_t)t0 * p.ldy + trow + gid + 8] = out[2];

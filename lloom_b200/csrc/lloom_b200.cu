@@ -184,7 +184,7 @@ static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t 
     const int64_t bars = gemv_mma_tile_bar_bytes(di, n);
     if (bars > kMmaMaxTiles * 8) return false;
     const int64_t stage = (int64_t)kMmaTileRows * bank_pitch(weight_row_bytes(w_dtype, k), 8);
-    return (int64_t)di.max_smem_optin - kMmaBarBytes - bars - mma_act_bytes(m, k) >= 2 * stage;
+    return (int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - bars - mma_act_bytes(m, k) >= 2 * stage;
 }
 
 // Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
@@ -233,12 +233,12 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.act_planes = act_planes ? 1 : 0;
         p.row_pitch = (int)row_pitch;
         p.tile_bar_bytes = (int)gemv_mma_tile_bar_bytes(di, n);
-        int64_t stages = ((int64_t)di.max_smem_optin - kMmaBarBytes - p.tile_bar_bytes - p.act_bytes) / stage;
+        int64_t stages = ((int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - p.tile_bar_bytes - p.act_bytes) / stage;
         if (stages > kMaxStages) stages = kMaxStages;
         p.n_cwarps = kMmaWarps;
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
-        const int smem = kMmaBarBytes + p.tile_bar_bytes + p.act_bytes + (int)(stages * stage);
+        const int smem = kMmaBarBytes + kMmaRedBytes + p.tile_bar_bytes + p.act_bytes + (int)(stages * stage);
         return launch_status(launch_gemv_mma(p, grid, smem, overlap_on, stream));
     }
     // Tile shapes {consumer warps, rows per lane}, widest first (after an optional pinned shape); the

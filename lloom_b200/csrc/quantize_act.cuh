@@ -93,6 +93,7 @@ __device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
 // Stand-alone Q8_0 quantizer: canonical 34-byte blocks {f16 d; i8 qs[32]}.  A warp covers 8 blocks.
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
                                                             int64_t total_blocks) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV behind may start streaming weights
     const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t blk = gthread >> 2;
     const int part = (int)(gthread & 3);
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restr
 // Stand-alone Q8_K quantizer: canonical 292-byte blocks {f32 d; i8 qs[256]; i16 bsums[16]}.
 __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
                                                            int64_t total_blocks) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV behind may start streaming weights
     const int lane = threadIdx.x & 31;
     const int64_t blk = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (blk >= total_blocks) return;  // whole warp leaves together
