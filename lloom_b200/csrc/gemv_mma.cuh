@@ -12,11 +12,13 @@
 //
 // Frame: persistent CTA per SM over a contiguous row range; a producer warp streams 16-row tiles
 // through a bulk-copy ring, one copy per row so that rows sit `row_pitch` bytes apart (8 banks mod 32:
-// the 64-bit fragment loads of four rows are conflict-free).  Tile i goes to consumer-warp pair i mod 8; the
-// even warp walks the first half of the tile's superblocks in order, the odd warp the second half, and the
-// even warp adds the two partial sums (first + second), so a row's f32 sum has one fixed order whatever the
-// batch, the shard or the launch.  Sixteen consumer warps, not eight: the per-superblock chain (loads, unpack,
-// MMA, integer scaling) is latency-bound, and four warps per scheduler hide it where two do not.
+// the 64-bit fragment loads of four rows are conflict-free).  The
+// sixteen consumer warps work as four teams of four; tile i goes to team i mod 4, warp j of the team walks
+// superblocks j, j+4, ... in order, and the team's first warp adds the four partial sums in warp order, so a
+// row's f32 sum has one fixed order whatever the batch, the shard or the launch.  (Measured on [14336, 4096],
+// 8 rows: teams of 2 / 4 / 8 / 16 warps give 11.9 / 11.1 / 11.2 / 12.5 us per forward.)  Every CTA quantizing
+// all activation rows itself was measured too: 128 blocks x ~200 instructions per CTA cost more than the
+// separate quantizer kernel's launch gap, so batches of 3+ rows keep that kernel.
 #pragma once
 
 #include "gemv.cuh"
@@ -24,9 +26,8 @@
 namespace lloom {
 
 constexpr int kMmaTileRows = 16;
-constexpr int kMmaPairs = 8;              // tiles in flight per CTA
-constexpr int kMmaWarps = 2 * kMmaPairs;  // consumer warps: a pair shares a tile, each warp takes half of its superblocks
-constexpr int kMmaRedBytes = 2 * kMmaPairs * 32 * 16;  // double-buffered partial sums of the odd warps
+constexpr int kMmaWarps = 16;  // consumer warps; SPLIT of them share a tile, warp j of a team takes superblocks j, j+SPLIT, ...
+constexpr int kMmaRedBytes = 2 * kMmaWarps * 32 * 16;  // double-buffered partial sums, one float4 per lane
 
 // Pitch in bytes (a multiple of 16, >= bytes) that is `want_words` 32-bit words modulo the 32 banks.
 __host__ __device__ inline int64_t bank_pitch(int64_t bytes, int want_words) {
@@ -95,16 +96,11 @@ __device__ __forceinline__ void stage_acts_mma(const GemvParams &p, uint8_t *act
     }
 }
 
-// f32 activations -> the plane image in global memory (the same bytes stage_acts_mma leaves in shared
-// memory), one warp per 256-element block; the GEMV then fetches the image with one bulk copy.
-// Block arithmetic: q8k_quantize_warp, shared with the canonical quantizer.
-__global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
-                                                                  int m, int nb, int act_pitch) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV may start streaming weights
-    const int lane = threadIdx.x & 31;
-    const int blk = (int)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
-    if (blk >= m * nb) return;  // whole warp leaves together
-    const int t = blk / nb, b = blk - t * nb;
+// One warp quantizes 256-element block (t, b) of the f32 activations into the three planes at `out` (global
+// or shared memory).  Block arithmetic: q8k_quantize_warp, shared with the canonical quantizer.
+__device__ __forceinline__ void q8k_block_to_planes(const float *__restrict__ x, uint8_t *out, int t, int b, int m, int nb,
+                                                    int act_pitch, int lane) {
+    const int blk = t * nb + b;
     float v[8];
     load8(x + (int64_t)blk * QK_K + lane * 8, v);
     uint32_t q_lo, q_hi;
@@ -122,10 +118,22 @@ __global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *_
     if (lane == 0) reinterpret_cast<float *>(out + (size_t)m * act_pitch + (size_t)m * nb * 16)[blk] = d;
 }
 
+// f32 activations -> the plane image in global memory (the same bytes stage_acts_mma leaves in shared
+// memory), one warp per 256-element block; the GEMV then fetches the image with one bulk copy.
+__global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                                  int m, int nb, int act_pitch) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV may start streaming weights
+    const int lane = threadIdx.x & 31;
+    const int blk = (int)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    if (blk >= m * nb) return;  // whole warp leaves together
+    q8k_block_to_planes(x, out, blk / nb, blk % nb, m, nb, act_pitch, lane);
+}
+
 constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image
 constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
 
 // Dynamic shared memory: [barriers 128 B][per-tile barriers][partial sums 8 KB][act planes][stage 0][stage 1]...
+template <int SPLIT>
 __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem);
@@ -136,12 +144,20 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     uint8_t *stage0 = act_smem + p.act_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r_begin = (int)(((int64_t)blockIdx.x * p.n) / gridDim.x);
-    const int r_end = (int)(((int64_t)(blockIdx.x + 1) * p.n) / gridDim.x);
+    // whole 16-row tiles per CTA (a ragged split would leave most CTAs a last tile of a row or two that costs a
+    // full tile's latency)
+    const int total_tiles = (p.n + kMmaTileRows - 1) / kMmaTileRows;
+    const int r_begin = (int)(((int64_t)blockIdx.x * total_tiles) / gridDim.x) * kMmaTileRows;
+    const int r_end = min(p.n, (int)(((int64_t)(blockIdx.x + 1) * total_tiles) / gridDim.x) * kMmaTileRows);
 
+#ifdef LLOOM_TRACE
+    if (threadIdx.x == 0) s_trace_slot = blockIdx.x < 160 ? g_trace_cnt[blockIdx.x]++ : 0;
+    __syncthreads();
+#endif
+    if (threadIdx.x == 0) LLOOM_TRACE_MARK(0);
     const int ntiles = (r_end - r_begin + kMmaTileRows - 1) / kMmaTileRows;
     for (int i = threadIdx.x; i < ntiles; i += blockDim.x) mbar_init(&tile_full[i], 1);
-    if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], 2);
+    if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], SPLIT);
     if (threadIdx.x == 32) mbar_init(act_bar, 1);
     fence_mbar_init();
     __syncthreads();
@@ -149,12 +165,14 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
 
     if (warp == kMmaWarps) {
         gemv_producer_rows(p, tile_full, empty, stage0, kMmaTileRows, p.row_pitch, r_begin, r_end, lane);
+        LLOOM_TRACE_MARK(8);
         return;
     }
 
     constexpr int nthreads = kMmaWarps * 32;
     bool alive = true;  // after a timed-out wait the warp keeps meeting its partner at the pair barrier but computes nothing
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) LLOOM_TRACE_MARK(14);
     if (p.act_planes) {
         if (threadIdx.x == 0) {
             mbar_arrive_expect_tx(act_bar, (uint32_t)p.act_bytes);
@@ -166,6 +184,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
         asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
     }
 
+    if (threadIdx.x == 0) LLOOM_TRACE_MARK(1);
     const int nb = p.k >> 8;
     const int gid = lane >> 2, tig = lane & 3;  // MMA fragment coordinates
     // B fragments come from activation row gid (rows past m read row 0; their columns are never stored)
@@ -179,13 +198,13 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     const float *d0 = dpl + (t0 < p.m ? t0 : 0) * nb, *d1 = dpl + (t1 < p.m ? t1 : 0) * nb;
     const bool min_lane = tig < 2;  // lanes that carry the eight mins / sub-block sums in the min-term MMAs
 
-    const int pair = warp >> 1, odd = warp & 1;
-    const int b_mid = (nb + 1) >> 1;
-    const int b_begin = odd ? b_mid : 0, b_end = odd ? nb : b_mid;
+    constexpr int kTeams = kMmaWarps / SPLIT;
+    const int team = warp / SPLIT, member = warp % SPLIT;
     int round = 0;
-    for (int it = pair; it < ntiles; it += kMmaPairs, ++round) {
+    for (int it = team; it < ntiles; it += kTeams, ++round) {
         const int s = it % p.stages;
         alive = alive && mbar_wait(&tile_full[it], 0);
+        if (member == 0 && (it == 0 || it == 5 || it == 6)) LLOOM_TRACE_MARK(it == 0 ? 2 : it == 5 ? 4 : 6);
         const int trow = r_begin + it * kMmaTileRows;
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
         const int rows = min(kMmaTileRows, r_end - trow);
@@ -195,7 +214,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
 
         float out[4] = {0.f, 0.f, 0.f, 0.f};  // (row gid, t0), (gid, t1), (gid+8, t0), (gid+8, t1)
 #pragma unroll 2
-        for (int b = b_begin; alive && b < b_end; ++b) {
+        for (int b = member; alive && b < nb; b += SPLIT) {
             const uint4 ha = *reinterpret_cast<const uint4 *>(rowa + (size_t)b * Q4K_BYTES);
             const uint4 hb = *reinterpret_cast<const uint4 *>(rowb + (size_t)b * Q4K_BYTES);
             // 6-bit scales / mins (utils.rs:50-60), four per word, for the two rows
@@ -252,13 +271,14 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
 
-        // odd warp -> shared memory -> even warp: first half + second half
-        float4 *slot = red + ((round & 1) * kMmaPairs + pair) * 32 + lane;
-        if (odd) *slot = make_float4(out[0], out[1], out[2], out[3]);
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
-        if (odd || !alive) continue;
-        {
-            const float4 o = *slot;
+        // partial sums of the team meet in shared memory; its first warp adds them in member order
+        float4 *slot = red + ((round & 1) * kMmaWarps + team * SPLIT) * 32 + lane;
+        if (member != 0) slot[member * 32] = make_float4(out[0], out[1], out[2], out[3]);
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "n"(SPLIT * 32) : "memory");
+        if (member != 0 || !alive) continue;
+#pragma unroll
+        for (int j = 1; j < SPLIT; ++j) {
+            const float4 o = slot[j * 32];
             out[0] += o.x;
             out[1] += o.y;
             out[2] += o.z;
@@ -272,6 +292,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             if (gid < rows) p.y[(int64_t)t1 * p.ldy + trow + gid] = out[1];
             if (gid + 8 < rows) p.y[(int64_t)t1 * p.ldy + trow + gid + 8] = out[3];
         }
+        if (it == 0 || it == 5 || it == 6) LLOOM_TRACE_MARK(it == 0 ? 3 : it == 5 ? 5 : 7);
     }
 }
 

@@ -138,8 +138,9 @@ static bool gemv_shape_override(int &cw, int &rw) {
     return cached == 1;
 }
 
-static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_mma_q4k_kernel;
+template <int SPLIT>
+static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    auto kern = gemv_mma_q4k_kernel<SPLIT>;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -161,6 +162,10 @@ static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    return launch_gemv_mma_inst<4>(p, grid, smem, overlap, stream);
+}
+
 // Development knob: LLOOM_GEMV_MMA=0 keeps 3 <= m <= 8 on the dp4a kernel.
 static bool gemv_mma_enabled() {
     static int cached = -1;
@@ -174,9 +179,9 @@ static bool gemv_mma_enabled() {
 // Whether the tensor-core GEMV takes this shape: Q4_K, 3..8 activation rows, two 16-row stages fit beside the
 // activation planes.
 static int64_t gemv_mma_tile_bar_bytes(const DeviceInfo &di, int64_t n) {
-    const int64_t grid = n < di.sm_count ? n : di.sm_count;
-    const int64_t tiles = ((n + grid - 1) / grid + kMmaTileRows - 1) / kMmaTileRows;
-    return round16(tiles * 8);
+    const int64_t total = (n + kMmaTileRows - 1) / kMmaTileRows;
+    const int64_t grid = total < di.sm_count ? total : di.sm_count;
+    return round16((total + grid - 1) / grid * 8);
 }
 
 static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
@@ -239,6 +244,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
         const int smem = kMmaBarBytes + kMmaRedBytes + p.tile_bar_bytes + p.act_bytes + (int)(stages * stage);
+        const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
+        if (grid > total_tiles) grid = (int)total_tiles;
         return launch_status(launch_gemv_mma(p, grid, smem, overlap_on, stream));
     }
     // Tile shapes {consumer warps, rows per lane}, widest first (after an optional pinned shape); the
