@@ -65,7 +65,8 @@ struct GemmScratch {
 };
 __host__ __device__ inline GemmScratch gemm_scratch_layout(int64_t m, int64_t n, int64_t k) {
     GemmScratch s;
-    const int64_t mt = gemm_m_tiles(m), nt = (n + kGemmBN - 1) / kGemmBN, nb = k / 256;
+    // weight images cover an even number of n-tiles (the CTA-pair kernel works on two at a time; rows past n are zero)
+    const int64_t mt = gemm_m_tiles(m), nt = ((n + kGemmBN - 1) / kGemmBN + 1) / 2 * 2, nb = k / 256;
     s.bimg = 0;
     s.minb = s.bimg + mt * (k / 64) * kGemmAtomBytes;
     s.dat = s.minb + mt * nb * kGemmMinBytes;
@@ -512,6 +513,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     }
 }
 
+cudaError_t gemm_launch_pair_kernel(const GemmParams &p, int max_smem, cudaStream_t stream, bool &launched);
+
 inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, int64_t m, int64_t n, int64_t k,
                        int64_t ldy, void *workspace, int /*sm_count*/, int max_smem, cudaStream_t stream, bool &handled,
                        int &cuda_err) {
@@ -526,7 +529,7 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
         configured = true;
     }
     const int64_t mt = gemm_m_tiles(m), nb = k / 256;
-    const int64_t ntiles = (n + kGemmBN - 1) / kGemmBN;
+    const int64_t ntiles = (n + kGemmBN - 1) / kGemmBN, ntiles_even = (ntiles + 1) / 2 * 2;
     gemm_prep_kernel<<<(unsigned)(mt * nb * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)n, (int)k, (uint8_t *)workspace);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
@@ -537,7 +540,7 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
         if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
         expand_configured = true;
     }
-    gemm_expand_kernel<<<(unsigned)(ntiles * nb), 128, kExpandSmem, stream>>>((const uint8_t *)w, (int)m, (int)n, (int)k, (uint8_t *)workspace);
+    gemm_expand_kernel<<<(unsigned)(ntiles_even * nb), 128, kExpandSmem, stream>>>((const uint8_t *)w, (int)m, (int)n, (int)k, (uint8_t *)workspace);
     e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
     GemmParams p;
@@ -551,6 +554,10 @@ inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, in
     p.k = (int)k;
     p.n_tiles = (int)ntiles;
     p.m_tiles = (int)mt;
+    bool launched = false;
+    e = gemm_launch_pair_kernel(p, max_smem, stream, launched);  // CTA-pair kernel (gemm_q4k_2sm.cuh), opt-in
+    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
+    if (launched) return LLOOM_OK;
     gemm_q4k_kernel<<<(unsigned)(p.n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }

@@ -2,7 +2,7 @@
 // headers included below.  No entry point allocates, frees or synchronises.
 #include "common.cuh"
 #include "dequant.cuh"
-#include "gemm_q4k.cuh"
+#include "gemm_q4k_2sm.cuh"
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "quantize_act.cuh"
@@ -504,6 +504,9 @@ int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float
 int lloom_b200_read_trace(unsigned long long *out, unsigned int *cnt) {  // development build only
     cudaMemcpyFromSymbol(cnt, g_trace_cnt, sizeof(g_trace_cnt));
     return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+}
+int lloom_b200_read_gemm2_trace(long long *out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, g_gemm2_trace, sizeof(g_gemm2_trace));
 }
 
 #endif

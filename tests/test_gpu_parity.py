@@ -289,3 +289,36 @@ def test_fwd_shape_rules_and_errors(dev, oracle):
     assert yh.dtype == torch.float16
     ref = mm.forward(xt.half().float()).half()
     assert yh.cpu().numpy().tobytes() == ref.cpu().numpy().tobytes()
+
+
+def test_gemm_q4k_cta_pair_kernel(oracle):
+    """The opt-in CTA-pair (tcgen05 cta_group::2) GEMM kernel against the oracle, in a process of its own (the
+    switch is read once per process): ragged tiles, an odd number of 128-row weight tiles, 1..16 superblocks."""
+    import subprocess
+    import sys
+
+    code = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, '.')
+from oracle import oracle as O
+import lloom_b200 as lb
+from lloom_b200 import quantized as Q
+dev = torch.device('cuda:0')
+for (n, k, m) in [(128, 256, 128), (130, 512, 70), (384, 2048, 96), (1000, 4096, 200)]:
+    rng = np.random.default_rng(n + k + m)
+    w = rng.standard_normal((n, k)).astype(np.float32) * np.float32(0.02)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    wq = Q.quantize_weights_host(w, 12)
+    qt = lb.QTensor.from_data(wq, 12, (n, k), dev)
+    got = lb.QMatMul.from_qtensor(qt).forward(torch.from_numpy(x).to(dev)).cpu().numpy()
+    assert Q.device_status() == 0
+    ref = O.matmul(12, x, wq, n, nthreads=8); A = O.matmul_absum(12, x, wq, n, nthreads=8)
+    err = np.abs(got.astype(np.float64) - ref)
+    assert (err <= 1e-5 * A + 1e-30).all(), (n, k, m, float((err / np.maximum(A, 1e-30)).max()))
+print("pair-ok")
+"""
+    import os
+    env = dict(os.environ, LLOOM_GEMM_2SM="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "pair-ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
