@@ -166,7 +166,7 @@ static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool
     return launch_gemv_mma_inst<4>(p, grid, smem, overlap, stream);
 }
 
-// Development knob: LLOOM_GEMV_MMA=0 keeps 3 <= m <= 8 on the dp4a kernel.
+// Development knob: LLOOM_GEMV_MMA=0 keeps 2 <= m <= 8 on the dp4a kernel.
 static bool gemv_mma_enabled() {
     static int cached = -1;
     if (cached < 0) {
@@ -176,7 +176,7 @@ static bool gemv_mma_enabled() {
     return cached == 1;
 }
 
-// Whether the tensor-core GEMV takes this shape: Q4_K, 3..8 activation rows, two 16-row stages fit beside the
+// Whether the tensor-core GEMV takes this shape: Q4_K, 2..8 activation rows, two 16-row stages fit beside the
 // activation planes.
 static int64_t gemv_mma_tile_bar_bytes(const DeviceInfo &di, int64_t n) {
     const int64_t total = (n + kMmaTileRows - 1) / kMmaTileRows;
@@ -185,7 +185,7 @@ static int64_t gemv_mma_tile_bar_bytes(const DeviceInfo &di, int64_t n) {
 }
 
 static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
-    if (w_dtype != LLOOM_Q4_K || m < 3 || m > 8 || !gemv_mma_enabled()) return false;
+    if (w_dtype != LLOOM_Q4_K || m < 2 || m > 8 || !gemv_mma_enabled()) return false;
     const int64_t bars = gemv_mma_tile_bar_bytes(di, n);
     if (bars > kMmaMaxTiles * 8) return false;
     const int64_t stage = (int64_t)kMmaTileRows * bank_pitch(weight_row_bytes(w_dtype, k), 8);
@@ -230,7 +230,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     if ((int64_t)grid > n) grid = (int)n;
     const bool overlap_on = g_launch_overlap.load(std::memory_order_relaxed) != 0;
     // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
-    if (gemv_mma_fits(di, w_dtype, m, n, k)) {
+    if (x == nullptr && gemv_mma_fits(di, w_dtype, m, n, k)) {
         const int64_t row_pitch = bank_pitch(p.row_bytes, 8);
         const int64_t stage = (int64_t)kMmaTileRows * row_pitch;
         p.act_bytes = (int)mma_act_bytes(m, k);
@@ -455,16 +455,18 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
     if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
     if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
-    // single-token decode: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
-    // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
-    if (m <= 2) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
     if (m <= 8) {
-        // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
-        // codes, scales and sums as the canonical blocks, laid out for its fragment loads)
         DeviceInfo di;
         rc = device_info(di);
         if (rc != LLOOM_OK) return rc;
-        if (gemv_mma_fits(di, w_dtype, m, n, k) && mma_act_bytes(m, k) <= need) {
+        const bool mma = gemv_mma_fits(di, w_dtype, m, n, k);
+        // single-token decode (and two rows of Q8_0 / Q6_K): one launch, the activation quantizer is the GEMV's
+        // prologue (the workspace stays unused).  From three rows on, every CTA re-quantizing all rows costs
+        // more than one small kernel does.
+        if (m <= 2 && !mma) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
+        // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
+        // codes, scales and sums as the canonical blocks, laid out for its fragment loads)
+        if (mma && mma_act_bytes(m, k) <= need) {
             const int nb = (int)(k / QK_K);
             quantize_q8k_planes_kernel<<<(unsigned)ceil_div64(m * nb * 32, 256), 256, 0, (cudaStream_t)stream>>>(
                 x, (uint8_t *)workspace, (int)m, nb, (int)mma_act_pitch(k));
