@@ -304,7 +304,7 @@ def run_gpu(args):
     achieved = WEIGHT_BYTES / (ms_gemv * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "traffic": GEMV_DRAM_TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}",
-                "kernel": "gemv_kernel<ItemQ4K<1>,1,RW>", "algorithmic_bytes_per_launch": WEIGHT_BYTES,
+                "kernel": "gemv_kernel<FmtQ4K, M=1, RW=1, CW=8>", "algorithmic_bytes_per_launch": WEIGHT_BYTES,
                 "us_per_launch": round(ms_gemv * 1e3, 3)}
 
     # prefill leg (the metric's second half): whole QMatMul::forward at M = 512 and 2048 on the C4 matrix
@@ -340,12 +340,22 @@ def run_gpu(args):
     y_dev = torch.empty(POOL, 1, N, dtype=torch.float32, device=dev)
     x_dev = torch.empty(1, K, dtype=torch.float32, device=dev)
 
-    def e2e_step():
+    # One step = pinned host activations -> device, 16 forwards through the public API, 16 outputs -> pinned host.
+    # The step is captured once in a CUDA graph (copies included) and replayed, the way a decode loop would run
+    # it: launched call by call from Python the step measures the interpreter (about 12 us per forward), not
+    # the library.
+    def e2e_body():
         x_dev.copy_(xs_host[1], non_blocking=True)
         for i, mm in enumerate(mats):
             mm.qtensor.storage.fwd((N, K), x_dev, out=y_dev[i])
         y_host.copy_(y_dev, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+
+    g_e2e = capture(e2e_body)
+
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            g_e2e.replay()
+        stream.synchronize()
 
     for _ in range(3):
         e2e_step()
@@ -376,7 +386,8 @@ def run_gpu(args):
                    "multi_gpu": "independent matrices per rank, no collective" if multi else "single GPU"},
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": 4 * K,
-                "d2h_bytes_per_step": 4 * POOL * N, "ms_per_step": round(e2e_ms, 4)},
+                "d2h_bytes_per_step": 4 * POOL * N, "ms_per_step": round(e2e_ms, 4),
+                "how": "pinned H2D + 16 QCudaStorage.fwd + pinned D2H, captured in one CUDA graph, host-timed per replay"},
         "gpu_launches": steps * POOL,  # one fused quantize+GEMV launch per matrix
         "roofline": roofline,
         "sweep_GBps": sweep,
@@ -432,30 +443,57 @@ def run_lm_head(args):
     x = torch.from_numpy(np.random.default_rng(5).standard_normal((1, k)).astype(np.float32)).to(dev)
     steps, warmup = args.steps, max(args.warmup, 3)
 
-    def step():
+    from lloom_b200.sharded import ShardedQMatMul
+
+    def step_nccl():
         out = None
         for q in pool:
             y_local = q.fwd(x)
             out = gather_rows(y_local, plan) if world > 1 else y_local
         return out
 
-    for _ in range(warmup):
-        step()
-    torch.cuda.synchronize()
+    def time_steps(step):
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([t_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_ms = float(t.item())
+        return t_ms
+
+    ms_nccl = time_steps(step_nccl)
+    ms, gather, fused_us = ms_nccl, ("NCCL all-gather" if world > 1 else "none (one GPU)"), None
     if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        # the same forwards with the gather fused into the GEMV (peer stores + one barrier kernel per forward)
+        fused = [ShardedQMatMul(None, plan, None, local=lb.QMatMul.from_qtensor(q)) for q in pool]
+        if all(f.enable_fused_gather(1) for f in fused):
+            def step_fused():
+                out = None
+                for f in fused:
+                    out = f.forward(x)
+                return out
+
+            ms_fused = time_steps(step_fused)
+            fused_us = ms_fused / steps / copies * 1e3
+            if Q.device_status() != 0:
+                raise RuntimeError("device status after the fused gather")
+            if ms_fused < ms_nccl:
+                ms, gather = ms_fused, "fused into the GEMV (peer stores over NVLink + barrier kernel)"
+            torch.cuda.synchronize()
+            dist.barrier()
+            for f in fused:
+                f.close()
     per_matmul_us = ms / steps / copies * 1e3
     value = n_total * row_bytes / (per_matmul_us * 1e-6) / 1e9
     if rank == 0:
@@ -463,7 +501,9 @@ def run_lm_head(args):
             "metric": "q6k_lm_head_gemv_weight_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-            "config": {"workload": "C3 Q6_K lm_head GEMV [128256x4096], M=1, rows sharded over ranks + NCCL all-gather",
+            "config": {"workload": "C3 Q6_K lm_head GEMV [128256x4096], M=1, rows sharded over ranks, logits gathered on every rank",
+                       "gather": gather, "us_per_sharded_matmul_nccl": round(ms_nccl / steps / copies * 1e3, 2),
+                       "us_per_sharded_matmul_fused": None if fused_us is None else round(fused_us, 2),
                        "copies_per_rank": copies, "us_per_sharded_matmul": round(per_matmul_us, 2),
                        "per_gpu_GBps": round(value / world, 1), "timing": "CUDA events, eager launches (no graph)"},
             "gpu_launches": steps * copies}), flush=True)

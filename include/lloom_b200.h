@@ -142,6 +142,35 @@ int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, voi
 int lloom_b200_get_rows(int dtype, const void *blocks, int64_t rows, int64_t hidden, const uint32_t *ids,
                         int64_t n_ids, float *out, void *stream);
 
+/* ---- Row-sharded forward with the all-gather fused into the GEMV (one node, up to 8 GPUs) ----
+ *
+ * The reference shards nothing on this path; the sharded layer here (rank g owns rows [g*ceil(n/G), ...), the
+ * logits are concatenated) normally ends in an NCCL all-gather.  This entry replaces that collective for decode
+ * batches: the GEMV stores every output value straight into the output buffer of each GPU (peer memory over
+ * NVLink), so the exchange overlaps the computation and costs no extra launch except the barrier below.
+ *
+ *   y_peers   host array of n_peers device pointers: the [m][ldy] f32 output buffer of every GPU of the group,
+ *             own buffer included, all mapped into this process (lloom_b200_peer_open); index = rank
+ *   col0      first output column of this shard (its first weight row in the unsharded matrix)
+ *   m <= 8; other arguments as lloom_b200_qmatmul_fwd.
+ * After it, lloom_b200_peer_barrier on the same stream; the gathered rows are complete on this GPU when that
+ * kernel has finished.  A buffer may be written again only after every GPU has finished reading it (alternate
+ * two buffers, as the Python layer does). */
+int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard, int64_t k,
+                                  int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, void *workspace,
+                                  int64_t workspace_bytes, void *stream);
+/* flag_peers: host array of n_peers device pointers, the flag array (LLOOM_B200_PEER_FLAG_WORDS u32, zeroed once)
+ * of every GPU, mapped into this process.  Bounded wait: LLOOM_ERR_TIMEOUT shows in lloom_b200_device_status. */
+#define LLOOM_B200_PEER_FLAG_WORDS 16
+int lloom_b200_peer_barrier(int rank, int n_peers, unsigned int *const *flag_peers, void *stream);
+/* Set-up helpers (not on the forward path; these do allocate / synchronise): a zeroed device buffer other processes
+ * of the node can map, its 64-byte CUDA IPC handle, mapping a peer's handle, and the matching releases. */
+int lloom_b200_peer_alloc(int64_t bytes, void **ptr);
+int lloom_b200_peer_free(void *ptr);
+int lloom_b200_peer_export(const void *ptr, unsigned char *handle64);
+int lloom_b200_peer_open(const unsigned char *handle64, void **ptr);
+int lloom_b200_peer_close(void *ptr);
+
 #ifdef __cplusplus
 }
 #endif

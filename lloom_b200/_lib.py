@@ -31,6 +31,13 @@ SYMBOLS = [
     ("lloom_b200_gemm", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd_static", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd_gather", _int, [_int, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(_vp), _int, _vp, _i64, _vp]),
+    ("lloom_b200_peer_barrier", _int, [_int, _int, C.POINTER(_vp), _vp]),
+    ("lloom_b200_peer_alloc", _int, [_i64, C.POINTER(_vp)]),
+    ("lloom_b200_peer_free", _int, [_vp]),
+    ("lloom_b200_peer_export", _int, [_vp, C.c_char_p]),
+    ("lloom_b200_peer_open", _int, [C.c_char_p, C.POINTER(_vp)]),
+    ("lloom_b200_peer_close", _int, [_vp]),
     ("lloom_b200_dequantize", _int, [_int, _vp, _i64, _vp, _int, _vp]),
     ("lloom_b200_get_rows", _int, [_int, _vp, _i64, _i64, _vp, _i64, _vp, _vp]),
     # include/lloom_b200_host.h: C view of the C++ host layer

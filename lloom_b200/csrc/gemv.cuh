@@ -287,6 +287,8 @@ struct FmtQ8_0 {
     }
 };
 
+constexpr int kMaxPeers = 8;  // GPUs of one node
+
 struct GemvParams {
     const uint8_t *w;    // canonical blocks, 16-byte aligned
     const uint8_t *act;  // canonical activation blocks [m][k/block] (used when x == nullptr)
@@ -306,7 +308,21 @@ struct GemvParams {
     int act_pitch;     // tensor-core kernel only: bytes between activation rows of the code plane
     int act_planes;    // tensor-core kernel only: `act` already holds the plane image (else canonical blocks)
     int tile_bar_bytes;  // tensor-core kernel only: bytes of the per-tile barrier array (multiple of 16)
+    // Fused gather: when n_peers > 0 every output value goes to the same place in each of these buffers (this GPU's
+    // own and its peers', mapped into this process) instead of `y`, so the row-sharded forward needs no separate
+    // all-gather: the stores cross NVLink while the rest of the rows are still being computed.
+    int n_peers;
+    float *y_peer[kMaxPeers];
 };
+
+// One output value to its destination(s).
+__device__ __forceinline__ void store_out(const GemvParams &p, int64_t idx, float v) {
+    if (p.n_peers == 0) {
+        p.y[idx] = v;
+    } else {
+        for (int g = 0; g < p.n_peers; ++g) p.y_peer[g][idx] = v;
+    }
+}
 
 constexpr int kMaxStages = 8;
 
@@ -633,7 +649,7 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
             for (int r = 0; r < RW; ++r)
                 if (valid[r]) {
 #pragma unroll
-                    for (int m = 0; m < M; ++m) p.y[(int64_t)m * p.ldy + row0 + r] = out[r][m];
+                    for (int m = 0; m < M; ++m) store_out(p, (int64_t)m * p.ldy + row0 + r, out[r][m]);
                 }
         }
     }

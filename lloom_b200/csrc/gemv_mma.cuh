@@ -286,12 +286,12 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             out[3] += o.w;
         }
         if (t0 < p.m) {
-            if (gid < rows) p.y[(int64_t)t0 * p.ldy + trow + gid] = out[0];
-            if (gid + 8 < rows) p.y[(int64_t)t0 * p.ldy + trow + gid + 8] = out[2];
+            if (gid < rows) store_out(p, (int64_t)t0 * p.ldy + trow + gid, out[0]);
+            if (gid + 8 < rows) store_out(p, (int64_t)t0 * p.ldy + trow + gid + 8, out[2]);
         }
         if (t1 < p.m) {
-            if (gid < rows) p.y[(int64_t)t1 * p.ldy + trow + gid] = out[1];
-            if (gid + 8 < rows) p.y[(int64_t)t1 * p.ldy + trow + gid + 8] = out[3];
+            if (gid < rows) store_out(p, (int64_t)t1 * p.ldy + trow + gid, out[1]);
+            if (gid + 8 < rows) store_out(p, (int64_t)t1 * p.ldy + trow + gid + 8, out[3]);
         }
         if (it == 0 || it == 5 || it == 6) LLOOM_TRACE_MARK(it == 0 ? 3 : it == 5 ? 5 : 7);
     }

@@ -10,6 +10,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace lloom {
@@ -194,8 +195,18 @@ static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t 
 
 // Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
 // quantized in the kernel's prologue) is non-null.
+struct PeerFlags {  // one flag array per GPU: kMaxPeers slots written by the peers + this GPU's call counter
+    unsigned int *f[kMaxPeers];
+};
+
+struct PeerOut {  // fused gather: output buffers of all GPUs (own included), already offset to this shard's column
+    int n = 0;
+    float *y[kMaxPeers] = {};
+};
+
 static int gemv_launch(int w_dtype, const void *w, const void *act, const float *x, float *y, int64_t m, int64_t n,
-                       int64_t k, int64_t ldy, cudaStream_t stream, bool act_planes = false) {
+                       int64_t k, int64_t ldy, cudaStream_t stream, bool act_planes = false,
+                       const PeerOut *peers = nullptr) {
     DeviceInfo di;
     int rc = device_info(di);
     if (rc != LLOOM_OK) return rc;
@@ -217,6 +228,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.act_pitch = 0;
     p.act_planes = 0;
     p.tile_bar_bytes = 0;
+    p.n_peers = peers ? peers->n : 0;
+    for (int g = 0; g < kMaxPeers; ++g) p.y_peer[g] = (peers && g < peers->n) ? peers->y[g] : nullptr;
     // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
     const int64_t units = k / (w_dtype == LLOOM_Q8_0 ? 64 : 256);
     int lpr_log2 = 0;
@@ -317,6 +330,37 @@ static int static_scratch_ptr(void **out) {
     *out = cache[dev];
     return LLOOM_OK;
 }
+
+// Decode forward (m <= 8) after argument checks: quantizer + GEMV, outputs to `y` or to the peers' buffers.
+static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n, int64_t k,
+                      int64_t ldy, void *workspace, int64_t need, void *stream, const PeerOut *peers) {
+    int rc;
+    {
+        DeviceInfo di;
+        rc = device_info(di);
+        if (rc != LLOOM_OK) return rc;
+        const bool mma = gemv_mma_fits(di, w_dtype, m, n, k);
+        // single-token decode (and two rows of Q8_0 / Q6_K): one launch, the activation quantizer is the GEMV's
+        // prologue (the workspace stays unused).  From three rows on, every CTA re-quantizing all rows costs
+        // more than one small kernel does.
+        if (m <= 2 && !mma)
+            return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream, false, peers);
+        // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
+        // codes, scales and sums as the canonical blocks, laid out for its fragment loads)
+        if (mma && mma_act_bytes(m, k) <= need) {
+            const int nb = (int)(k / QK_K);
+            quantize_q8k_planes_kernel<<<(unsigned)ceil_div64(m * nb * 32, 256), 256, 0, (cudaStream_t)stream>>>(
+                x, (uint8_t *)workspace, (int)m, nb, (int)mma_act_pitch(k));
+            rc = launch_status(cudaGetLastError());
+            if (rc != LLOOM_OK) return rc;
+            return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, true, peers);
+        }
+    }
+    rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
+    if (rc != LLOOM_OK) return rc;
+    return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, false, peers);
+}
+
 
 }  // namespace lloom
 
@@ -455,33 +499,102 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
     if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
     if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
-    if (m <= 8) {
-        DeviceInfo di;
-        rc = device_info(di);
-        if (rc != LLOOM_OK) return rc;
-        const bool mma = gemv_mma_fits(di, w_dtype, m, n, k);
-        // single-token decode (and two rows of Q8_0 / Q6_K): one launch, the activation quantizer is the GEMV's
-        // prologue (the workspace stays unused).  From three rows on, every CTA re-quantizing all rows costs
-        // more than one small kernel does.
-        if (m <= 2 && !mma) return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream);
-        // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
-        // codes, scales and sums as the canonical blocks, laid out for its fragment loads)
-        if (mma && mma_act_bytes(m, k) <= need) {
-            const int nb = (int)(k / QK_K);
-            quantize_q8k_planes_kernel<<<(unsigned)ceil_div64(m * nb * 32, 256), 256, 0, (cudaStream_t)stream>>>(
-                x, (uint8_t *)workspace, (int)m, nb, (int)mma_act_pitch(k));
-            rc = launch_status(cudaGetLastError());
-            if (rc != LLOOM_OK) return rc;
-            return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, true);
-        }
-    }
+    if (m <= 8) return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, nullptr);
     rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
     if (rc != LLOOM_OK) return rc;
-    if (m <= 8) return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream);
     const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
     return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
                            workspace_bytes - act, stream);
 }
+
+int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard, int64_t k,
+                                  int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, void *workspace,
+                                  int64_t workspace_bytes, void *stream) {
+    int rc = check_common(w_dtype, m, n_shard, k);
+    if (rc != LLOOM_OK) return rc;
+    if (m > 8 || n_peers < 1 || n_peers > kMaxPeers || col0 < 0 || ldy < col0 + n_shard) return LLOOM_ERR_SHAPE;
+    if (!w_shard || !x || !y_peers) return LLOOM_ERR_NULL;
+    const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n_shard, k);
+    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(workspace, 256) || !aligned(w_shard, 16) || !aligned(x, 16)) return LLOOM_ERR_ALIGN;
+    PeerOut peers;
+    peers.n = n_peers;
+    for (int g = 0; g < n_peers; ++g) {
+        if (!y_peers[g]) return LLOOM_ERR_NULL;
+        if (!aligned(y_peers[g], 4)) return LLOOM_ERR_ALIGN;
+        peers.y[g] = y_peers[g] + col0;
+    }
+    return decode_fwd(w_dtype, w_shard, x, peers.y[0], m, n_shard, k, ldy, workspace, need, stream, &peers);
+}
+
+// Cross-GPU barrier after a fused gather: one small kernel per GPU.  Each GPU bumps its own epoch, publishes it in
+// slot [rank] of every GPU's flag array (system-scope release: the gather's stores, finished with the previous
+// kernel on this stream, are visible before it) and waits until all slots of its own array have reached the
+// epoch.  The wait is bounded in time; on a time-out the status word is set and the kernel returns.
+__global__ void peer_barrier_kernel(int rank, int n_peers, PeerFlags flags) {
+    __shared__ unsigned int s_epoch;
+    unsigned int *mine = flags.f[rank];
+    if (threadIdx.x == 0) {
+        s_epoch = mine[kMaxPeers] + 1;  // slot kMaxPeers: this GPU's call counter
+        mine[kMaxPeers] = s_epoch;
+        __threadfence_system();
+    }
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int g = threadIdx.x;
+    if (g >= n_peers) return;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.f[g] + rank), "r"(epoch) : "memory");
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; i < kMaxSpins; ++i) {
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + g) : "memory");
+        if ((int)(seen - epoch) >= 0) return;
+        if ((i & 63) == 63) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kMaxWaitNs) break;
+        }
+        __nanosleep(100);
+    }
+    atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
+}
+
+int lloom_b200_peer_barrier(int rank, int n_peers, unsigned int *const *flag_peers, void *stream) {
+    if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return LLOOM_ERR_SHAPE;
+    if (!flag_peers) return LLOOM_ERR_NULL;
+    PeerFlags flags;
+    for (int g = 0; g < kMaxPeers; ++g) {
+        flags.f[g] = g < n_peers ? flag_peers[g] : nullptr;
+        if (g < n_peers && !flags.f[g]) return LLOOM_ERR_NULL;
+    }
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(rank, n_peers, flags);
+    return launch_status(cudaGetLastError());
+}
+
+// Set-up helpers for buffers that other processes of the node map (CUDA IPC); not on the forward path.
+int lloom_b200_peer_alloc(int64_t bytes, void **ptr) {
+    if (!ptr || bytes <= 0) return LLOOM_ERR_NULL;
+    cudaError_t e = cudaMalloc(ptr, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaMemset(*ptr, 0, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return launch_status(e);
+}
+int lloom_b200_peer_free(void *ptr) { return launch_status(cudaFree(ptr)); }
+int lloom_b200_peer_export(const void *ptr, unsigned char *handle64) {
+    if (!ptr || !handle64) return LLOOM_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void *>(ptr));
+    if (e == cudaSuccess) memcpy(handle64, &h, 64);
+    return launch_status(e);
+}
+int lloom_b200_peer_open(const unsigned char *handle64, void **ptr) {
+    if (!ptr || !handle64) return LLOOM_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    return launch_status(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+int lloom_b200_peer_close(void *ptr) { return launch_status(cudaIpcCloseMemHandle(ptr)); }
 
 int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
                                   int64_t k, int64_t ldy, void *stream) {

@@ -8,6 +8,10 @@ slices with one all-gather (NCCL over NVLink through ``torch.distributed``; ``gl
 tests).  Per-row arithmetic does not depend on the shard, so the gathered result equals the
 unsharded one bit for bit.  The reference has no distributed layer for this path; its only
 collective code is the tensor-parallel example candle-examples/examples/llama_multiprocess/model.rs:31-98.
+
+Decode batches (m <= 8) can skip the collective: with ``enable_fused_gather`` the GEMV stores every output
+value into the output buffer of each GPU of the node (peer memory mapped through CUDA IPC), followed by one
+small cross-GPU barrier kernel -- same bits, no NCCL launch on the critical path.
 """
 from __future__ import annotations
 
@@ -66,13 +70,69 @@ def gather_rows(y_local: torch.Tensor, plan: ShardPlan, group=None) -> torch.Ten
     return out[:, : plan.n]
 
 
+class _DeviceBytes:
+    """Zero-copy view of raw device memory for ``torch.as_tensor``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerBuffer:
+    """One zeroed device buffer per rank, each mapped into every process of the group (CUDA IPC): ``ptrs[g]`` is
+    rank g's buffer as seen from this process.  Set-up only; collective over the group."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        import ctypes as C
+
+        from . import _lib
+
+        L = _lib.lib()
+        self._L, self.nbytes, self.device, self.rank = L, int(nbytes), device, dist.get_rank(group)
+        world = dist.get_world_size(group)
+        with torch.cuda.device(device):
+            own = C.c_void_p()
+            _lib.check(L.lloom_b200_peer_alloc(self.nbytes, C.byref(own)), "peer_alloc")
+            handle = C.create_string_buffer(64)
+            _lib.check(L.lloom_b200_peer_export(own, handle), "peer_export")
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.ptrs = []
+            for g in range(world):
+                if g == self.rank:
+                    self.ptrs.append(own.value)
+                else:
+                    p = C.c_void_p()
+                    _lib.check(L.lloom_b200_peer_open(handles[g], C.byref(p)), "peer_open")
+                    self.ptrs.append(p.value)
+            self.array = (C.c_void_p * world)(*self.ptrs)  # host array of device pointers for the C ABI
+        dist.barrier(group=group)
+
+    def own_tensor(self) -> torch.Tensor:
+        return torch.as_tensor(_DeviceBytes(self.ptrs[self.rank], self.nbytes), device=self.device)
+
+    def close(self, group=None) -> None:
+        """Collective: every rank unmaps its peers, then frees its own buffer."""
+        if not self.ptrs:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for g, p in enumerate(self.ptrs):
+                if g != self.rank:
+                    self._L.lloom_b200_peer_close(p)
+            dist.barrier(group=group)
+            self._L.lloom_b200_peer_free(self.ptrs[self.rank])
+        self.ptrs = []
+
+
 class ShardedQMatMul:
     """``QMatMul`` whose weight rows are split over the ranks of a process group."""
 
-    def __init__(self, local_forward: Callable[[torch.Tensor], torch.Tensor], plan: ShardPlan, group=None):
+    def __init__(self, local_forward: Callable[[torch.Tensor], torch.Tensor], plan: ShardPlan, group=None, local=None):
         self._fwd = local_forward
         self.plan = plan
         self.group = group
+        self._local = local  # the shard's QMatMul (None on a rank without rows)
+        self._fused = None
 
     @classmethod
     def from_data(cls, data, dtype, shape: Sequence[int], device, group=None) -> "ShardedQMatMul":
@@ -91,11 +151,59 @@ class ShardedQMatMul:
         if rows == 0:
             return cls(lambda x: x.new_empty(x.shape[0], 0, dtype=torch.float32), plan, group)
         mm = QMatMul.from_qtensor(QTensor.from_data(np.ascontiguousarray(raw[lo:hi]), dtype, (rows, k), device))
-        return cls(lambda x: mm.forward(x.reshape(-1, k)), plan, group)
+        return cls(lambda x: mm.forward(x.reshape(-1, k)), plan, group, local=mm)
+
+    def enable_fused_gather(self, max_m: int = 8) -> bool:
+        """Collective.  Prepares the peer-store path for batches of up to ``max_m`` (<= 8) rows: two output buffers
+        per rank (alternated call by call, so a buffer is rewritten only two forwards later) and one flag array,
+        all mapped into every process.  Returns False, changing nothing, when some rank holds no rows or the
+        group has more than eight ranks."""
+        world = self.plan.world
+        if world > 8 or any(self.plan.rows_of(r) == 0 for r in range(world)) or self._local is None:
+            return False
+        max_m = max(1, min(8, int(max_m)))
+        dev = self._local.qtensor.device()
+        outs = [PeerBuffer(4 * max_m * self.plan.n, dev, self.group) for _ in range(2)]
+        flags = PeerBuffer(256, dev, self.group)
+        self._fused = {"max_m": max_m, "outs": outs, "flags": flags, "turn": 0,
+                       "views": [o.own_tensor().view(torch.float32) for o in outs]}
+        return True
+
+    def close(self) -> None:
+        if self._fused is not None:
+            for b in self._fused["outs"] + [self._fused["flags"]]:
+                b.close(self.group)
+            self._fused = None
+
+    def _forward_fused(self, x2: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        from .quantized import _Workspace, _stream_ptr
+
+        f, L = self._fused, _lib.lib()
+        st = self._local.qtensor.storage
+        rows, k = self._local.qtensor.shape
+        m, n = x2.shape[0], self.plan.n
+        rank = dist.get_rank(self.group)
+        lo, _ = self.plan.range_of(rank)
+        out, view = f["outs"][f["turn"]], f["views"][f["turn"]]
+        f["turn"] ^= 1
+        dev = st.device()
+        with torch.cuda.device(dev):
+            ws_bytes = int(L.lloom_b200_workspace_bytes(int(st.dtype()), m, rows, k))
+            ws = _Workspace.get(dev, ws_bytes)
+            _lib.check(L.lloom_b200_qmatmul_fwd_gather(int(st.dtype()), st.device_ptr(), x2.data_ptr(), m, rows, k, n, lo,
+                                                       out.array, self.plan.world, ws.data_ptr(), ws.numel(),
+                                                       _stream_ptr(dev)), "qmatmul_fwd_gather")
+            _lib.check(L.lloom_b200_peer_barrier(rank, self.plan.world, f["flags"].array, _stream_ptr(dev)), "peer_barrier")
+        return view[: m * n].view(m, n)
 
     def forward(self, xs: torch.Tensor) -> torch.Tensor:
         lead = xs.shape[:-1]
-        y_local = self._fwd(xs.reshape(-1, xs.shape[-1]))
+        x2 = xs.reshape(-1, xs.shape[-1])
+        if (self._fused is not None and x2.shape[0] <= self._fused["max_m"] and x2.dtype == torch.float32
+                and x2.is_contiguous()):
+            return self._forward_fused(x2).reshape(*lead, self.plan.n)
+        y_local = self._fwd(x2)
         return gather_rows(y_local, self.plan, self.group).reshape(*lead, self.plan.n)
 
     __call__ = forward

@@ -37,6 +37,19 @@ def _worker(rank, world, port, out_dir):
                 assert y.cpu().numpy().tobytes() == full.cpu().numpy().tobytes(), (rank, dt, n, k, m)
             else:       # a shard changes the GEMM's tile boundaries, not the per-element arithmetic
                 assert y.cpu().numpy().tobytes() == full.cpu().numpy().tobytes(), (rank, dt, n, k, m)
+            if m <= 8:
+                # gather fused into the GEMV: peer stores + barrier kernel, no collective call; several forwards
+                # in a row (the two output buffers alternate), each on a fresh activation
+                assert sharded.enable_fused_gather(8)
+                for it in range(5):
+                    xi = x + float(it)
+                    yi = sharded.forward(xi).clone()
+                    fi = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq, dt, (n, k), dev)).forward(xi)
+                    torch.cuda.synchronize()
+                    assert yi.cpu().numpy().tobytes() == fi.cpu().numpy().tobytes(), (rank, dt, n, k, m, it, "fused")
+                from lloom_b200.quantized import device_status
+                assert device_status() == 0
+                sharded.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
