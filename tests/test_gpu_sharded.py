@@ -67,3 +67,49 @@ def test_sharded_forward_nccl(tmp_path, cuda_lib):
     world = 2
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_fused_gather_entry_one_gpu(cuda_lib, oracle):
+    """The gather entry on one GPU: with two output buffers standing in for two GPUs' buffers the GEMV writes
+    identical rows into both at the shard's column offset and leaves the other columns alone; the barrier kernel
+    with a group of one returns at once.  Covers both GEMV kernels (dp4a and tensor-core)."""
+    import ctypes as C
+
+    import lloom_b200 as lb
+    from lloom_b200 import _lib
+    from lloom_b200.quantized import device_status, quantize_weights_host
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    dev = torch.device("cuda", 0)
+    L = _lib.lib()
+    for dt, n, k, m in ((12, 520, 1024, 1), (12, 520, 1024, 5), (14, 300, 512, 1), (8, 257, 256, 8)):
+        rng = np.random.default_rng(dt * 1000 + n + m)
+        w = rng.standard_normal((n, k)).astype(np.float32) * np.float32(0.02)
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dev)
+        wq = quantize_weights_host(w, dt)
+        qt = lb.QTensor.from_data(wq, dt, (n, k), dev)
+        full = lb.QMatMul.from_qtensor(qt).forward(x)
+        ldy, col0 = n + 40, 24
+        bufs = [torch.full((m, ldy), -7.0, dtype=torch.float32, device=dev) for _ in range(2)]
+        ptrs = (C.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+        ws_bytes = int(L.lloom_b200_workspace_bytes(dt, m, n, k))
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = L.lloom_b200_qmatmul_fwd_gather(dt, qt.device_ptr(), x.data_ptr(), m, n, k, ldy, col0, ptrs, 2,
+                                             ws.data_ptr(), ws.numel(), stream)
+        assert rc == 0, rc
+        flags = torch.zeros(16, dtype=torch.int32, device=dev)
+        fptr = (C.c_void_p * 1)(flags.data_ptr())
+        assert L.lloom_b200_peer_barrier(0, 1, fptr, stream) == 0
+        torch.cuda.synchronize()
+        assert device_status() == 0
+        assert int(flags[0].item()) == 1 and int(flags[8].item()) == 1  # slot of rank 0 and the call counter
+        for b in bufs:
+            got = b.cpu().numpy()
+            assert got[:, col0:col0 + n].tobytes() == full.cpu().numpy().tobytes(), (dt, n, k, m)
+            assert (got[:, :col0] == -7.0).all() and (got[:, col0 + n:] == -7.0).all()
+    # argument checks
+    assert L.lloom_b200_qmatmul_fwd_gather(12, qt.device_ptr(), x.data_ptr(), 9, n, k, ldy, col0, ptrs, 2,
+                                           ws.data_ptr(), ws.numel(), stream) == _lib.ERR_SHAPE
+    assert L.lloom_b200_peer_barrier(1, 1, fptr, stream) == _lib.ERR_SHAPE
