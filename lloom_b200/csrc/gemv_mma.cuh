@@ -17,9 +17,9 @@
 // superblocks j, j+4, ... in order, and the team's first warp adds the four partial sums in warp order, so a
 // row's f32 sum has one fixed order whatever the batch, the shard or the launch.  (Measured on [14336, 4096],
 // 8 rows: teams of 2 / 4 / 8 / 16 warps give 11.9 / 11.1 / 11.2 / 12.5 us per forward.)  Every CTA quantizing
-// all activation rows itself was measured too: 128 blocks x ~200 instructions per CTA cost more than the
-// separate quantizer kernel's launch gap, so these batches keep that kernel.  (Two rows: 11.1 us here against
-// 12.2 us on the dp4a kernel with its fused quantizer; one row stays there, 8.6 us against 11.0 us.)
+// all activation rows itself was measured too: from three rows on the blocks x ~200 instructions per CTA cost more
+// than the separate quantizer kernel's launch gap, so those batches keep that kernel.  (Two rows, prologue
+// quantizer: 10.2 us here against 12.2 us on the dp4a kernel; one row stays there, 8.6 us against 11.0 us.)
 #pragma once
 
 #include "gemv.cuh"
@@ -27,6 +27,9 @@
 namespace lloom {
 
 constexpr int kMmaTileRows = 16;
+// Up to this many rows the quantizer runs as the kernel's prologue (measured per forward: 10.0 us against 11.5 us
+// with the separate quantizer at M = 2; 11.6 against 11.4 at M = 4).
+constexpr int kMmaFusedMaxM = 2;
 constexpr int kMmaWarps = 16;  // consumer warps; SPLIT of them share a tile, warp j of a team takes superblocks j, j+SPLIT, ...
 constexpr int kMmaRedBytes = 2 * kMmaWarps * 32 * 16;  // double-buffered partial sums, one float4 per lane
 
@@ -174,7 +177,12 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     bool alive = true;  // after a timed-out wait the warp keeps meeting its partner at the pair barrier but computes nothing
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) LLOOM_TRACE_MARK(14);
-    if (p.act_planes) {
+    if (p.x) {  // quantizer as prologue: this CTA quantizes the activation rows into its own planes
+        const int nbq = p.k >> 8, nblk = p.m * nbq;
+        for (int blk = warp; blk < nblk; blk += kMmaWarps)
+            q8k_block_to_planes(p.x, act_smem, blk / nbq, blk % nbq, p.m, nbq, p.act_pitch, lane);
+        asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
+    } else if (p.act_planes) {
         if (threadIdx.x == 0) {
             mbar_arrive_expect_tx(act_bar, (uint32_t)p.act_bytes);
             bulk_g2s(act_smem, p.act, (uint32_t)p.act_bytes, act_bar);

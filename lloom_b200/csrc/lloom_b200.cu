@@ -243,7 +243,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     if ((int64_t)grid > n) grid = (int)n;
     const bool overlap_on = g_launch_overlap.load(std::memory_order_relaxed) != 0;
     // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
-    if (x == nullptr && gemv_mma_fits(di, w_dtype, m, n, k)) {
+    if ((x == nullptr || m <= kMmaFusedMaxM) && gemv_mma_fits(di, w_dtype, m, n, k)) {
         const int64_t row_pitch = bank_pitch(p.row_bytes, 8);
         const int64_t stage = (int64_t)kMmaTileRows * row_pitch;
         p.act_bytes = (int)mma_act_bytes(m, k);
@@ -340,10 +340,9 @@ static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *
         rc = device_info(di);
         if (rc != LLOOM_OK) return rc;
         const bool mma = gemv_mma_fits(di, w_dtype, m, n, k);
-        // single-token decode (and two rows of Q8_0 / Q6_K): one launch, the activation quantizer is the GEMV's
-        // prologue (the workspace stays unused).  From three rows on, every CTA re-quantizing all rows costs
-        // more than one small kernel does.
-        if (m <= 2 && !mma)
+        // up to two rows: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
+        // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
+        if ((m <= 2 && !mma) || (mma && m <= kMmaFusedMaxM))
             return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream, false, peers);
         // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
         // codes, scales and sums as the canonical blocks, laid out for its fragment loads)

@@ -9,11 +9,19 @@
 
 namespace lloom {
 
-// Rust `f32 as i8` after `round()`: saturating, NaN -> 0.
+// Rust `f32 as i8` after `round()`: saturating, NaN -> 0.  The float -> s32 conversion saturates and maps NaN
+// to 0 in hardware; the s32 -> s8 step saturates again.  v is integer-valued (or NaN / infinite), so the
+// rounding mode of the first conversion does not matter.
 __device__ __forceinline__ int sat_i8_from_rounded(float v) {
-    if (v != v) return 0;
-    v = fminf(fmaxf(v, -128.0f), 127.0f);
-    return (int)v;
+    int r;
+    asm("{\n"
+        ".reg .s32 t;\n"
+        "cvt.rzi.s32.f32 t, %1;\n"
+        "cvt.sat.s8.s32 %0, t;\n"
+        "}\n"
+        : "=r"(r)
+        : "f"(v));
+    return r;
 }
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
@@ -29,21 +37,21 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 // untouched; they only ever multiply d == 0).
 __device__ __forceinline__ void q8k_quantize_warp(const float (&v)[8], int lane, uint32_t &q_lo, uint32_t &q_hi,
                                                   float &d, int &sum16) {
+    // The sequential scan keeps the FIRST element of largest magnitude (`if amax < ax`; NaN never wins).  In-lane:
+    // the same scan over the lane's 8 elements.  Across lanes: the largest magnitude by a max-reduction, then the
+    // lowest lane holding it (ballot + find-first) hands over its candidate -- lanes are in element order.
     float amax = 0.0f, vmax = 0.0f;
-    int idx = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float ax = fabsf(v[i]);
-        if (amax < ax) { amax = ax; vmax = v[i]; idx = lane * 8 + i; }
+        if (amax < ax) { amax = ax; vmax = v[i]; }
     }
+    float wmax = amax;
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
-        const float ov = __shfl_xor_sync(0xffffffffu, vmax, off);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
-        // larger magnitude wins; equal magnitudes -> lower index (the sequential scan's first hit)
-        if (oa > amax || (oa == amax && oi < idx)) { amax = oa; vmax = ov; idx = oi; }
-    }
+    for (int off = 1; off < 32; off <<= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, off));
+    const unsigned holders = __ballot_sync(0xffffffffu, amax == wmax);
+    vmax = __shfl_sync(0xffffffffu, vmax, __ffs(holders) - 1);
+    amax = wmax;
     if (amax == 0.0f) {
         q_lo = q_hi = 0;
         d = 0.0f;
