@@ -142,6 +142,19 @@ int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, voi
 int lloom_b200_get_rows(int dtype, const void *blocks, int64_t rows, int64_t hidden, const uint32_t *ids,
                         int64_t n_ids, float *out, void *stream);
 
+/* ---- Blocks on the GEMV's store: the reference's MvStore (mod.rs:1668-1696) ----
+ * QMatMul::forward_silu (mod.rs:2105-2122): y = silu(W.x), SiLU as v / (1 + exp(-v)) in f32 (op.rs:755-757).
+ * QMatMul::forward_mul_into (mod.rs:2124-2155): y <- y * (W.x) in y's own buffer, the SwiGLU's up projection
+ * landing as silu(g) * u.  One launch each (plus the quantizer kernel for 3..8 rows), no extra pass over y.
+ * Like the reference's store blocks they serve the matvec path only: m <= 8, else LLOOM_ERR_SHAPE and the caller
+ * composes.  Other arguments as lloom_b200_qmatmul_fwd. */
+#define LLOOM_STORE_PLAIN 0
+#define LLOOM_STORE_SILU 1
+#define LLOOM_STORE_MUL_INTO 2
+int lloom_b200_qmatmul_fwd_store(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                                 int64_t k, int64_t ldy, int store, void *workspace, int64_t workspace_bytes,
+                                 void *stream);
+
 /* ---- Row-sharded forward with the all-gather fused into the GEMV (one node, up to 8 GPUs) ----
  *
  * The reference shards nothing on this path; the sharded layer here (rank g owns rows [g*ceil(n/G), ...), the

@@ -31,6 +31,7 @@ SYMBOLS = [
     ("lloom_b200_gemm", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd_static", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd_store", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd_gather", _int, [_int, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(_vp), _int, _vp, _i64, _vp]),
     ("lloom_b200_peer_barrier", _int, [_int, _int, C.POINTER(_vp), _vp]),
     ("lloom_b200_peer_alloc", _int, [_i64, C.POINTER(_vp)]),

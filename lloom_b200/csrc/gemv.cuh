@@ -312,13 +312,18 @@ struct GemvParams {
     // own and its peers', mapped into this process) instead of `y`, so the row-sharded forward needs no separate
     // all-gather: the stores cross NVLink while the rest of the rows are still being computed.
     int n_peers;
+    // Block on the store (the reference's MvStore, lloom-tensor/src/quantized/mod.rs:1668-1696):
+    // 0 plain, 1 silu(W.x), 2 dst <- dst * (W.x).
+    int store_mode;
     float *y_peer[kMaxPeers];
 };
 
-// One output value to its destination(s).
+// One output value to its destination(s).  SiLU in the reference's f32 form v / (1 + exp(-v)) (op.rs:755-757,
+// kernels/metal_src/quantized_store.metal:17-25); MulInto reads the destination and multiplies it by the product.
 __device__ __forceinline__ void store_out(const GemvParams &p, int64_t idx, float v) {
+    if (p.store_mode == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
     if (p.n_peers == 0) {
-        p.y[idx] = v;
+        p.y[idx] = (p.store_mode == LLOOM_STORE_MUL_INTO) ? __fmul_rn(p.y[idx], v) : v;
     } else {
         for (int g = 0; g < p.n_peers; ++g) p.y_peer[g][idx] = v;
     }

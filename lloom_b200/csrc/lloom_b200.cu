@@ -202,6 +202,7 @@ struct PeerFlags {  // one flag array per GPU: kMaxPeers slots written by the pe
 struct PeerOut {  // fused gather: output buffers of all GPUs (own included), already offset to this shard's column
     int n = 0;
     float *y[kMaxPeers] = {};
+    int store = LLOOM_STORE_PLAIN;  // block on the store (also used alone, with n == 0)
 };
 
 static int gemv_launch(int w_dtype, const void *w, const void *act, const float *x, float *y, int64_t m, int64_t n,
@@ -229,6 +230,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.act_planes = 0;
     p.tile_bar_bytes = 0;
     p.n_peers = peers ? peers->n : 0;
+    p.store_mode = peers ? peers->store : LLOOM_STORE_PLAIN;
     for (int g = 0; g < kMaxPeers; ++g) p.y_peer[g] = (peers && g < peers->n) ? peers->y[g] : nullptr;
     // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
     const int64_t units = k / (w_dtype == LLOOM_Q8_0 ? 64 : 256);
@@ -504,6 +506,21 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
     return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
                            workspace_bytes - act, stream);
+}
+
+int lloom_b200_qmatmul_fwd_store(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                                 int64_t k, int64_t ldy, int store, void *workspace, int64_t workspace_bytes,
+                                 void *stream) {
+    int rc = check_common(w_dtype, m, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (m > 8 || ldy < n || store < LLOOM_STORE_PLAIN || store > LLOOM_STORE_MUL_INTO) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !x || !y) return LLOOM_ERR_NULL;
+    const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
+    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    PeerOut out;
+    out.store = store;
+    return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, &out);
 }
 
 int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard, int64_t k,

@@ -155,7 +155,9 @@ class QCudaStorage:
 
     # cuda.rs:862-894 fwd: weight [n,k]; x [..., k] contiguous f32 (f16/bf16 widen first); out [..., n].
     def fwd(self, self_shape: Sequence[int], x: torch.Tensor, out: torch.Tensor | None = None,
-            out_col_offset: int = 0) -> torch.Tensor:
+            out_col_offset: int = 0, store: int = 0) -> torch.Tensor:
+        """``store``: block on the GEMV's store (the reference's MvStore, mod.rs:1668-1696): 0 plain, 1 ``silu(W.x)``,
+        2 ``out <- out * (W.x)`` (needs ``out``); served for at most 8 rows, like the reference's matvec store."""
         if len(self_shape) != 2:
             raise LloomError(_lib.ERR_SHAPE, "fwd", f"weight shape {tuple(self_shape)} is not [n, k]")
         n, k = int(self_shape[0]), int(self_shape[1])
@@ -186,8 +188,15 @@ class QCudaStorage:
             if ws_bytes <= 0:
                 raise LloomError(_lib.ERR_SHAPE, "fwd", f"unsupported shape m={m} n={n} k={k} for {self._dtype!r}")
             ws = _Workspace.get(dev, ws_bytes)
-            check(L.lloom_b200_qmatmul_fwd(int(self._dtype), self._data.data_ptr(), x.data_ptr(), yptr, m, n, k, ldy,
-                                           ws.data_ptr(), ws.numel(), _stream_ptr(dev)), "qmatmul_fwd")
+            if store:
+                if store == 2 and out is None:
+                    raise LloomError(_lib.ERR_NULL, "fwd", "the multiply-into store needs the destination buffer")
+                check(L.lloom_b200_qmatmul_fwd_store(int(self._dtype), self._data.data_ptr(), x.data_ptr(), yptr, m, n, k,
+                                                     ldy, int(store), ws.data_ptr(), ws.numel(), _stream_ptr(dev)),
+                      "qmatmul_fwd_store")
+            else:
+                check(L.lloom_b200_qmatmul_fwd(int(self._dtype), self._data.data_ptr(), x.data_ptr(), yptr, m, n, k, ldy,
+                                               ws.data_ptr(), ws.numel(), _stream_ptr(dev)), "qmatmul_fwd")
         if out is None and in_dtype != torch.float32:
             y = y.to(in_dtype)
         return y
@@ -274,6 +283,32 @@ class QMatMul:
         return self.qtensor.fwd(xs)
 
     __call__ = forward
+
+    MV_STORE_MAX_ROWS = 8
+
+    def mv_store_serves(self, xs: torch.Tensor) -> bool:
+        """Whether the store blocks serve this input (mod.rs ``mv_store_serves``): f32, contiguous, at most 8 rows."""
+        k = self.qtensor.shape[1]
+        return (xs.dtype == torch.float32 and xs.is_contiguous() and xs.dim() >= 2 and xs.shape[-1] == k
+                and xs.numel() // k <= self.MV_STORE_MAX_ROWS)
+
+    def forward_silu(self, xs: torch.Tensor):
+        """``silu(W.x)`` with the SiLU on the GEMV's store, one launch (mod.rs:2105-2122).  ``None`` where the
+        store block does not serve: the caller composes."""
+        if not self.mv_store_serves(xs):
+            return None
+        return self.qtensor.storage.fwd(self.qtensor.shape, xs, store=1)
+
+    def forward_mul_into(self, xs: torch.Tensor, gate: torch.Tensor):
+        """``gate <- gate * (W.x)`` in ``gate``'s own buffer (mod.rs:2124-2155): the SwiGLU's up projection landing as
+        ``silu(g) * u``.  ``gate`` is overwritten.  ``None`` where the store block does not serve."""
+        n, k = self.qtensor.shape
+        rows = xs.numel() // k if xs.dim() >= 2 else 0
+        if (not self.mv_store_serves(xs) or gate.dtype != torch.float32 or not gate.is_contiguous()
+                or gate.device != xs.device or gate.numel() != rows * n):
+            return None
+        self.qtensor.storage.fwd(self.qtensor.shape, xs, out=gate.view(rows, n), store=2)
+        return gate
 
 
 def quantize_weights_host(src, dtype: GgmlDType, nthreads: int = 0) -> np.ndarray:

@@ -322,3 +322,30 @@ print("pair-ok")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "pair-ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dt,n,k", [(12, 520, 1024), (14, 300, 512), (8, 257, 256)])
+def test_store_blocks_silu_and_mul_into(dev, oracle, dt, n, k):
+    """forward_silu / forward_mul_into (mod.rs:2105-2155): the product is the plain forward's, bit for bit; SiLU is
+    v / (1 + exp(-v)) in f32 (exp within a few ulp of the host's); the multiply-into is one exact f32 product."""
+    import torch
+
+    import lloom_b200 as lb
+
+    for m in (1, 2, 5, 8):
+        _, x, wq = make_case(oracle, dt, n, k, m, seed=dt + m)
+        mm = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq.tobytes(), dt, (n, k), dev))
+        xt = torch.from_numpy(x).to(dev)
+        plain = mm.forward(xt)
+        got = mm.forward_silu(xt)
+        assert got is not None and tuple(got.shape) == (m, n)
+        p64 = plain.double()
+        want = (p64 / (1.0 + torch.exp(-p64))).float()
+        torch.testing.assert_close(got, want, rtol=3e-6, atol=1e-9)
+        gate0 = torch.from_numpy(np.random.default_rng(m).standard_normal((m, n)).astype(np.float32)).to(dev)
+        gate = gate0.clone()
+        assert mm.forward_mul_into(xt, gate) is gate
+        assert gate.cpu().numpy().tobytes() == (gate0 * plain).cpu().numpy().tobytes()
+    # more than eight rows: the store blocks do not serve, the caller composes
+    xt = torch.zeros(9, k, device=dev)
+    assert mm.forward_silu(xt) is None and mm.forward_mul_into(xt, torch.zeros(9, n, device=dev)) is None
