@@ -453,8 +453,27 @@ def run_lm_head(args):
         return out
 
     def time_steps(step):
+        """CUDA-event time of `steps` calls of `step`, which is captured once in a CUDA graph where capture works
+        (launched call by call from Python a 40 us forward is bound by the interpreter); returns (ms, how)."""
         for _ in range(warmup):
             step()
+        torch.cuda.synchronize()
+        how, run = "eager launches", step
+        side = torch.cuda.Stream(device=dev)
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    step()
+            torch.cuda.synchronize()
+
+            def run():
+                g.replay()
+            how = "CUDA graph replays"
+            run()
+        except Exception:
+            torch.cuda.synchronize()
+            how, run = "eager launches", step
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
@@ -462,7 +481,7 @@ def run_lm_head(args):
         torch.cuda.synchronize()
         e0.record()
         for _ in range(steps):
-            step()
+            run()
         e1.record()
         torch.cuda.synchronize()
         t_ms = e0.elapsed_time(e1)
@@ -470,10 +489,10 @@ def run_lm_head(args):
             t = torch.tensor([t_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             t_ms = float(t.item())
-        return t_ms
+        return t_ms, how
 
-    ms_nccl = time_steps(step_nccl)
-    ms, gather, fused_us = ms_nccl, ("NCCL all-gather" if world > 1 else "none (one GPU)"), None
+    ms_nccl, how_nccl = time_steps(step_nccl)
+    ms, gather, fused_us, how = ms_nccl, ("NCCL all-gather" if world > 1 else "none (one GPU)"), None, how_nccl
     if world > 1:
         # the same forwards with the gather fused into the GEMV (peer stores + one barrier kernel per forward)
         fused = [ShardedQMatMul(None, plan, None, local=lb.QMatMul.from_qtensor(q)) for q in pool]
@@ -484,12 +503,12 @@ def run_lm_head(args):
                     out = f.forward(x)
                 return out
 
-            ms_fused = time_steps(step_fused)
+            ms_fused, how_fused = time_steps(step_fused)
             fused_us = ms_fused / steps / copies * 1e3
             if Q.device_status() != 0:
                 raise RuntimeError("device status after the fused gather")
             if ms_fused < ms_nccl:
-                ms, gather = ms_fused, "fused into the GEMV (peer stores over NVLink + barrier kernel)"
+                ms, gather, how = ms_fused, "fused into the GEMV (peer stores over NVLink + barrier kernel)", how_fused
             torch.cuda.synchronize()
             dist.barrier()
             for f in fused:
@@ -505,7 +524,8 @@ def run_lm_head(args):
                        "gather": gather, "us_per_sharded_matmul_nccl": round(ms_nccl / steps / copies * 1e3, 2),
                        "us_per_sharded_matmul_fused": None if fused_us is None else round(fused_us, 2),
                        "copies_per_rank": copies, "us_per_sharded_matmul": round(per_matmul_us, 2),
-                       "per_gpu_GBps": round(value / world, 1), "timing": "CUDA events, eager launches (no graph)"},
+                       "per_gpu_GBps": round(value / world, 1), "timing": "CUDA events, " + how,
+                       "timing_nccl": how_nccl},
             "gpu_launches": steps * copies}), flush=True)
     if world > 1:
         dist.barrier()

@@ -549,6 +549,9 @@ int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float 
 // epoch.  The wait is bounded in time; on a time-out the status word is set and the kernel returns.
 __global__ void peer_barrier_kernel(int rank, int n_peers, PeerFlags flags) {
     __shared__ unsigned int s_epoch;
+    // launched with programmatic serialization when launch overlap is on: resident early, it waits here for the
+    // GEMV before it (and that GEMV's peer stores) to finish
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     unsigned int *mine = flags.f[rank];
     if (threadIdx.x == 0) {
         s_epoch = mine[kMaxPeers] + 1;  // slot kMaxPeers: this GPU's call counter
@@ -583,8 +586,16 @@ int lloom_b200_peer_barrier(int rank, int n_peers, unsigned int *const *flag_pee
         flags.f[g] = g < n_peers ? flag_peers[g] : nullptr;
         if (g < n_peers && !flags.f[g]) return LLOOM_ERR_NULL;
     }
-    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(rank, n_peers, flags);
-    return launch_status(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_launch_overlap.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+    return launch_status(cudaLaunchKernelEx(&cfg, peer_barrier_kernel, rank, n_peers, flags));
 }
 
 // Set-up helpers for buffers that other processes of the node map (CUDA IPC); not on the forward path.
