@@ -2,7 +2,8 @@
 
 The package holds the CUDA kernels with their C ABI (``csrc/``, ``include/lloom_b200.h``) and the
 host-side mirror of the reference's ``GgmlDType`` / ``QTensor`` / ``QMatMul`` / ``QCudaStorage``
-interface (``quantized.py``), plus the row-sharded multi-GPU forward (``sharded.py``).
+interface (``quantized.py``), plus the row-sharded multi-GPU forward (``sharded.py``) and the GGUF
+container reader that feeds ``QTensor`` from a file's block bytes (``gguf_file.py``).
 """
 from ._lib import LloomError  # noqa: F401
 from .quantized import GgmlDType, QCudaStorage, QMatMul, QTensor  # noqa: F401

@@ -91,7 +91,7 @@ class QCudaStorage:
             raise LloomError(_lib.ERR_SHAPE, "load_quantized", f"{nbytes} bytes is not a whole number of blocks")
         pad = MATRIX_ROW_PADDING * dtype.type_size() // dtype.block_size()
         buf = torch.zeros(nbytes + pad, dtype=torch.uint8, device=device)
-        buf[:nbytes].copy_(host, non_blocking=False)
+        buf[:nbytes].copy_(host, non_blocking=host.is_pinned())  # pinned staging buffer: one asynchronous copy
         return cls(buf, nbytes, dtype)
 
     # cuda.rs:624-637 zeros
