@@ -146,7 +146,7 @@ class Content:
             return cls._string(f, version, file_size)
         if vtype == T_ARRAY:
             if depth >= GGUF_MAX_VALUE_DEPTH:
-                raise GgufError(f"gguf: nested arrays deeper than {GGUF_MAX_VALUE_DEPTH}")
+                raise GgufError(f"gguf: array nesting depth exceeds {GGUF_MAX_VALUE_DEPTH}")
             etype = struct.unpack("<I", _need(f, 4))[0]
             n = cls._length(f, version)
             if n > GGUF_MAX_ARRAY_ELEMENTS:

@@ -145,3 +145,44 @@ def test_tensor_ingest_to_device(oracle, cuda_lib, tmp_path):
             c.tensor(fh, "blk.0.attn_norm.weight", dev)
         with pytest.raises(G.GgufError, match="cannot find"):
             c.tensor(fh, "missing", dev)
+
+
+# ---- the reference's header-hardening cases (lloom-tensor/tests/gguf_tests.rs:10-112, 222-240), rebuilt byte by byte ----
+def _header(tensor_count, kv_count, version=3):
+    if version == 1:
+        return struct.pack("<IIII", 0x46554747, 1, tensor_count, kv_count)
+    return struct.pack("<IIQQ", 0x46554747, version, tensor_count, kv_count)
+
+
+def _lp(s: bytes) -> bytes:
+    return struct.pack("<Q", len(s)) + s
+
+
+def _rejects(buf: bytes, msg: str):
+    with pytest.raises(G.GgufError, match=msg):
+        G.Content.read(io.BytesIO(buf))
+
+
+def test_reference_header_hardening_cases():
+    for version in (3, 1):  # empty_header_loads, empty_v1_header_loads
+        c = G.Content.read(io.BytesIO(_header(0, 0, version)))
+        assert not c.metadata and not c.tensor_infos
+    _rejects(_header(0, 1 << 31), "metadata_kv_count")
+    _rejects(_header(1 << 31, 0), "tensor_count")
+    _rejects(_header(1, 0) + struct.pack("<Q", 1 << 31) + b"\0" * 64, "string length")
+    _rejects(_header(0, 1) + _lp(b"k") + struct.pack("<IIQ", 9, 0, 1 << 31) + b"\0" * 64, "array length")
+    _rejects(_header(1, 0) + _lp(b"t") + struct.pack("<I", 0xFFFFFFFF) + b"\0" * 64, "dimensions")
+    nested = _header(0, 1) + _lp(b"k") + struct.pack("<I", 9)
+    nested += struct.pack("<IQ", 9, 1) * 256 + struct.pack("<IQ", 0, 0)
+    _rejects(nested, "nesting depth")
+    _rejects(_header(1, 0) + struct.pack("<Q", 1 << 20) + b"\0" * 40, "remaining file bytes")  # string longer than the file
+
+
+def test_reference_alignment_cases():
+    def alignment_header(a):
+        return _header(0, 1) + _lp(b"general.alignment") + struct.pack("<II", 4, a)
+
+    _rejects(alignment_header(0), "alignment must be nonzero")
+    for a in (1, 8, 24, 32):  # positive legacy alignments are kept, powers of two or not
+        buf = alignment_header(a)
+        assert G.Content.read(io.BytesIO(buf)).tensor_data_offset == -(-len(buf) // a) * a
