@@ -312,6 +312,11 @@ struct GemvParams {
     // own and its peers', mapped into this process) instead of `y`, so the row-sharded forward needs no separate
     // all-gather: the stores cross NVLink while the rest of the rows are still being computed.
     int n_peers;
+    // Fused gather with staging: bytes of the shared-memory area (after the activation planes) that collects the
+    // CTA's output rows, [m][out_pitch] floats; the CTA writes them to the peers in whole lines when it is done.
+    // 0: every value goes out on its own.
+    int out_bytes;
+    int out_pitch;
     // Block on the store (the reference's MvStore, lloom-tensor/src/quantized/mod.rs:1668-1696):
     // 0 plain, 1 silu(W.x), 2 dst <- dst * (W.x).
     int store_mode;
@@ -345,6 +350,31 @@ __device__ __forceinline__ unsigned long long trace_now() {
 #else
 #define LLOOM_TRACE_MARK(slot) do { } while (0)
 #endif
+
+// Output of row `row` (of this CTA's range starting at r_begin), activation row m: staged in shared memory when the
+// launch has a staging area, else straight to its destination(s).
+__device__ __forceinline__ void emit_out(const GemvParams &p, float *out_s, int r_begin, int m, int row, float v) {
+    if (p.out_bytes) {
+        if (p.store_mode == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
+        out_s[m * p.out_pitch + (row - r_begin)] = v;
+    } else {
+        store_out(p, (int64_t)m * p.ldy + row, v);
+    }
+}
+
+// The staged rows of this CTA to every peer buffer: consecutive threads write consecutive floats, so a peer
+// receives whole 128-byte lines instead of one small packet per value.  Called by `nthreads` consumer threads
+// after a barrier among them.
+__device__ __forceinline__ void flush_out(const GemvParams &p, const float *out_s, int r_begin, int r_end, int tid,
+                                          int nthreads) {
+    const int rows = r_end - r_begin;
+    for (int g = 0; g < p.n_peers; ++g)
+        for (int m = 0; m < p.m; ++m) {
+            float *dst = p.y_peer[g] + (int64_t)m * p.ldy + r_begin;
+            const float *src = out_s + m * p.out_pitch;
+            for (int i = tid; i < rows; i += nthreads) dst[i] = src[i];
+        }
+}
 
 // Canonical activation blocks (global) -> planes (shared); all `nthreads` consumer threads take part.
 __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_smem, int tid, int nthreads,
@@ -534,7 +564,7 @@ __device__ __forceinline__ void gemv_producer_rows(const GemvParams &p, uint64_t
     }
 }
 
-// Dynamic shared memory: [barriers 128 B][act planes][stage 0][stage 1]...
+// Dynamic shared memory: [barriers 128 B][act planes][staged output rows, fused gather only][stage 0][stage 1]...
 // Launch overlap: the kernel lets its stream successor start as soon as it is set up
 // (griddepcontrol.launch_dependents) and itself waits for its predecessor (griddepcontrol.wait) only
 // before it reads activations or writes outputs.  The producer warp starts streaming weights right
@@ -550,7 +580,7 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + kMaxStages;
     uint8_t *act_smem = smem + 128;
-    uint8_t *stage0 = act_smem + p.act_bytes;
+    uint8_t *stage0 = act_smem + p.act_bytes + p.out_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int lpr = 1 << p.lpr_log2;
@@ -595,10 +625,15 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
 
     const int units = p.k / Fmt::kUnitElems;
     const int group = lane >> p.lpr_log2, lig = lane & (lpr - 1);
+    float *out_s = reinterpret_cast<float *>(act_smem + p.act_bytes);
     int it = 0;
+    bool ok = true;  // a timed-out wait ends the loop; the warp still meets the others at the flush barrier
     for (int trow = r_begin; trow < r_end; trow += tile_rows, ++it) {
         const int s = it % p.stages;
-        if (!mbar_wait(&full[s], (it / p.stages) & 1)) return;
+        if (!mbar_wait(&full[s], (it / p.stages) & 1)) {
+            ok = false;
+            break;
+        }
         if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(2 + 2 * it);
         const int64_t start = (int64_t)trow * p.row_bytes;
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
@@ -654,9 +689,14 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
             for (int r = 0; r < RW; ++r)
                 if (valid[r]) {
 #pragma unroll
-                    for (int m = 0; m < M; ++m) store_out(p, (int64_t)m * p.ldy + row0 + r, out[r][m]);
+                    for (int m = 0; m < M; ++m) emit_out(p, out_s, r_begin, m, row0 + r, out[r][m]);
                 }
         }
+    }
+    if (p.out_bytes) {
+        const int nthreads = p.n_cwarps * 32;
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (ok) flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);
     }
     if (threadIdx.x == 0) LLOOM_TRACE_MARK(15);
 }

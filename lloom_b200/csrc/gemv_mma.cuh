@@ -136,7 +136,8 @@ __global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *_
 constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image
 constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
 
-// Dynamic shared memory: [barriers 128 B][per-tile barriers][partial sums 8 KB][act planes][stage 0][stage 1]...
+// Dynamic shared memory: [barriers 128 B][per-tile barriers][partial sums][act planes][staged output rows, fused
+// gather only][stage 0][stage 1]...
 template <int SPLIT>
 __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -145,7 +146,8 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     uint64_t *tile_full = reinterpret_cast<uint64_t *>(smem + kMmaBarBytes);
     float4 *red = reinterpret_cast<float4 *>(smem + kMmaBarBytes + p.tile_bar_bytes);
     uint8_t *act_smem = smem + kMmaBarBytes + p.tile_bar_bytes + kMmaRedBytes;
-    uint8_t *stage0 = act_smem + p.act_bytes;
+    float *out_s = reinterpret_cast<float *>(act_smem + p.act_bytes);  // staged output rows (fused gather only)
+    uint8_t *stage0 = act_smem + p.act_bytes + p.out_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // whole 16-row tiles per CTA (a ragged split would leave most CTAs a last tile of a row or two that costs a
@@ -294,14 +296,18 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             out[3] += o.w;
         }
         if (t0 < p.m) {
-            if (gid < rows) store_out(p, (int64_t)t0 * p.ldy + trow + gid, out[0]);
-            if (gid + 8 < rows) store_out(p, (int64_t)t0 * p.ldy + trow + gid + 8, out[2]);
+            if (gid < rows) emit_out(p, out_s, r_begin, t0, trow + gid, out[0]);
+            if (gid + 8 < rows) emit_out(p, out_s, r_begin, t0, trow + gid + 8, out[2]);
         }
         if (t1 < p.m) {
-            if (gid < rows) store_out(p, (int64_t)t1 * p.ldy + trow + gid, out[1]);
-            if (gid + 8 < rows) store_out(p, (int64_t)t1 * p.ldy + trow + gid + 8, out[3]);
+            if (gid < rows) emit_out(p, out_s, r_begin, t1, trow + gid, out[1]);
+            if (gid + 8 < rows) emit_out(p, out_s, r_begin, t1, trow + gid + 8, out[3]);
         }
         if (it == 0 || it == 5 || it == 6) LLOOM_TRACE_MARK(it == 0 ? 3 : it == 5 ? 5 : 7);
+    }
+    if (p.out_bytes) {  // every consumer warp gets here, timed-out ones included
+        asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
+        flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);
     }
 }
 

@@ -230,6 +230,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.act_planes = 0;
     p.tile_bar_bytes = 0;
     p.n_peers = peers ? peers->n : 0;
+    p.out_bytes = 0;
+    p.out_pitch = 0;
     p.store_mode = peers ? peers->store : LLOOM_STORE_PLAIN;
     for (int g = 0; g < kMaxPeers; ++g) p.y_peer[g] = (peers && g < peers->n) ? peers->y[g] : nullptr;
     // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
@@ -244,6 +246,13 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     int grid = di.sm_count;
     if ((int64_t)grid > n) grid = (int)n;
     const bool overlap_on = g_launch_overlap.load(std::memory_order_relaxed) != 0;
+    // Fused gather: room to stage a CTA's output rows (so that they leave for the peers in whole lines), if small
+    auto staging = [&](int64_t rows_per_cta, int &pitch) -> int64_t {
+        if (p.n_peers == 0) return 0;
+        pitch = (int)((rows_per_cta + 3) / 4 * 4);
+        const int64_t bytes = (int64_t)m * pitch * 4;
+        return bytes <= 32 * 1024 ? bytes : 0;
+    };
     // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
     if ((x == nullptr || m <= kMmaFusedMaxM) && gemv_mma_fits(di, w_dtype, m, n, k)) {
         const int64_t row_pitch = bank_pitch(p.row_bytes, 8);
@@ -253,12 +262,23 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.act_planes = act_planes ? 1 : 0;
         p.row_pitch = (int)row_pitch;
         p.tile_bar_bytes = (int)gemv_mma_tile_bar_bytes(di, n);
-        int64_t stages = ((int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - p.tile_bar_bytes - p.act_bytes) / stage;
+        const int64_t room = (int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - p.tile_bar_bytes - p.act_bytes;
+        {
+            const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
+            const int64_t g = total_tiles < grid ? total_tiles : grid;
+            int pitch = 0;
+            const int64_t want = staging((total_tiles + g - 1) / g * kMmaTileRows, pitch);
+            if (want > 0 && room - want >= 2 * stage) {
+                p.out_bytes = (int)want;
+                p.out_pitch = pitch;
+            }
+        }
+        int64_t stages = (room - p.out_bytes) / stage;
         if (stages > kMaxStages) stages = kMaxStages;
         p.n_cwarps = kMmaWarps;
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
-        const int smem = kMmaBarBytes + kMmaRedBytes + p.tile_bar_bytes + p.act_bytes + (int)(stages * stage);
+        const int smem = kMmaBarBytes + kMmaRedBytes + p.tile_bar_bytes + p.act_bytes + p.out_bytes + (int)(stages * stage);
         const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
         if (grid > total_tiles) grid = (int)total_tiles;
         return launch_status(launch_gemv_mma(p, grid, smem, overlap_on, stream));
@@ -279,19 +299,28 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     }
     const int full[5][2] = {{8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};
     for (auto &f : full) shapes[ns++] = {f[0], f[1], false};
+    int out_pitch = 0;
+    const int64_t out_want = staging((n + grid - 1) / grid, out_pitch);
     for (int si = 0; si < ns; ++si) {
         const int cw = shapes[si].cw, rw = shapes[si].rw;
         const int64_t per_block = shapes[si].half ? (int64_t)(di.smem_per_sm - 2 * di.smem_reserved) / 2 / 16 * 16
                                                   : (int64_t)di.max_smem_optin;
-        const int64_t budget = per_block - 128 - p.act_bytes;
+        int64_t budget = per_block - 128 - p.act_bytes;
         const int64_t stage = round16((int64_t)cw * groups * rw * p.row_bytes + pad);
         if (budget < 2 * stage) continue;
+        p.out_bytes = 0;
+        p.out_pitch = 0;
+        if (out_want > 0 && budget - out_want >= 2 * stage) {
+            p.out_bytes = (int)out_want;
+            p.out_pitch = out_pitch;
+            budget -= out_want;
+        }
         int64_t stages = budget / stage;
         if (stages > kMaxStages) stages = kMaxStages;
         p.n_cwarps = cw;
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
-        const int smem = 128 + p.act_bytes + (int)(stages * stage);
+        const int smem = 128 + p.act_bytes + p.out_bytes + (int)(stages * stage);
         cudaError_t e = (rw == 2) ? launch_gemv_fmt<2>(p, grid, smem, overlap, stream)
                                   : launch_gemv_fmt<1>(p, grid, smem, overlap, stream);
         return launch_status(e);
