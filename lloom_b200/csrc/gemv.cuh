@@ -307,7 +307,9 @@ struct GemvParams {
     int row_pitch;     // tensor-core kernel only: bytes between weight rows inside a stage
     int act_pitch;     // tensor-core kernel only: bytes between activation rows of the code plane
     int act_planes;    // tensor-core kernel only: `act` already holds the plane image (else canonical blocks)
-    int tile_bar_bytes;  // tensor-core kernel only: bytes of the per-tile barrier array (multiple of 16)
+    int tile_bar_bytes;  // tensor-core kernel only: bytes of the per-item barrier array (multiple of 16)
+    int chunk_sb;        // tensor-core kernel only: superblocks of a row per stage (all of them unless K is large)
+    int nchunks;         // tensor-core kernel only: stages' worth of superblocks per row
     // Fused gather: when n_peers > 0 every output value goes to the same place in each of these buffers (this GPU's
     // own and its peers', mapped into this process) instead of `y`, so the row-sharded forward needs no separate
     // all-gather: the stores cross NVLink while the rest of the rows are still being computed.
@@ -540,27 +542,6 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
                 mbar_arrive(&full[s]);
             }
         }
-    }
-}
-
-// Row-wise variant for row sizes that are multiples of 16 bytes: one bulk copy per row, rows `row_pitch` bytes
-// apart in the stage (the caller picks a pitch that spreads the rows a warp reads together over the banks).
-// Every tile completes a barrier of its own (tile_full[it], used once): the consumers of a stage are different
-// warps from one use to the next, and a phase parity cannot tell a late warp which use it is looking at.
-__device__ __forceinline__ void gemv_producer_rows(const GemvParams &p, uint64_t *tile_full, uint64_t *empty, uint8_t *stage0,
-                                                   int tile_rows, int row_pitch, int r_begin, int r_end, int lane) {
-    int it = 0;
-    for (int row0 = r_begin; row0 < r_end; row0 += tile_rows, ++it) {
-        const int s = it % p.stages;
-        if (it >= p.stages) {
-            if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
-        }
-        const int rows = min(tile_rows, r_end - row0);
-        uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
-        if (lane == 0) mbar_arrive_expect_tx(&tile_full[it], (uint32_t)(rows * p.row_bytes));
-        __syncwarp();
-        for (int r = lane; r < rows; r += 32)
-            bulk_g2s(dst + (size_t)r * row_pitch, p.w + (int64_t)(row0 + r) * p.row_bytes, (uint32_t)p.row_bytes, &tile_full[it]);
     }
 }
 

@@ -133,6 +133,35 @@ __global__ void __launch_bounds__(256) quantize_q8k_planes_kernel(const float *_
     q8k_block_to_planes(x, out, blk / nb, blk % nb, m, nb, act_pitch, lane);
 }
 
+// Producer loop: work items in order (tile 0: chunks 0.., tile 1: ...).  An item is `chunk_sb` superblocks (fewer in a
+// row's last chunk) of up to 16 consecutive rows: one bulk copy per row, rows `row_pitch` bytes apart in the stage.
+// Every item completes a barrier of its own (item_full[it], used once): the consumers of a stage are different
+// warps from one use to the next, and a phase parity cannot tell a late warp which use it is looking at.
+__device__ __forceinline__ void gemv_mma_producer(const GemvParams &p, uint64_t *item_full, uint64_t *empty, uint8_t *stage0,
+                                                  int r_begin, int r_end, int lane) {
+    const int nb = p.k >> 8;
+    const int ntiles = (r_end - r_begin + kMmaTileRows - 1) / kMmaTileRows;
+    int it = 0;
+    for (int tile = 0; tile < ntiles; ++tile) {
+        const int row0 = r_begin + tile * kMmaTileRows;
+        const int rows = min(kMmaTileRows, r_end - row0);
+        for (int c = 0; c < p.nchunks; ++c, ++it) {
+            const int s = it % p.stages;
+            if (it >= p.stages) {
+                if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
+            }
+            const int sb0 = c * p.chunk_sb;
+            const uint32_t bytes = (uint32_t)(min(p.chunk_sb, nb - sb0) * Q4K_BYTES);
+            uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
+            if (lane == 0) mbar_arrive_expect_tx(&item_full[it], (uint32_t)rows * bytes);
+            __syncwarp();
+            for (int r = lane; r < rows; r += 32)
+                bulk_g2s(dst + (size_t)r * p.row_pitch, p.w + (int64_t)(row0 + r) * p.row_bytes + (int64_t)sb0 * Q4K_BYTES, bytes,
+                         &item_full[it]);
+        }
+    }
+}
+
 constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image
 constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
 
@@ -162,7 +191,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
 #endif
     if (threadIdx.x == 0) LLOOM_TRACE_MARK(0);
     const int ntiles = (r_end - r_begin + kMmaTileRows - 1) / kMmaTileRows;
-    for (int i = threadIdx.x; i < ntiles; i += blockDim.x) mbar_init(&tile_full[i], 1);
+    for (int i = threadIdx.x; i < ntiles * p.nchunks; i += blockDim.x) mbar_init(&tile_full[i], 1);
     if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], SPLIT);
     if (threadIdx.x == 32) mbar_init(act_bar, 1);
     fence_mbar_init();
@@ -170,7 +199,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == kMmaWarps) {
-        gemv_producer_rows(p, tile_full, empty, stage0, kMmaTileRows, p.row_pitch, r_begin, r_end, lane);
+        gemv_mma_producer(p, tile_full, empty, stage0, r_begin, r_end, lane);
         LLOOM_TRACE_MARK(8);
         return;
     }
@@ -213,28 +242,31 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     const int team = warp / SPLIT, member = warp % SPLIT;
     int round = 0;
     for (int it = team; it < ntiles; it += kTeams, ++round) {
-        const int s = it % p.stages;
-        alive = alive && mbar_wait(&tile_full[it], 0);
-        if (member == 0 && (it == 0 || it == 5 || it == 6)) LLOOM_TRACE_MARK(it == 0 ? 2 : it == 5 ? 4 : 6);
         const int trow = r_begin + it * kMmaTileRows;
-        const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
         const int rows = min(kMmaTileRows, r_end - trow);
         // rows of the A fragment held by this lane; rows past the end of the range read row 0 and are dropped later
         const int ra = gid < rows ? gid : 0, rb = gid + 8 < rows ? gid + 8 : 0;
-        const uint8_t *rowa = tile_base + (size_t)ra * p.row_pitch, *rowb = tile_base + (size_t)rb * p.row_pitch;
-
         float out[4] = {0.f, 0.f, 0.f, 0.f};  // (row gid, t0), (gid, t1), (gid+8, t0), (gid+8, t1)
+        // the tile's chunks of superblocks, in order: a warp's partial sums run over all of them
+        for (int c = 0; c < p.nchunks; ++c) {
+        const int item = it * p.nchunks + c, s = item % p.stages;
+        alive = alive && mbar_wait(&tile_full[item], 0);
+        if (member == 0 && c == 0 && (it == 0 || it == 5 || it == 6)) LLOOM_TRACE_MARK(it == 0 ? 2 : it == 5 ? 4 : 6);
+        const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
+        const uint8_t *rowa = tile_base + (size_t)ra * p.row_pitch, *rowb = tile_base + (size_t)rb * p.row_pitch;
+        const int sb0 = c * p.chunk_sb, nsb = min(p.chunk_sb, nb - sb0);
 #pragma unroll 2
-        for (int b = member; alive && b < nb; b += SPLIT) {
-            const uint4 ha = *reinterpret_cast<const uint4 *>(rowa + (size_t)b * Q4K_BYTES);
-            const uint4 hb = *reinterpret_cast<const uint4 *>(rowb + (size_t)b * Q4K_BYTES);
+        for (int bl = member; alive && bl < nsb; bl += SPLIT) {
+            const int b = sb0 + bl;  // superblock of the row; bl: its place in the stage
+            const uint4 ha = *reinterpret_cast<const uint4 *>(rowa + (size_t)bl * Q4K_BYTES);
+            const uint4 hb = *reinterpret_cast<const uint4 *>(rowb + (size_t)bl * Q4K_BYTES);
             // 6-bit scales / mins (utils.rs:50-60), four per word, for the two rows
             const uint32_t sca[2] = {ha.y & 0x3f3f3f3fu, (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4)};
             const uint32_t scb[2] = {hb.y & 0x3f3f3f3fu, (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4)};
             const uint32_t mna[2] = {ha.z & 0x3f3f3f3fu, ((ha.w >> 4) & 0x0f0f0f0fu) | (((ha.z >> 6) & 0x03030303u) << 4)};
             const uint32_t mnb[2] = {hb.z & 0x3f3f3f3fu, ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4)};
-            const uint2 *qa = reinterpret_cast<const uint2 *>(rowa + (size_t)b * Q4K_BYTES + 16) + tig;
-            const uint2 *qb = reinterpret_cast<const uint2 *>(rowb + (size_t)b * Q4K_BYTES + 16) + tig;
+            const uint2 *qa = reinterpret_cast<const uint2 *>(rowa + (size_t)bl * Q4K_BYTES + 16) + tig;
+            const uint2 *qb = reinterpret_cast<const uint2 *>(rowb + (size_t)bl * Q4K_BYTES + 16) + tig;
             const uint4 *act = reinterpret_cast<const uint4 *>(codes + (size_t)b * 256);
             int S[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -281,6 +313,7 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
         // this warp is done reading the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+        }  // chunks
 
         // partial sums of the team meet in shared memory; its first warp adds them in member order
         float4 *slot = red + ((round & 1) * kMmaWarps + team * SPLIT) * 32 + lane;

@@ -164,6 +164,9 @@ static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem,
 }
 
 static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    // whole rows per stage: four teams of four warps, a tile each; rows cut into pieces: one team of sixteen, so
+    // that a piece is consumed (and its stage handed back) as fast as possible
+    if (p.nchunks > 1) return launch_gemv_mma_inst<16>(p, grid, smem, overlap, stream);
     return launch_gemv_mma_inst<4>(p, grid, smem, overlap, stream);
 }
 
@@ -177,20 +180,53 @@ static bool gemv_mma_enabled() {
     return cached == 1;
 }
 
-// Whether the tensor-core GEMV takes this shape: Q4_K, 2..8 activation rows, two 16-row stages fit beside the
-// activation planes.
-static int64_t gemv_mma_tile_bar_bytes(const DeviceInfo &di, int64_t n) {
+// Whether the tensor-core GEMV quantizes the activations itself (as its prologue): up to two rows, and few enough
+// 256-element blocks that a CTA's sixteen warps get through them in two rounds.
+static bool gemv_mma_fused(int64_t m, int64_t k) { return m <= kMmaFusedMaxM && m * (k / QK_K) <= 32; }
+
+// Shared-memory plan of the tensor-core GEMV: a stage holds `chunk_sb` superblocks of 16 rows -- whole rows when two
+// such stages fit beside the activation planes, else the rows are cut into `nchunks` pieces of equal length
+// (K = 14336: planes and whole-row stages would need 250 KB).
+struct MmaPlan {
+    bool ok = false;
+    int chunk_sb = 0, nchunks = 0;
+    int64_t bar_bytes = 0, row_pitch = 0, stage = 0, room = 0;
+};
+
+static MmaPlan gemv_mma_plan(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
+    MmaPlan pl;
+    if (w_dtype != LLOOM_Q4_K || m < 2 || m > 8 || !gemv_mma_enabled()) return pl;
+    const int64_t nb = k / QK_K;
     const int64_t total = (n + kMmaTileRows - 1) / kMmaTileRows;
     const int64_t grid = total < di.sm_count ? total : di.sm_count;
-    return round16((total + grid - 1) / grid * 8);
+    const int64_t tiles = (total + grid - 1) / grid;
+    for (int64_t nchunks = 1; nchunks <= nb && nchunks <= 16; ++nchunks) {
+        const int64_t chunk = (nb + nchunks - 1) / nchunks;
+        const int64_t bars = round16(tiles * nchunks * 8);
+        if (tiles * nchunks > kMmaMaxTiles) return pl;
+        const int64_t pitch = bank_pitch(chunk * Q4K_BYTES, 8);
+        const int64_t stage = (int64_t)kMmaTileRows * pitch;
+        const int64_t room = (int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - bars - mma_act_bytes(m, k);
+        if (room >= 2 * stage) {
+            // (a single row stays on the dp4a kernel even at K = 14336, where this kernel alone would be faster --
+            // 11.8 us against 14.9 us: the quantizer launch in front of it breaks the chain of overlapping
+            // launches, and a 225-matmul decode step got 8 % slower with it)
+            pl.ok = true;
+            pl.chunk_sb = (int)chunk;
+            pl.nchunks = (int)((nb + chunk - 1) / chunk);
+            pl.bar_bytes = bars;
+            pl.row_pitch = pitch;
+            pl.stage = stage;
+            pl.room = room;
+            return pl;
+        }
+    }
+    return pl;
 }
 
+// Whether the tensor-core GEMV takes this shape: Q4_K, 2..8 activation rows, a plan exists.
 static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
-    if (w_dtype != LLOOM_Q4_K || m < 2 || m > 8 || !gemv_mma_enabled()) return false;
-    const int64_t bars = gemv_mma_tile_bar_bytes(di, n);
-    if (bars > kMmaMaxTiles * 8) return false;
-    const int64_t stage = (int64_t)kMmaTileRows * bank_pitch(weight_row_bytes(w_dtype, k), 8);
-    return (int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - bars - mma_act_bytes(m, k) >= 2 * stage;
+    return gemv_mma_plan(di, w_dtype, m, n, k).ok;
 }
 
 // Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
@@ -229,6 +265,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.act_pitch = 0;
     p.act_planes = 0;
     p.tile_bar_bytes = 0;
+    p.chunk_sb = 0;
+    p.nchunks = 1;
     p.n_peers = peers ? peers->n : 0;
     p.out_bytes = 0;
     p.out_pitch = 0;
@@ -254,15 +292,17 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         return bytes <= 32 * 1024 ? bytes : 0;
     };
     // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
-    if ((x == nullptr || m <= kMmaFusedMaxM) && gemv_mma_fits(di, w_dtype, m, n, k)) {
-        const int64_t row_pitch = bank_pitch(p.row_bytes, 8);
-        const int64_t stage = (int64_t)kMmaTileRows * row_pitch;
+    const MmaPlan plan = gemv_mma_plan(di, w_dtype, m, n, k);
+    if (plan.ok && (x == nullptr || gemv_mma_fused(m, k))) {
+        const int64_t stage = plan.stage;
         p.act_bytes = (int)mma_act_bytes(m, k);
         p.act_pitch = (int)mma_act_pitch(k);
         p.act_planes = act_planes ? 1 : 0;
-        p.row_pitch = (int)row_pitch;
-        p.tile_bar_bytes = (int)gemv_mma_tile_bar_bytes(di, n);
-        const int64_t room = (int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - p.tile_bar_bytes - p.act_bytes;
+        p.row_pitch = (int)plan.row_pitch;
+        p.tile_bar_bytes = (int)plan.bar_bytes;
+        p.chunk_sb = plan.chunk_sb;
+        p.nchunks = plan.nchunks;
+        const int64_t room = plan.room;
         {
             const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
             const int64_t g = total_tiles < grid ? total_tiles : grid;
@@ -373,7 +413,7 @@ static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *
         const bool mma = gemv_mma_fits(di, w_dtype, m, n, k);
         // up to two rows: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
         // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
-        if ((m <= 2 && !mma) || (mma && m <= kMmaFusedMaxM))
+        if ((m <= 2 && !mma) || (mma && gemv_mma_fused(m, k)))
             return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream, false, peers);
         // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
         // codes, scales and sums as the canonical blocks, laid out for its fragment loads)

@@ -349,3 +349,18 @@ def test_store_blocks_silu_and_mul_into(dev, oracle, dt, n, k):
     # more than eight rows: the store blocks do not serve, the caller composes
     xt = torch.zeros(9, k, device=dev)
     assert mm.forward_silu(xt) is None and mm.forward_mul_into(xt, torch.zeros(9, n, device=dev)) is None
+
+
+@pytest.mark.parametrize("n,m", [(40, 8), (130, 5), (97, 2), (64, 1)])
+def test_q4k_long_rows(dev, oracle, n, m):
+    """K = 14336 (an FFN down projection): the tensor-core GEMV cuts the rows into several stages' worth of
+    superblocks and carries each warp's partial sums across the pieces (a single row stays on the dp4a kernel)."""
+    k = 14336
+    _, x, wq = make_case(oracle, 12, n, k, m, seed=n + m)
+    ref = oracle.matmul(12, x, wq, n, nthreads=8)
+    absum = oracle.matmul_absum(12, x, wq, n, nthreads=8)
+    got = run_fwd(dev, 12, wq, n, k, x)
+    assert_matmul_close(got, ref, absum, f"Q4K long rows n={n} m={m}")
+    assert run_fwd(dev, 12, wq, n, k, x).tobytes() == got.tobytes()  # run-to-run bit-stable
+    half = n // 2  # a row shard gives the same bits for its rows
+    assert run_fwd(dev, 12, np.ascontiguousarray(wq[half:]), n - half, k, x).tobytes() == np.ascontiguousarray(got[:, half:]).tobytes()
