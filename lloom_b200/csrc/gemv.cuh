@@ -309,7 +309,9 @@ struct GemvParams {
     int act_planes;    // tensor-core kernel only: `act` already holds the plane image (else canonical blocks)
     int tile_bar_bytes;  // tensor-core kernel only: bytes of the per-item barrier array (multiple of 16)
     int chunk_sb;        // tensor-core kernel only: superblocks of a row per stage (all of them unless K is large)
-    int nchunks;         // tensor-core kernel only: stages' worth of superblocks per row
+    int nchunks;         // both kernels: pieces a row is cut into, each a stage's worth (1: whole rows)
+    int chunk_units;     // dp4a kernel, nchunks > 1: units (superblocks / pairs of Q8_0 blocks) of a row per piece
+    int unit_bytes;      // dp4a kernel: bytes of a unit (144 / 210 / 68)
     // Fused gather: when n_peers > 0 every output value goes to the same place in each of these buffers (this GPU's
     // own and its peers', mapped into this process) instead of `y`, so the row-sharded forward needs no separate
     // all-gather: the stores cross NVLink while the rest of the rows are still being computed.
@@ -327,6 +329,9 @@ struct GemvParams {
 
 // One output value to its destination(s).  SiLU in the reference's f32 form v / (1 + exp(-v)) (op.rs:755-757,
 // kernels/metal_src/quantized_store.metal:17-25); MulInto reads the destination and multiplies it by the product.
+// Only the EPI = 1 kernel instances contain this code: inlined into the sixteen unrolled stores of an 8-row
+// instance it cost the plain forward 25-60 % of that instance's time, and as an out-of-line call it still cost
+// every instance 5-20 % (registers held across the call sites).
 __device__ __forceinline__ void store_out(const GemvParams &p, int64_t idx, float v) {
     if (p.store_mode == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
     if (p.n_peers == 0) {
@@ -545,6 +550,33 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
     }
 }
 
+// The producer loop for rows cut into pieces (long rows: a whole-row tile would not leave room for two stages in
+// the side-by-side shape).  Work items in order -- tile 0: pieces 0.., tile 1: ... -- each `chunk_units` units
+// (fewer in a row's last piece) of up to `tile_rows` rows, one bulk copy per row, the pieces of a tile's rows packed
+// `chunk_units * unit_bytes` apart.  Needs row sizes and piece sizes that are multiples of 16 bytes.
+__device__ __forceinline__ void gemv_producer_pieces(const GemvParams &p, uint64_t *full, uint64_t *empty, uint8_t *stage0,
+                                                     int tile_rows, int units, int r_begin, int r_end, int lane) {
+    const int pitch = p.chunk_units * p.unit_bytes;
+    int it = 0;
+    for (int row0 = r_begin; row0 < r_end; row0 += tile_rows) {
+        const int rows = min(tile_rows, r_end - row0);
+        for (int c = 0; c < p.nchunks; ++c, ++it) {
+            const int s = it % p.stages;
+            if (it >= p.stages) {
+                if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
+            }
+            const int u0 = c * p.chunk_units;
+            const uint32_t bytes = (uint32_t)(min(p.chunk_units, units - u0) * p.unit_bytes);
+            uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
+            if (lane == 0) mbar_arrive_expect_tx(&full[s], (uint32_t)rows * bytes);
+            __syncwarp();
+            for (int r = lane; r < rows; r += 32)
+                bulk_g2s(dst + (size_t)r * pitch, p.w + (int64_t)(row0 + r) * p.row_bytes + (int64_t)u0 * p.unit_bytes, bytes,
+                         &full[s]);
+        }
+    }
+}
+
 // Dynamic shared memory: [barriers 128 B][act planes][staged output rows, fused gather only][stage 0][stage 1]...
 // Launch overlap: the kernel lets its stream successor start as soon as it is set up
 // (griddepcontrol.launch_dependents) and itself waits for its predecessor (griddepcontrol.wait) only
@@ -553,7 +585,10 @@ __device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *ful
 // launch attribute both instructions do nothing.  RW == 1 instances are built to fit two per SM, so
 // a successor's CTA can sit beside its predecessor's and keep the HBM stream going across launches.
 // CW = most consumer warps the instance may be launched with (8, or 12 for the side-by-side m <= 2 shapes).
-template <class Fmt, int M, int RW, int CW = 8>
+// PIECES = the instance for rows cut into pieces (p.nchunks > 1); the whole-row instances keep the loop over pieces
+// out of their code.  EPI = 1: the instance with the store blocks and the fused gather (store_out / emit_out);
+// EPI = 0 stores every value to p.y and nothing else.
+template <class Fmt, int M, int RW, int CW = 8, bool PIECES = false, int EPI = 0>
 __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(const GemvParams p) {
     constexpr int MC = M > 4 ? (M + 1) / 2 : M;  // activation rows per pass
     constexpr int NPASS = (M + MC - 1) / MC;
@@ -588,7 +623,8 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
 
     if (warp == p.n_cwarps) {
         // ---------------- producer warp ----------------
-        gemv_producer(p, full, empty, stage0, tile_rows, r_begin, r_end, lane);
+        if (PIECES) gemv_producer_pieces(p, full, empty, stage0, tile_rows, p.k / Fmt::kUnitElems, r_begin, r_end, lane);
+        else gemv_producer(p, full, empty, stage0, tile_rows, r_begin, r_end, lane);
         return;
     }
 
@@ -607,55 +643,74 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
     const int units = p.k / Fmt::kUnitElems;
     const int group = lane >> p.lpr_log2, lig = lane & (lpr - 1);
     float *out_s = reinterpret_cast<float *>(act_smem + p.act_bytes);
-    int it = 0;
+    int it = 0;  // work items so far: a tile, or one piece of a tile's rows when the rows are cut into pieces
     bool ok = true;  // a timed-out wait ends the loop; the warp still meets the others at the flush barrier
-    for (int trow = r_begin; trow < r_end; trow += tile_rows, ++it) {
-        const int s = it % p.stages;
-        if (!mbar_wait(&full[s], (it / p.stages) & 1)) {
-            ok = false;
-            break;
-        }
-        if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(2 + 2 * it);
-        const int64_t start = (int64_t)trow * p.row_bytes;
-        const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
+    const int nchunks = PIECES ? p.nchunks : 1;
+    const int unit_chunk = PIECES ? p.chunk_units : units;
+    const int piece_pitch = unit_chunk * p.unit_bytes;
+    for (int trow = r_begin; trow < r_end && ok; trow += tile_rows) {
         const int local0 = (warp * groups + group) * RW;
         const int row0 = trow + local0;
-        const uint8_t *rowp[RW];
         bool valid[RW];
 #pragma unroll
-        for (int r = 0; r < RW; ++r) {
-            valid[r] = row0 + r < r_end;
-            rowp[r] = tile_base + (size_t)(local0 + r) * p.row_bytes;
-        }
-
-        float out[RW][M];
+        for (int r = 0; r < RW; ++r) valid[r] = row0 + r < r_end;
+        float accs[NPASS][RW][MC];
 #pragma unroll
-        for (int pass = 0; pass < NPASS; ++pass) {
-            const int m0 = pass * MC;
-            float acc[RW][MC];
+        for (int pass = 0; pass < NPASS; ++pass)
 #pragma unroll
             for (int r = 0; r < RW; ++r)
 #pragma unroll
-                for (int m = 0; m < MC; ++m) acc[r][m] = 0.0f;
+                for (int m = 0; m < MC; ++m) accs[pass][r][m] = 0.0f;
+        for (int c = 0; c < nchunks; ++c, ++it) {
+            const int s = it % p.stages;
+            if (!mbar_wait(&full[s], (it / p.stages) & 1)) {
+                ok = false;
+                break;
+            }
+            if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(2 + 2 * it);
+            const uint8_t *rowp[RW];
+            const int u0 = c * unit_chunk, u1 = min(units, u0 + unit_chunk);
+            if (PIECES) {
+                // pieces packed back to back; the pointer is the row's virtual start, so that unit u sits at
+                // u * unit_bytes as in a whole row
+                const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
+#pragma unroll
+                for (int r = 0; r < RW; ++r)
+                    rowp[r] = tile_base + (size_t)(local0 + r) * piece_pitch - (size_t)u0 * p.unit_bytes;
+            } else {
+                const int64_t start = (int64_t)trow * p.row_bytes;
+                const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
+#pragma unroll
+                for (int r = 0; r < RW; ++r) rowp[r] = tile_base + (size_t)(local0 + r) * p.row_bytes;
+            }
             if (valid[0]) {
-                // the last pass of an odd M re-reads row m0+MC-1 == M-1 ... clamp instead: see m_hi below
-                for (int u = lig; u < units; u += lpr) {
-                    if (m0 + MC <= M) Fmt::template unit<MC, RW>(planes, m0, u, rowp, valid, acc);
-                    else Fmt::template unit<MC, RW>(planes, M - MC, u, rowp, valid, acc);  // overlap the previous pass
+#pragma unroll
+                for (int pass = 0; pass < NPASS; ++pass) {
+                    const int m0 = pass * MC;
+                    // the last pass of an odd M starts at M - MC: it overlaps the previous pass instead of running past M
+                    for (int u = u0 + lig; u < u1; u += lpr) {
+                        if (m0 + MC <= M) Fmt::template unit<MC, RW>(planes, m0, u, rowp, valid, accs[pass]);
+                        else Fmt::template unit<MC, RW>(planes, M - MC, u, rowp, valid, accs[pass]);
+                    }
                 }
             }
+            // this warp is done reading the stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(3 + 2 * it);
+        }
+        if (!ok) break;
+        float out[RW][M];
+#pragma unroll
+        for (int pass = 0; pass < NPASS; ++pass)
 #pragma unroll
             for (int r = 0; r < RW; ++r)
 #pragma unroll
                 for (int m = 0; m < MC; ++m) {
+                    const int m0 = pass * MC;
                     const int mi = (m0 + MC <= M) ? m0 + m : M - MC + m;
-                    out[r][mi] = acc[r][m];
+                    out[r][mi] = accs[pass][r][m];
                 }
-        }
-        // this warp is done reading the stage
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
-        if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(3 + 2 * it);
 
 #pragma unroll
         for (int r = 0; r < RW; ++r)
@@ -670,11 +725,14 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
             for (int r = 0; r < RW; ++r)
                 if (valid[r]) {
 #pragma unroll
-                    for (int m = 0; m < M; ++m) emit_out(p, out_s, r_begin, m, row0 + r, out[r][m]);
+                    for (int m = 0; m < M; ++m) {
+                        if (EPI == 0) p.y[(int64_t)m * p.ldy + row0 + r] = out[r][m];
+                        else emit_out(p, out_s, r_begin, m, row0 + r, out[r][m]);
+                    }
                 }
         }
     }
-    if (p.out_bytes) {
+    if (EPI != 0 && p.out_bytes) {
         const int nthreads = p.n_cwarps * 32;
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
         if (ok) flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);

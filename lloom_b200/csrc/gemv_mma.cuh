@@ -167,7 +167,7 @@ constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
 
 // Dynamic shared memory: [barriers 128 B][per-tile barriers][partial sums][act planes][staged output rows, fused
 // gather only][stage 0][stage 1]...
-template <int SPLIT>
+template <int SPLIT, int EPI = 0>
 __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *empty = reinterpret_cast<uint64_t *>(smem);
@@ -328,17 +328,28 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             out[2] += o.z;
             out[3] += o.w;
         }
-        if (t0 < p.m) {
-            if (gid < rows) emit_out(p, out_s, r_begin, t0, trow + gid, out[0]);
-            if (gid + 8 < rows) emit_out(p, out_s, r_begin, t0, trow + gid + 8, out[2]);
-        }
-        if (t1 < p.m) {
-            if (gid < rows) emit_out(p, out_s, r_begin, t1, trow + gid, out[1]);
-            if (gid + 8 < rows) emit_out(p, out_s, r_begin, t1, trow + gid + 8, out[3]);
+        if (EPI == 0) {
+            if (t0 < p.m) {
+                if (gid < rows) p.y[(int64_t)t0 * p.ldy + trow + gid] = out[0];
+                if (gid + 8 < rows) p.y[(int64_t)t0 * p.ldy + trow + gid + 8] = out[2];
+            }
+            if (t1 < p.m) {
+                if (gid < rows) p.y[(int64_t)t1 * p.ldy + trow + gid] = out[1];
+                if (gid + 8 < rows) p.y[(int64_t)t1 * p.ldy + trow + gid + 8] = out[3];
+            }
+        } else {
+            if (t0 < p.m) {
+                if (gid < rows) emit_out(p, out_s, r_begin, t0, trow + gid, out[0]);
+                if (gid + 8 < rows) emit_out(p, out_s, r_begin, t0, trow + gid + 8, out[2]);
+            }
+            if (t1 < p.m) {
+                if (gid < rows) emit_out(p, out_s, r_begin, t1, trow + gid, out[1]);
+                if (gid + 8 < rows) emit_out(p, out_s, r_begin, t1, trow + gid + 8, out[3]);
+            }
         }
         if (it == 0 || it == 5 || it == 6) LLOOM_TRACE_MARK(it == 0 ? 3 : it == 5 ? 5 : 7);
     }
-    if (p.out_bytes) {  // every consumer warp gets here, timed-out ones included
+    if (EPI != 0 && p.out_bytes) {  // every consumer warp gets here, timed-out ones included
         asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
         flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);
     }

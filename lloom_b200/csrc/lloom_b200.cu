@@ -67,9 +67,12 @@ static int64_t weight_row_bytes(int dtype, int64_t k) {
 
 // ---- GEMV launch planning ----
 
-template <class Item, int M, int RW, int CW = 8>
-static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_kernel<Item, M, RW, CW>;
+// EPI = 1 instances carry the store blocks and the fused gather; the plain forward uses the EPI = 0 instances.
+static bool gemv_needs_epi(const GemvParams &p) { return p.n_peers != 0 || p.store_mode != LLOOM_STORE_PLAIN; }
+
+template <class Item, int M, int RW, int CW, bool PIECES, int EPI>
+static cudaError_t launch_gemv_inst2(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    auto kern = gemv_kernel<Item, M, RW, CW, PIECES, EPI>;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -94,8 +97,20 @@ static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, boo
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+template <class Item, int M, int RW, int CW = 8, bool PIECES = false>
+static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    if (gemv_needs_epi(p)) return launch_gemv_inst2<Item, M, RW, CW, PIECES, 1>(p, grid, smem, overlap, stream);
+    return launch_gemv_inst2<Item, M, RW, CW, PIECES, 0>(p, grid, smem, overlap, stream);
+}
+
 template <class Fmt, int RW>
 static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    if (RW == 1 && p.nchunks > 1) {  // rows cut into pieces: side-by-side shapes with eight consumer warps, m <= 2 only
+        if (p.n_cwarps > 8) return cudaErrorInvalidValue;
+        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 8, true>(p, grid, smem, overlap, stream);
+        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 8, true>(p, grid, smem, overlap, stream);
+        return cudaErrorInvalidValue;
+    }
     if (RW == 1 && p.n_cwarps > 8) {  // twelve-consumer-warp instances exist for m <= 2 only
         if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 12>(p, grid, smem, overlap, stream);
         if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 12>(p, grid, smem, overlap, stream);
@@ -139,9 +154,9 @@ static bool gemv_shape_override(int &cw, int &rw) {
     return cached == 1;
 }
 
-template <int SPLIT>
+template <int SPLIT, int EPI>
 static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_mma_q4k_kernel<SPLIT>;
+    auto kern = gemv_mma_q4k_kernel<SPLIT, EPI>;
     static int configured_smem[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -166,8 +181,12 @@ static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem,
 static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
     // whole rows per stage: four teams of four warps, a tile each; rows cut into pieces: one team of sixteen, so
     // that a piece is consumed (and its stage handed back) as fast as possible
-    if (p.nchunks > 1) return launch_gemv_mma_inst<16>(p, grid, smem, overlap, stream);
-    return launch_gemv_mma_inst<4>(p, grid, smem, overlap, stream);
+    if (gemv_needs_epi(p)) {
+        if (p.nchunks > 1) return launch_gemv_mma_inst<16, 1>(p, grid, smem, overlap, stream);
+        return launch_gemv_mma_inst<4, 1>(p, grid, smem, overlap, stream);
+    }
+    if (p.nchunks > 1) return launch_gemv_mma_inst<16, 0>(p, grid, smem, overlap, stream);
+    return launch_gemv_mma_inst<4, 0>(p, grid, smem, overlap, stream);
 }
 
 // Development knob: LLOOM_GEMV_MMA=0 keeps 2 <= m <= 8 on the dp4a kernel.
@@ -267,6 +286,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.tile_bar_bytes = 0;
     p.chunk_sb = 0;
     p.nchunks = 1;
+    p.chunk_units = 0;
+    p.unit_bytes = w_dtype == LLOOM_Q4_K ? Q4K_BYTES : w_dtype == LLOOM_Q6_K ? Q6K_BYTES : 2 * Q8_0_BYTES;
     p.n_peers = peers ? peers->n : 0;
     p.out_bytes = 0;
     p.out_pitch = 0;
@@ -346,8 +367,25 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         const int64_t per_block = shapes[si].half ? (int64_t)(di.smem_per_sm - 2 * di.smem_reserved) / 2 / 16 * 16
                                                   : (int64_t)di.max_smem_optin;
         int64_t budget = per_block - 128 - p.act_bytes;
-        const int64_t stage = round16((int64_t)cw * groups * rw * p.row_bytes + pad);
-        if (budget < 2 * stage) continue;
+        int64_t stage = round16((int64_t)cw * groups * rw * p.row_bytes + pad);
+        p.nchunks = 1;
+        p.chunk_units = 0;
+        p.lpr_log2 = lpr_log2;
+        if (budget < 2 * stage) {
+            // Long rows in a side-by-side shape: cut the rows into pieces of 16 units (32 for Q8_0), so that a stage
+            // is 16 (8) rows x one piece -- the tile the kernel streams at K = 4096 -- instead of giving up the
+            // overlap between consecutive launches for a one-CTA-per-SM shape.
+            if (!shapes[si].half || cw > 8 || p.row_bytes % 16 != 0) continue;
+            const int cu = w_dtype == LLOOM_Q8_0 ? 32 : 16;
+            if (units <= cu || ((int64_t)cu * p.unit_bytes) % 16 != 0) continue;
+            const int cl = w_dtype == LLOOM_Q8_0 ? 5 : 4;
+            const int64_t pstage = round16((int64_t)cw * (32 >> cl) * rw * cu * p.unit_bytes + pad);
+            if (budget < 2 * pstage) continue;
+            stage = pstage;
+            p.nchunks = (int)((units + cu - 1) / cu);
+            p.chunk_units = cu;
+            p.lpr_log2 = cl;
+        }
         p.out_bytes = 0;
         p.out_pitch = 0;
         if (out_want > 0 && budget - out_want >= 2 * stage) {
