@@ -304,7 +304,7 @@ def run_gpu(args):
     achieved = WEIGHT_BYTES / (ms_gemv * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "traffic": GEMV_DRAM_TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}",
-                "kernel": "gemv_kernel<FmtQ4K, M=1, RW=1, CW=8>", "algorithmic_bytes_per_launch": WEIGHT_BYTES,
+                "kernel": "gemv_kernel<FmtQ4K, M=1, RW=1, CW=8, PIECES=false, EPI=0>", "algorithmic_bytes_per_launch": WEIGHT_BYTES,
                 "us_per_launch": round(ms_gemv * 1e3, 3)}
 
     # prefill leg (the metric's second half): whole QMatMul::forward at M = 512 and 2048 on the C4 matrix
