@@ -390,7 +390,7 @@ void QCudaStorage::embedding(int64_t rows, int64_t hidden, const uint32_t *ids, 
     status_check(lloom_b200_get_rows((int)dtype_, data_, rows, hidden, ids, n_ids, out, dev_.stream), "get_rows");
 }
 
-void QCudaStorage::fwd(int64_t n, int64_t k, const float *x, int64_t m, float *y, int64_t ldy) const {
+void QCudaStorage::fwd(int64_t n, int64_t k, const float *x, int64_t m, float *y, int64_t ldy, int store) const {
     if (n * k / block_size(dtype_) * type_size(dtype_) != len_)
         throw Error(LLOOM_ERR_SHAPE, "fwd: weight shape does not match the storage");
     const int64_t need = lloom_b200_workspace_bytes((int)dtype_, m, n, k);
@@ -406,8 +406,12 @@ void QCudaStorage::fwd(int64_t n, int64_t k, const float *x, int64_t m, float *y
         cuda_check(cudaMalloc(&ws.ptr, (size_t)grow), "cudaMalloc");
         ws.bytes = grow;
     }
-    status_check(lloom_b200_qmatmul_fwd((int)dtype_, data_, x, y, m, n, k, ldy, ws.ptr, ws.bytes, dev_.stream),
-                 "qmatmul_fwd");
+    if (store != LLOOM_STORE_PLAIN)
+        status_check(lloom_b200_qmatmul_fwd_store((int)dtype_, data_, x, y, m, n, k, ldy, store, ws.ptr, ws.bytes, dev_.stream),
+                     "qmatmul_fwd_store");
+    else
+        status_check(lloom_b200_qmatmul_fwd((int)dtype_, data_, x, y, m, n, k, ldy, ws.ptr, ws.bytes, dev_.stream),
+                     "qmatmul_fwd");
 }
 
 // ---- QTensor / QMatMul ----
@@ -457,6 +461,24 @@ void QMatMul::forward(const float *xs, const std::vector<int64_t> &xs_dims, floa
     int64_t m = 1;
     for (size_t i = 0; i + 1 < xs_dims.size(); ++i) m *= xs_dims[i];
     w_->storage().fwd(n, k, xs, m, y, n);
+}
+
+bool QMatMul::forward_store(const float *xs, const std::vector<int64_t> &xs_dims, float *y, int store) const {
+    const auto &ws = w_->shape();
+    if (ws.size() != 2 || xs_dims.size() < 2 || xs_dims.back() != ws[1]) return false;
+    int64_t m = 1;
+    for (size_t i = 0; i + 1 < xs_dims.size(); ++i) m *= xs_dims[i];
+    if (m > 8) return false;  // the store blocks serve the matvec path only
+    w_->storage().fwd(ws[0], ws[1], xs, m, y, ws[0], store);
+    return true;
+}
+
+bool QMatMul::forward_silu(const float *xs, const std::vector<int64_t> &xs_dims, float *y) const {
+    return forward_store(xs, xs_dims, y, LLOOM_STORE_SILU);
+}
+
+bool QMatMul::forward_mul_into(const float *xs, const std::vector<int64_t> &xs_dims, float *gate) const {
+    return forward_store(xs, xs_dims, gate, LLOOM_STORE_MUL_INTO);
 }
 
 }  // namespace host

@@ -62,7 +62,8 @@ class QCudaStorage {
     // cuda.rs:828-860; ids u32 on device, out f32 [n_ids, hidden] on device
     void embedding(int64_t rows, int64_t hidden, const uint32_t *ids, int64_t n_ids, float *out) const;
     // cuda.rs:862-894; weight [n,k], x f32 [m,k] contiguous on device, y f32 with row stride ldy
-    void fwd(int64_t n, int64_t k, const float *x, int64_t m, float *y, int64_t ldy) const;
+    // store: LLOOM_STORE_PLAIN, or a block on the GEMV's store (m <= 8): LLOOM_STORE_SILU, LLOOM_STORE_MUL_INTO
+    void fwd(int64_t n, int64_t k, const float *x, int64_t m, float *y, int64_t ldy, int store = 0) const;
 
   private:
     QCudaStorage(const CudaDevice &dev, GgmlDType dtype) : dev_(dev), dtype_(dtype) {}
@@ -97,9 +98,14 @@ class QMatMul {
     static QMatMul from_arc(std::shared_ptr<QTensor> w) { return QMatMul(std::move(w)); }  // mod.rs:1714-1729
     // Module::forward (mod.rs:2022-2026): xs dims [.., k] contiguous f32 on device -> y dims [.., n]
     void forward(const float *xs, const std::vector<int64_t> &xs_dims, float *y) const;
+    // mod.rs:2105-2155: silu(W.x) / gate <- gate * (W.x) on the GEMV's store.  false where the store block does not
+    // serve (more than 8 rows): the caller composes, as with the reference's None.
+    bool forward_silu(const float *xs, const std::vector<int64_t> &xs_dims, float *y) const;
+    bool forward_mul_into(const float *xs, const std::vector<int64_t> &xs_dims, float *gate) const;
     const QTensor &weight() const { return *w_; }
 
   private:
+    bool forward_store(const float *xs, const std::vector<int64_t> &xs_dims, float *y, int store) const;
     std::shared_ptr<QTensor> w_;
 };
 
