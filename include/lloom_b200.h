@@ -32,8 +32,11 @@ extern "C" {
 #define LLOOM_B200_VERSION 100
 
 /* GgmlDType ids (mod.rs:505-568): only these are implemented; anything else returns LLOOM_ERR_DTYPE. */
+#define LLOOM_Q4_0 2
+#define LLOOM_Q5_0 6
 #define LLOOM_Q8_0 8
 #define LLOOM_Q4_K 12
+#define LLOOM_Q5_K 13
 #define LLOOM_Q6_K 14
 #define LLOOM_Q8_K 15 /* activation-only */
 
@@ -56,9 +59,15 @@ int lloom_b200_version(void);
 const char *lloom_b200_error_string(int status);
 /* The cudaError_t of the last LLOOM_ERR_LAUNCH on this thread (0 if none). */
 int lloom_b200_last_cuda_error(void);
-/* Reads (synchronously) and clears the device-side status word: 0, or LLOOM_ERR_TIMEOUT
- * when a bounded mbarrier wait inside a kernel gave up.  For tests and post-mortems. */
+/* Reads and clears (one atomic exchange on the device, then a synchronous copy) the status word of the
+ * current device: 0, or LLOOM_ERR_TIMEOUT when a bounded wait inside a kernel gave up since the last call.
+ * One word per device serves every stream.  For tests and post-mortems; safe to call from several host threads. */
 int lloom_b200_device_status(int *status_out);
+/* Time limit of every bounded device-side wait (mbarrier waits inside the kernels, the cross-GPU flag waits) on the
+ * current device, in nanoseconds; 0 restores the default of 2 s.  A wait that runs out sets the status word to
+ * LLOOM_ERR_TIMEOUT and the kernel unwinds by itself (no trap; the context stays usable).  Synchronous; call it
+ * between launches.  (The reference has no counterpart: its kernels never wait on one another.) */
+int lloom_b200_set_wait_limit_ns(uint64_t ns);
 
 /* Launch overlap for the decode GEMV (off by default; returns the previous setting).  When on, GEMV
  * launches carry the programmatic-stream-serialization attribute: a GEMV may start streaming its
@@ -82,6 +91,22 @@ int64_t lloom_b200_act_row_bytes(int w_dtype, int64_t k);
  * fast_mmvq.rs:44-81 / fast_mmq.rs:135-174; the caller owns it.  256-byte aligned. */
 int64_t lloom_b200_workspace_bytes(int w_dtype, int64_t m, int64_t n, int64_t k);
 
+/* ---- Prebuilt weight images for the prefill GEMM ----
+ * The tensor-core GEMM reads the weights as f16 operand images (exact integers: scale x code).  By default every
+ * call with m > 8 builds them in its workspace, slab by slab; a caller that runs many prefill calls on the same
+ * weights can build the image once into a buffer it owns (about 3.6x the Q4_K bytes, 3.8x Q8_0, 4.9x Q6_K) and
+ * pass it to lloom_b200_qmatmul_fwd_image, which then needs only lloom_b200_workspace_bytes_with_image.
+ * (The reference re-quantizes activations per call but keeps no second weight form; 180 GB of HBM per GPU is
+ * what makes the second form affordable here.)  image: 1024-byte aligned.  0 bytes = no GEMM for this type/shape. */
+int64_t lloom_b200_weight_image_bytes(int w_dtype, int64_t n, int64_t k);
+int lloom_b200_weight_image_build(int w_dtype, const void *w_blocks, int64_t n, int64_t k, void *image, int64_t image_bytes,
+                                  void *stream);
+int64_t lloom_b200_workspace_bytes_with_image(int w_dtype, int64_t m, int64_t n, int64_t k);
+/* lloom_b200_qmatmul_fwd with the weight image prebuilt (w_image == NULL: exactly lloom_b200_qmatmul_fwd). */
+int lloom_b200_qmatmul_fwd_image(int w_dtype, const void *w_blocks, const void *w_image, const float *x, float *y,
+                                 int64_t m, int64_t n, int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes,
+                                 void *stream);
+
 /* Activation quantizer: x f32 [m,k] contiguous -> canonical Q8_0 / Q8_K blocks [m][k/block],
  * bit-exact with BlockQ8_0::from_float (k_quants.rs:738-767) / BlockQ8K::from_float
  * (k_quants.rs:2400-2438).  Replaces launch_mmvq_gguf_quantize_q8_1_f32 (ffi.rs:412) and
@@ -95,8 +120,10 @@ int lloom_b200_gemv(int w_dtype, const void *w_blocks, const void *act_blocks, f
                     int64_t k, int64_t ldy, void *stream);
 
 /* Prefill GEMM, any m >= 1 (meant for m > 8): same result definition as the GEMV
- * (matmul m > 1 arm, k_quants.rs:2518-2585).  Q4_K runs on tcgen05 tensor cores.
- * Replaces launch_mmq_gguf_* (ffi.rs:583).  `workspace` as sized by lloom_b200_workspace_bytes. */
+ * (matmul m > 1 arm, k_quants.rs:2518-2585).  Q4_K, Q6_K and Q8_0 (k a multiple of 128) run on tcgen05 tensor
+ * cores; other shapes fall to slabs of eight rows through the GEMV.
+ * Replaces launch_mmq_gguf_* (ffi.rs:583).  `workspace`: lloom_b200_workspace_bytes minus the activation blocks
+ * (passing a buffer of the full lloom_b200_workspace_bytes is always enough). */
 int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,
                     int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream);
 
@@ -155,6 +182,20 @@ int lloom_b200_qmatmul_fwd_store(int w_dtype, const void *w_blocks, const float 
                                  int64_t k, int64_t ldy, int store, void *workspace, int64_t workspace_bytes,
                                  void *stream);
 
+/* ---- Grouped decode forward: several weight matrices that share one activation, one launch ----
+ * The reference's callers run gate|up (lloom/src/models/quantized_lfm2.rs:20-23) and q|k|v as separate
+ * QMatMul::forward calls on the same input; each pays a launch and re-quantizes the activations.  This entry
+ * streams up to LLOOM_B200_MAX_GROUP matrices of one dtype and one k, in the order given, with one activation read:
+ * for one activation row (and two rows of the formats without a tensor-core GEMV) a single persistent launch walks
+ * the concatenated rows; for wider batches the activations are quantized once and each matrix gets its GEMV launch.
+ * ys[g] f32 [m][ldys[g]], ns[g] rows of matrix g, stores[g] one of LLOOM_STORE_* (NULL = all plain; MUL_INTO reads
+ * and writes ys[g]).  Each matrix's result is bit-identical to its own lloom_b200_qmatmul_fwd.  m <= 8.
+ * workspace: lloom_b200_workspace_bytes(w_dtype, m, max ns, k). */
+#define LLOOM_B200_MAX_GROUP 4
+int lloom_b200_qmatmul_fwd_group(int w_dtype, int n_mats, const void *const *w_blocks, const float *x, float *const *ys,
+                                 const int64_t *ns, const int64_t *ldys, const int *stores, int64_t m, int64_t k,
+                                 void *workspace, int64_t workspace_bytes, void *stream);
+
 /* ---- Row-sharded forward with the all-gather fused into the GEMV (one node, up to 8 GPUs) ----
  *
  * The reference shards nothing on this path; the sharded layer here (rank g owns rows [g*ceil(n/G), ...), the
@@ -176,6 +217,26 @@ int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float 
  * of every GPU, mapped into this process.  Bounded wait: LLOOM_ERR_TIMEOUT shows in lloom_b200_device_status. */
 #define LLOOM_B200_PEER_FLAG_WORDS 16
 int lloom_b200_peer_barrier(int rank, int n_peers, unsigned int *const *flag_peers, void *stream);
+/* The same gather with the barrier folded into the GEMV: the last CTA to finish on each GPU publishes that GPU's
+ * call counter into slot [rank] of every GPU's flag array (after a system-scope fence behind its peer stores), so no
+ * barrier kernel runs between the GEMV and its consumer.  The consumer waits (bounded) until all n_peers slots of its
+ * own flag array have reached its own counter: either lloom_b200_peer_wait on the same stream, or the next forward
+ * on the gathered rows itself -- pass the gather's own-GPU flag array as `wait_flags` to the next
+ * lloom_b200_qmatmul_fwd_gather_sync / lloom_b200_qmatmul_fwd_after_gather (m <= 2: the wait then sits in the GEMV's
+ * quantizer prologue, behind its weight prefetch).  A flag array serves one gathered buffer pair on one stream; words
+ * [8] and [9] of it are the GPU's call counter and CTA arrival counter.  flag_peers as for lloom_b200_peer_barrier
+ * (do not mix the two protocols on one flag array).  wait_flags may be NULL. */
+int lloom_b200_qmatmul_fwd_gather_sync(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard,
+                                       int64_t k, int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, int rank,
+                                       unsigned int *const *flag_peers, const unsigned int *wait_flags, void *workspace,
+                                       int64_t workspace_bytes, void *stream);
+/* An ordinary (replicated) decode forward whose activations are the output of a gather_sync: waits on that gather's
+ * flags in its prologue.  m <= 2. */
+int lloom_b200_qmatmul_fwd_after_gather(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                                        int64_t k, int64_t ldy, const unsigned int *wait_flags, int n_peers,
+                                        void *workspace, int64_t workspace_bytes, void *stream);
+/* One-warp kernel that waits (bounded) for the last gather_sync on this stream to be complete on this GPU. */
+int lloom_b200_peer_wait(int n_peers, const unsigned int *flags_own, void *stream);
 /* Set-up helpers (not on the forward path; these do allocate / synchronise): a zeroed device buffer other processes
  * of the node can map, its 64-byte CUDA IPC handle, mapping a peer's handle, and the matching releases. */
 int lloom_b200_peer_alloc(int64_t bytes, void **ptr);

@@ -21,6 +21,17 @@ SYMBOLS = [
     ("lloom_b200_last_cuda_error", _int, []),
     ("lloom_b200_device_status", _int, [C.POINTER(_int)]),
     ("lloom_b200_set_launch_overlap", _int, [_int]),
+    ("lloom_b200_set_wait_limit_ns", _int, [C.c_uint64]),
+    ("lloom_b200_weight_image_bytes", _i64, [_int, _i64, _i64]),
+    ("lloom_b200_weight_image_build", _int, [_int, _vp, _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_workspace_bytes_with_image", _i64, [_int, _i64, _i64, _i64]),
+    ("lloom_b200_qmatmul_fwd_image", _int, [_int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd_group", _int, [_int, _int, C.POINTER(_vp), _vp, C.POINTER(_vp), C.POINTER(_i64),
+                                            C.POINTER(_i64), C.POINTER(_int), _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd_gather_sync", _int, [_int, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(_vp), _int, _int,
+                                                  C.POINTER(_vp), _vp, _vp, _i64, _vp]),
+    ("lloom_b200_qmatmul_fwd_after_gather", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _vp, _i64, _vp]),
+    ("lloom_b200_peer_wait", _int, [_int, _vp, _vp]),
     ("lloom_b200_block_elems", _i64, [_int]),
     ("lloom_b200_block_bytes", _i64, [_int]),
     ("lloom_b200_act_dtype", _int, [_int]),

@@ -40,21 +40,44 @@ def is_stale() -> bool:
     return any(os.path.getmtime(s) > t for s in sources())
 
 
+def translation_units() -> list[str]:
+    """Every .cu / .cpp under csrc/: the kernels are split over several units so that they compile in parallel."""
+    out = []
+    for root, _, files in os.walk(SRC_DIR):
+        out += [os.path.join(root, f) for f in files if f.endswith((".cu", ".cpp"))]
+    return sorted(out)
+
+
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile every CUDA source of the package into one shared library; returns its path."""
+    """Compile every CUDA source of the package (one object per translation unit, in parallel) and link them
+    into one shared library; returns its path."""
     if not force and not is_stale():
         return LIB_PATH
-    units = [os.path.join(SRC_DIR, "lloom_b200.cu"), os.path.join(SRC_DIR, "host", "qcuda_storage.cpp")]
-    units = [u for u in units if os.path.exists(u)]
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB_PATH, *units]
+    from concurrent.futures import ThreadPoolExecutor
+
+    obj_dir = os.path.join(_PKG, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    compile_flags = [f for f in NVCC_FLAGS if f != "--shared"]
+
+    def compile_unit(src: str) -> tuple[str, str]:
+        obj = os.path.join(obj_dir, os.path.basename(src) + ".o")
+        cmd = [_nvcc(), *compile_flags, "-c", src, "-o", obj]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        return obj, res.stderr
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        results = list(pool.map(compile_unit, translation_units()))
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
+        for _, log in results:
+            print(log)
+    cmd = [_nvcc(), "--shared", "-o", LIB_PATH, *[obj for obj, _ in results]]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
+        raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
     return LIB_PATH
 
 

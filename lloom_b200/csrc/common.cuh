@@ -22,9 +22,36 @@ constexpr int Q8K_BYTES = 292;
 // Q6_K : u8 ql[128] @0, u8 qh[64] @128, i8 scales[16] @192, f16 d @208
 // Q8_K : f32 d @0, i8 qs[256] @4, i16 bsums[16] @260
 
-// Device-side status word: 0, or LLOOM_ERR_TIMEOUT once a bounded wait gave up.
-// (The library is one translation unit, so this definition is unique.)
-__device__ int g_device_status = 0;
+// Device-side status word: 0, or LLOOM_ERR_TIMEOUT once a bounded wait gave up, and the time limit of those
+// waits.  The library is several translation units compiled without relocatable device code, so each unit has
+// its own copy of both; LLOOM_TU_REGISTER (below) hands the host-side accessors of a unit's copies to the ABI
+// unit, which reads / writes all of them (lloom_b200_device_status, lloom_b200_set_wait_limit_ns).
+static __device__ int g_device_status = 0;
+static __device__ int g_status_fetch = 0;  // landing place of the atomic read-and-clear
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // 2 s
+static __device__ unsigned long long g_wait_limit_ns = kDefaultWaitNs;
+
+struct TuHooks {
+    cudaError_t (*fetch_status)(int *status, cudaStream_t stream);  // read-and-clear, atomic on the device
+    cudaError_t (*set_wait_limit)(unsigned long long ns);
+};
+void register_tu(const TuHooks &hooks);  // lloom_b200.cu
+
+static __global__ void status_fetch_kernel() { g_status_fetch = atomicExch(&g_device_status, 0); }
+
+#define LLOOM_TU_REGISTER()                                                                                    \
+    namespace {                                                                                                \
+    cudaError_t tu_fetch_status(int *status, cudaStream_t stream) {                                            \
+        status_fetch_kernel<<<1, 1, 0, stream>>>();                                                            \
+        cudaError_t e = cudaGetLastError();                                                                    \
+        if (e != cudaSuccess) return e;                                                                        \
+        return cudaMemcpyFromSymbol(status, g_status_fetch, sizeof(int));                                      \
+    }                                                                                                          \
+    cudaError_t tu_set_wait_limit(unsigned long long ns) {                                                     \
+        return cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns));                                           \
+    }                                                                                                          \
+    const int tu_registered = (::lloom::register_tu({tu_fetch_status, tu_set_wait_limit}), 0);                 \
+    }
 
 __host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
@@ -62,7 +89,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // bound).  On expiry the status word is set and false is returned; the caller unwinds (no trap, the
 // context stays usable).
 constexpr uint32_t kMaxSpins = 1u << 24;
-constexpr unsigned long long kMaxWaitNs = 2000000000ull;  // 2 s
+__device__ __forceinline__ unsigned long long wait_limit_ns() { return *(volatile unsigned long long *)&g_wait_limit_ns; }
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -75,7 +102,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
         if ((i & 255) == 255) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kMaxWaitNs) break;
+            else if (now - t0 > wait_limit_ns()) break;
             __nanosleep(64);
         }
     }

@@ -1,0 +1,422 @@
+// Prefill GEMM for Q8_0 and Q6_K weights on tcgen05 tensor cores (sm_100a), exact-integer formulation.
+//
+//   Q8_0 x Q8_0 (k_quants.rs:800-818, avx.rs:71-87):     y[m,n] = sum over 32-element blocks b of (d_w[n,b]*d_a[m,b]) * dot32(q_w, q_a)
+//   Q6_K x Q8_K (k_quants.rs:2115-2172, avx.rs:131-216):  y[m,n] = sum over superblocks b of (d_a[m,b]*d_w[n,b]) * S,
+//                                                         S = sum_{j<16} sc_j * dot16(q6_j - 32, q8_j)
+// through the m > 1 arm of k_quants::matmul (k_quants.rs:2518-2585).
+//
+// The block sums are integer contractions, so they run on the tensor cores (kind::f16, f32 accumulators in tensor
+// memory) with every operand an integer that f16 represents exactly:
+//   Q8_0: A = q_w, B = q_a (|.| <= 127); one accumulator drain per 32 of K, where the two f16 block scales meet.
+//   Q6_K: v = sc_j * (q6 - 32) has up to 13 significant bits, so it is split v = hi + lo with lo = v mod 64 in
+//         [0, 63] and hi a multiple of 64 in [-4096, 4032]: both exact in f16.  The two planes multiply the same
+//         B = q8 codes and add into the same accumulator, which then holds S itself; one drain per 256 of K.
+// The kernel is the Q4_K GEMM's frame (gemm_q4k.cuh) with the drain group and the plane count as parameters:
+// 128 x 128 output tile per CTA; operands arrive as ready-made 128-byte-swizzled K-major images by bulk copies;
+// four 128-column accumulators in tensor memory, so the drain of group g overlaps the MMAs of g+1..g+3.
+// Warp roles: 0-7 epilogue, 8 operand copies, 9 MMA issuer (one elected lane), 10 activation-scale copies.
+// All waits are bounded and abortable; tensor memory is released on every path.
+#pragma once
+
+#include "gemm_q4k.cuh"
+
+namespace lloom {
+
+template <int GROUP_K, int PLANES>
+struct PlanesCfg {
+    static constexpr int kGroupK = GROUP_K;            // K elements per accumulator drain
+    static constexpr int kPlanes = PLANES;             // f16 images per weight element
+    static constexpr int kStageK = PLANES == 1 ? 128 : 64;  // K elements per pipeline stage
+    static constexpr int kStages = PLANES == 1 ? 3 : 4;
+    static constexpr int kAtomsPerStage = kStageK / 64;
+    static constexpr int kStageABytes = kAtomsPerStage * PLANES * kGemmAtomBytes;
+    static constexpr int kStageBBytes = kAtomsPerStage * kGemmAtomBytes;
+    static constexpr int kAccBufs = 4;
+    // shared memory map (offsets from a 1024-byte aligned base)
+    static constexpr int kOffA = 0;
+    static constexpr int kOffB = kOffA + kStages * kStageABytes;
+    static constexpr int kOffDa = kOffB + kStages * kStageBBytes;
+    static constexpr int kOffBars = kOffDa + kAccBufs * kGemmDaBytes;
+    static constexpr int kNumBars = 2 * kStages + 3 * kAccBufs;
+    static constexpr int kOffMisc = kOffBars + kNumBars * 8;
+    static constexpr int kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
+};
+
+constexpr int kPlanesThreads = 352;  // 8 epilogue warps + operand copies + MMA issuer + scale copies
+
+// Operand images: activation side [m-tile][k/64 atoms][16 KB] + scales [m-tile][k/GROUP_K][128] f32;
+// weight side [n-tile][k/64 atoms][PLANES][16 KB].
+struct PlanesActLayout {
+    int64_t bimg, dat, total;
+};
+__host__ __device__ inline PlanesActLayout planes_act_layout(int64_t m, int64_t k, int group_k) {
+    PlanesActLayout s;
+    const int64_t mt = gemm_m_tiles(m);
+    s.bimg = 0;
+    s.dat = mt * (k / 64) * kGemmAtomBytes;
+    s.total = (s.dat + mt * (k / group_k) * kGemmDaBytes + 1023) / 1024 * 1024;
+    return s;
+}
+__host__ __device__ inline int64_t planes_weight_bytes(int64_t n, int64_t k, int planes) {
+    return (n + kGemmBN - 1) / kGemmBN * (k / 64) * planes * kGemmAtomBytes;
+}
+
+__device__ __forceinline__ uint32_t f16x2_from_ints(int a, int b) {
+    const __half2 h = __halves2half2(__int2half_rn(a), __int2half_rn(b));
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// Canonical activation blocks -> B image + scale plane.  One CTA per (m-tile, 64-element atom of K), one thread
+// per token of the tile.  ACT_Q8_0: 34-byte Q8_0 blocks (f16 d, 32 codes); else 292-byte Q8_K blocks (f32 d, 256 codes).
+template <bool ACT_Q8_0>
+__global__ void __launch_bounds__(128) planes_prep_kernel(const uint8_t *__restrict__ act, int m, int k,
+                                                          uint8_t *__restrict__ scratch) {
+    const int atoms = k / 64;
+    const int mt = blockIdx.x / atoms, atom = blockIdx.x % atoms;
+    const int t = threadIdx.x, row = mt * kGemmBM + t;
+    const int group_k = ACT_Q8_0 ? 32 : 256;
+    const PlanesActLayout lay = planes_act_layout(m, k, group_k);
+    uint8_t *img = scratch + lay.bimg + ((int64_t)mt * atoms + atom) * kGemmAtomBytes;
+    float *dat = reinterpret_cast<float *>(scratch + lay.dat) + (int64_t)mt * (k / group_k) * 128;
+    int q[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) q[i] = 0;
+    if (row < m) {
+        if (ACT_Q8_0) {
+            const uint8_t *blk = act + ((int64_t)row * (k / 32) + atom * 2) * Q8_0_BYTES;  // 2-byte aligned
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const unsigned short *p16 = reinterpret_cast<const unsigned short *>(blk + h * Q8_0_BYTES);
+                dat[(atom * 2 + h) * 128 + t] = f16_bits_to_f32(p16[0]);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const unsigned short w = p16[1 + i];
+                    q[h * 32 + 2 * i] = (int)(int8_t)(w & 0xff);
+                    q[h * 32 + 2 * i + 1] = (int)(int8_t)(w >> 8);
+                }
+            }
+        } else {
+            const uint8_t *blk = act + ((int64_t)row * (k / 256) + (atom >> 2)) * Q8K_BYTES;  // 4-byte aligned
+            if ((atom & 3) == 0) dat[(atom >> 2) * 128 + t] = *reinterpret_cast<const float *>(blk);
+            const uint32_t *p32 = reinterpret_cast<const uint32_t *>(blk + 4 + (atom & 3) * 64);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t w = p32[i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) q[4 * i + j] = (int)(int8_t)(w >> (8 * j));
+            }
+        }
+    } else {
+        if (ACT_Q8_0) {
+            dat[(atom * 2) * 128 + t] = 0.0f;
+            dat[(atom * 2 + 1) * 128 + t] = 0.0f;
+        } else if ((atom & 3) == 0) {
+            dat[(atom >> 2) * 128 + t] = 0.0f;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const uint4 out = make_uint4(f16x2_from_ints(q[8 * c], q[8 * c + 1]), f16x2_from_ints(q[8 * c + 2], q[8 * c + 3]),
+                                     f16x2_from_ints(q[8 * c + 4], q[8 * c + 5]), f16x2_from_ints(q[8 * c + 6], q[8 * c + 7]));
+        *reinterpret_cast<uint4 *>(img + sw128_offset(t, 8 * c)) = out;
+    }
+}
+
+// Q8_0 weight blocks -> A image (one plane: the codes as f16).  One CTA per (n-tile, 64-element atom), one thread
+// per weight row; rows past n are zero.  `row0` is the first row of the image's slab within the matrix.
+__global__ void __launch_bounds__(128) planes_expand_q8_0_kernel(const uint8_t *__restrict__ w, int64_t row0, int n_end,
+                                                                 int k, uint8_t *__restrict__ image) {
+    const int atoms = k / 64;
+    const int nt = blockIdx.x / atoms, atom = blockIdx.x % atoms;
+    const int r = threadIdx.x;
+    const int64_t row = row0 + (int64_t)nt * kGemmBN + r;
+    uint8_t *img = image + ((int64_t)nt * atoms + atom) * kGemmAtomBytes;
+    int q[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) q[i] = 0;
+    if (row < n_end) {
+        const uint8_t *blk = w + (row * (k / 32) + atom * 2) * Q8_0_BYTES;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const unsigned short *p16 = reinterpret_cast<const unsigned short *>(blk + h * Q8_0_BYTES);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const unsigned short v = __ldg(p16 + 1 + i);
+                q[h * 32 + 2 * i] = (int)(int8_t)(v & 0xff);
+                q[h * 32 + 2 * i + 1] = (int)(int8_t)(v >> 8);
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const uint4 out = make_uint4(f16x2_from_ints(q[8 * c], q[8 * c + 1]), f16x2_from_ints(q[8 * c + 2], q[8 * c + 3]),
+                                     f16x2_from_ints(q[8 * c + 4], q[8 * c + 5]), f16x2_from_ints(q[8 * c + 6], q[8 * c + 7]));
+        *reinterpret_cast<uint4 *>(img + sw128_offset(r, 8 * c)) = out;
+    }
+}
+
+// Q6_K weight blocks -> A image, two planes per atom: hi = v - (v mod 64), lo = v mod 64 with v = sc_j * (q6 - 32)
+// (k_quants.rs:2327-2358 for the code layout).  One CTA per (n-tile, 64-element atom), one thread per weight row.
+__global__ void __launch_bounds__(128) planes_expand_q6k_kernel(const uint8_t *__restrict__ w, int64_t row0, int n_end,
+                                                                int k, uint8_t *__restrict__ image) {
+    const int atoms = k / 64;
+    const int nt = blockIdx.x / atoms, atom = blockIdx.x % atoms;
+    const int r = threadIdx.x;
+    const int64_t row = row0 + (int64_t)nt * kGemmBN + r;
+    uint8_t *img_hi = image + (((int64_t)nt * atoms + atom) * 2) * kGemmAtomBytes;
+    uint8_t *img_lo = img_hi + kGemmAtomBytes;
+    const int a = atom & 3;         // atom of the superblock: elements 64a .. 64a+63
+    const int h = a >> 1;           // half of the superblock
+    const int gq0 = (a & 1) * 2;    // element e = 128h + 32gq + l: this atom holds gq0 (l = 0..31) and gq0 + 1
+    int v[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = 0;
+    if (row < n_end) {
+        const uint8_t *blk = w + (row * (k / 256) + (atom >> 2)) * Q6K_BYTES;  // 2-byte aligned
+        const unsigned short *ql16 = reinterpret_cast<const unsigned short *>(blk + 64 * h);
+        const unsigned short *qh16 = reinterpret_cast<const unsigned short *>(blk + 128 + 32 * h);
+        const unsigned short *sc16 = reinterpret_cast<const unsigned short *>(blk + 192 + 8 * h);
+        int sc[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const unsigned short s2 = __ldg(sc16 + i);
+            sc[2 * i] = (int)(int8_t)(s2 & 0xff);
+            sc[2 * i + 1] = (int)(int8_t)(s2 >> 8);
+        }
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi) {
+            const int gq = gq0 + gi;  // gq 0: ql[l] low nibble, 1: ql[l+32] low, 2: ql[l] high, 3: ql[l+32] high
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {  // two elements l = 2i, 2i+1 per 16-bit load
+                const unsigned short lw = __ldg(ql16 + ((gq & 1) * 32 + 2 * i) / 2);
+                const unsigned short hw = __ldg(qh16 + i);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int l = 2 * i + j;
+                    const int lb = (lw >> (8 * j)) & 0xff, hb = (hw >> (8 * j)) & 0xff;
+                    const int lo4 = (gq & 2) ? (lb >> 4) : (lb & 0xF);
+                    const int code = (lo4 | (((hb >> (2 * gq)) & 3) << 4)) - 32;
+                    v[gi * 32 + l] = sc[(l >> 4) + 2 * gq] * code;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        int lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo[i] = v[8 * c + i] & 63;
+            hi[i] = v[8 * c + i] - lo[i];
+        }
+        const int off = sw128_offset(r, 8 * c);
+        *reinterpret_cast<uint4 *>(img_hi + off) = make_uint4(f16x2_from_ints(hi[0], hi[1]), f16x2_from_ints(hi[2], hi[3]),
+                                                              f16x2_from_ints(hi[4], hi[5]), f16x2_from_ints(hi[6], hi[7]));
+        *reinterpret_cast<uint4 *>(img_lo + off) = make_uint4(f16x2_from_ints(lo[0], lo[1]), f16x2_from_ints(lo[2], lo[3]),
+                                                              f16x2_from_ints(lo[4], lo[5]), f16x2_from_ints(lo[6], lo[7]));
+    }
+}
+
+struct PlanesParams {
+    const uint8_t *w;        // canonical weight blocks of the whole matrix (for the per-group f16 scales)
+    const uint8_t *act_img;  // planes_prep_kernel output
+    const uint8_t *w_img;    // expand kernel output for rows [row0, row0 + n_tiles * 128)
+    float *y;
+    int64_t ldy;
+    int64_t row_bytes;
+    int64_t row0;   // first weight row of this launch (a slab of the matrix)
+    int m, n_end, k;  // n_end: rows of the whole matrix (rows >= n_end are masked)
+    int n_tiles, m_tiles;
+    int scale_stride, scale_off;  // weight scale of group g of a row: f16 at row + g * scale_stride + scale_off
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const PlanesParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::kOffBars);
+    uint64_t *full = bars, *empty = bars + Cfg::kStages;
+    uint64_t *acc_full = bars + 2 * Cfg::kStages, *acc_empty = acc_full + Cfg::kAccBufs, *da_full = acc_empty + Cfg::kAccBufs;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + Cfg::kOffMisc);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::kOffMisc + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // m-tiles of one n-tile are neighbours in launch order, so the n-tile's A images are shared through L2
+    const int mt = blockIdx.x % p.m_tiles, nt = blockIdx.x / p.m_tiles;
+    const int m0 = mt * kGemmBM;
+    const int64_t n0 = p.row0 + (int64_t)nt * kGemmBN;
+    const int atoms = p.k / 64;
+    const int ngroups = p.k / Cfg::kGroupK;
+    const int nstages = p.k / Cfg::kStageK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int i = 0; i < Cfg::kAccBufs; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], kGemmEpiWarps);
+            mbar_init(&da_full[i], 1);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == kGemmEpiWarps + 1) {  // tensor memory: all 512 columns, four 128-column accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < kGemmEpiWarps) {
+        // ------------------------------ epilogue ------------------------------
+        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 64*(w/4)..
+        const int q = warp & 3, half = warp >> 2;
+        const int r = q * 32 + lane;  // row of the tile == TMEM lane
+        const int64_t n = n0 + r;
+        const bool row_ok = n < p.n_end;
+        const uint8_t *wrow = p.w + (row_ok ? n : 0) * p.row_bytes + p.scale_off;
+        uint64_t out2[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) out2[j] = 0ull;
+        unsigned short hdr_next = row_ok ? __ldg(reinterpret_cast<const unsigned short *>(wrow)) : (unsigned short)0;
+        bool ok = true;
+        for (int g = 0; g < ngroups && ok; ++g) {
+            const int buf = g % Cfg::kAccBufs;
+            const uint32_t par = (g / Cfg::kAccBufs) & 1;
+            const unsigned short hdr = hdr_next;
+            if (g + 1 < ngroups && row_ok)
+                hdr_next = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)(g + 1) * p.scale_stride));
+            const float dw = f16_bits_to_f32(hdr);
+            const uint64_t dw2 = pack2f(dw, dw);
+            ok = mbar_wait_abortable<64>(&da_full[buf], par, abort_flag) && mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + half * 64);
+            uint32_t va[32], vb[32];
+            tmem_ld32(t_main, va);
+            tmem_ld32(t_main + 32, vb);
+            // the 64 activation scales of this warp's columns, as f32 pairs, times the weight scale: (d_a * d_w)
+            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + Cfg::kOffDa + buf * kGemmDaBytes + half * 256);
+            uint64_t d2[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const ulonglong2 t = dap[j];
+                d2[2 * j] = mul_f32x2(t.x, dw2);
+                d2[2 * j + 1] = mul_f32x2(t.y, dw2);
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                out2[j] = fma_f32x2(d2[j], (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[j]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const ulonglong2 t = dap[8 + j];
+                d2[2 * j] = mul_f32x2(t.x, dw2);
+                d2[2 * j + 1] = mul_f32x2(t.y, dw2);
+            }
+            // everything this warp needs from tensor memory and from the scale tile is in registers now
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                out2[16 + j] = fma_f32x2(d2[j], (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[16 + j]);
+        }
+        if (ok && row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int mrow = m0 + half * 64 + 2 * j;
+                if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] & 0xffffffffu));
+                if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
+            }
+        }
+    } else if (warp == kGemmEpiWarps) {
+        // ------------------------------ operand tiles: bulk copies ------------------------------
+        // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
+        const uint8_t *aimg = p.w_img + (int64_t)nt * atoms * Cfg::kPlanes * kGemmAtomBytes;
+        const uint8_t *bimg = p.act_img + (int64_t)mt * atoms * kGemmAtomBytes;
+        bool ok = true;
+        for (int it = 0; it < nstages && ok; ++it) {
+            const int s = it % Cfg::kStages;
+            if (it >= Cfg::kStages) ok = mbar_wait_abortable<32>(&empty[s], ((it / Cfg::kStages) - 1) & 1, abort_flag);
+            if (!ok) break;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&full[s], Cfg::kStageABytes + Cfg::kStageBBytes);
+                bulk_g2s(smem + Cfg::kOffA + s * Cfg::kStageABytes, aimg + (int64_t)it * Cfg::kStageABytes, Cfg::kStageABytes, &full[s]);
+                bulk_g2s(smem + Cfg::kOffB + s * Cfg::kStageBBytes, bimg + (int64_t)it * Cfg::kStageBBytes, Cfg::kStageBBytes, &full[s]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == kGemmEpiWarps + 2) {
+        // ------------------------------ activation scales of each drain group ------------------------------
+        const PlanesActLayout lay = planes_act_layout(p.m, p.k, Cfg::kGroupK);
+        const uint8_t *dat = p.act_img + lay.dat + (int64_t)mt * ngroups * kGemmDaBytes;
+        bool ok = true;
+        for (int g = 0; g < ngroups && ok; ++g) {
+            const int buf = g % Cfg::kAccBufs;
+            if (g >= Cfg::kAccBufs) ok = mbar_wait_abortable<32>(&acc_empty[buf], ((g / Cfg::kAccBufs) - 1) & 1, abort_flag);
+            if (!ok) break;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&da_full[buf], kGemmDaBytes);
+                bulk_g2s(smem + Cfg::kOffDa + buf * kGemmDaBytes, dat + (int64_t)g * kGemmDaBytes, kGemmDaBytes, &da_full[buf]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == kGemmEpiWarps + 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        // The whole warp walks the loop; lane 0 issues the MMAs and commits.
+        // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(kGemmBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
+        constexpr int kStepsPerStage = Cfg::kStageK / 16;
+        constexpr int kStepsPerGroup = Cfg::kGroupK / 16;
+        bool ok = true;
+        for (int it = 0; it < nstages && ok; ++it) {
+            const int s = it % Cfg::kStages;
+            ok = mbar_wait_abortable<0>(&full[s], (it / Cfg::kStages) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(smem + Cfg::kOffA + s * Cfg::kStageABytes);
+            const uint32_t b_addr = smem_u32(smem + Cfg::kOffB + s * Cfg::kStageBBytes);
+#pragma unroll
+            for (int kk = 0; kk < kStepsPerStage; ++kk) {  // K = 16 per instruction: atom kk/4, 32 bytes along its swizzled row
+                const int step = it * kStepsPerStage + kk;
+                const int g = step / kStepsPerGroup, in_group = step % kStepsPerGroup;
+                const int buf = g % Cfg::kAccBufs;
+                if (in_group == 0 && g >= Cfg::kAccBufs) {
+                    ok = mbar_wait_abortable<0>(&acc_empty[buf], ((g / Cfg::kAccBufs) - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                if (lane == 0) {
+                    const uint32_t d_acc = tmem_base + (uint32_t)(buf * 128);
+                    const uint32_t boff = (uint32_t)((kk >> 2) * kGemmAtomBytes + (kk & 3) * 32);
+#pragma unroll
+                    for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
+                        const uint32_t aoff = (uint32_t)(((kk >> 2) * Cfg::kPlanes + pl) * kGemmAtomBytes + (kk & 3) * 32);
+                        umma_f16(d_acc, umma_desc(a_addr + aoff, 16, 1024, 2), umma_desc(b_addr + boff, 16, 1024, 2), idesc,
+                                 (in_group | pl) != 0 ? 1u : 0u);
+                    }
+                    if (in_group == kStepsPerGroup - 1) umma_commit(&acc_full[buf]);
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(&empty[s]);
+            __syncwarp();
+        }
+    }
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kGemmEpiWarps + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace lloom

@@ -59,26 +59,31 @@ constexpr int kGemmSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 
 __host__ __device__ inline int64_t gemm_m_tiles(int64_t m) { return (m + kGemmBM - 1) / kGemmBM; }
 
-// Workspace planes the GEMM reads (after the canonical activation blocks): B images, min-B images, scales.
-struct GemmScratch {
-    int64_t bimg, minb, dat, aimg, mina, total;
+// Operand images the GEMM reads.  Activation side (per call, in the caller's workspace): B images, min-B images,
+// scales.  Weight side: A images and min-A images -- built per call in the workspace, or once per weight matrix
+// into a caller-owned buffer (lloom_b200_weight_image_build) that later calls pass instead.
+struct GemmActLayout {
+    int64_t bimg, minb, dat, total;
 };
-__host__ __device__ inline GemmScratch gemm_scratch_layout(int64_t m, int64_t n, int64_t k) {
-    GemmScratch s;
-    // weight images cover an even number of n-tiles (the CTA-pair kernel works on two at a time; rows past n are zero)
-    const int64_t mt = gemm_m_tiles(m), nt = ((n + kGemmBN - 1) / kGemmBN + 1) / 2 * 2, nb = k / 256;
+struct GemmWeightLayout {
+    int64_t aimg, mina, total;
+};
+__host__ __device__ inline GemmActLayout gemm_act_layout(int64_t m, int64_t k) {
+    GemmActLayout s;
+    const int64_t mt = gemm_m_tiles(m), nb = k / 256;
     s.bimg = 0;
     s.minb = s.bimg + mt * (k / 64) * kGemmAtomBytes;
     s.dat = s.minb + mt * nb * kGemmMinBytes;
-    s.aimg = (s.dat + mt * nb * kGemmDaBytes + 1023) / 1024 * 1024;
-    s.mina = s.aimg + nt * (k / 64) * kGemmAtomBytes;
-    s.total = (s.mina + nt * nb * kGemmMinBytes + 255) / 256 * 256;
+    s.total = (s.dat + mt * nb * kGemmDaBytes + 1023) / 1024 * 1024;
     return s;
 }
-
-inline int64_t gemm_scratch_bytes(int w_dtype, int64_t m, int64_t n, int64_t k) {
-    if (w_dtype != LLOOM_Q4_K || m <= 8) return 0;
-    return gemm_scratch_layout(m, n, k).total;
+__host__ __device__ inline GemmWeightLayout gemm_weight_layout(int64_t n, int64_t k) {
+    GemmWeightLayout s;
+    const int64_t nt = (n + kGemmBN - 1) / kGemmBN, nb = k / 256;
+    s.aimg = 0;
+    s.mina = s.aimg + nt * (k / 64) * kGemmAtomBytes;
+    s.total = (s.mina + nt * nb * kGemmMinBytes + 1023) / 1024 * 1024;
+    return s;
 }
 
 // Byte offset of element (row r, k-element e in [0,64)) inside a 128-row k-stage image:
@@ -94,12 +99,12 @@ __host__ __device__ inline int min_tile_offset(int r, int e) {
 
 // Canonical Q8_K activation blocks -> the GEMM's operand images.  One CTA per (m-tile, superblock):
 // thread (t, c) converts 8 consecutive codes of token t to f16 and stores one 16-byte chunk.
-__global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restrict__ act, int m, int n, int k,
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restrict__ act, int m, int k,
                                                         uint8_t *__restrict__ scratch) {
     const int nb = k / 256;
     const int quarter = blockIdx.x & 3;  // 32 tokens of the tile per CTA
     const int mt = (blockIdx.x >> 2) / nb, b = (blockIdx.x >> 2) % nb;
-    const GemmScratch lay = gemm_scratch_layout(m, n, k);
+    const GemmActLayout lay = gemm_act_layout(m, k);
     uint8_t *bimg = scratch + lay.bimg + ((int64_t)mt * (k / 64) + (int64_t)b * 4) * kGemmAtomBytes;
     uint8_t *minb = scratch + lay.minb + ((int64_t)mt * nb + b) * kGemmMinBytes;
     float *dat = reinterpret_cast<float *>(scratch + lay.dat) + ((int64_t)mt * nb + b) * 128;
@@ -146,13 +151,13 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
 // Q4_K weight blocks -> the GEMM's A images.  One CTA per (n-tile, superblock), one thread per weight row:
 // the 144-byte block becomes four 128-byte rows of f16 (sc_j * q, exact) in the four swizzle atoms of the
 // superblock, plus the 32-byte min row (m_j duplicated against the two 16-element bsums of sub-block j).
-__global__ void __launch_bounds__(128) gemm_expand_kernel(const uint8_t *__restrict__ w, int m, int n, int k,
+__global__ void __launch_bounds__(128) gemm_expand_kernel(const uint8_t *__restrict__ w, int n, int k,
                                                           uint8_t *__restrict__ scratch) {
     // [4 atoms x 16 KB][min tile 4 KB]: assembled in shared memory, written out by two bulk stores
     extern __shared__ __align__(1024) uint8_t ex_smem[];
     const int nb = k / 256;
     const int nt = blockIdx.x / nb, b = blockIdx.x % nb;
-    const GemmScratch lay = gemm_scratch_layout(m, n, k);
+    const GemmWeightLayout lay = gemm_weight_layout(n, k);
     const int r = threadIdx.x, row = nt * kGemmBN + r;
     uint4 blk[9];
 #pragma unroll
@@ -288,7 +293,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t pari
             if (*abort_flag) return false;
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kMaxWaitNs) break;
+            else if (now - t0 > wait_limit_ns()) break;
         }
     }
     *abort_flag = 1;
@@ -298,7 +303,8 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t pari
 
 struct GemmParams {
     const uint8_t *w;        // Q4_K blocks [n][k/256], 16-byte aligned
-    const uint8_t *scratch;  // planes written by gemm_prep_kernel
+    const uint8_t *act_img;  // planes written by gemm_prep_kernel
+    const uint8_t *w_img;    // images written by gemm_expand_kernel
     float *y;
     int64_t ldy;
     int64_t row_bytes;
@@ -327,7 +333,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     const int mt = blockIdx.x % p.m_tiles, nt = blockIdx.x / p.m_tiles;
     const int n0 = nt * kGemmBN, m0 = mt * kGemmBM;
     const int nb = p.k / 256;
-    const GemmScratch lay = gemm_scratch_layout(p.m, p.n, p.k);
+    const GemmActLayout alay = gemm_act_layout(p.m, p.k);
+    const GemmWeightLayout wlay = gemm_weight_layout(p.n, p.k);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
@@ -427,11 +434,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     } else if (warp == kGemmEpiWarps) {
         // ------------------------------ operand tiles: bulk copies ------------------------------
         // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
-        const uint8_t *aimg = p.scratch + lay.aimg + (int64_t)nt * (p.k / 64) * kGemmAtomBytes;
-        const uint8_t *mina = p.scratch + lay.mina + (int64_t)nt * nb * kGemmMinBytes;
-        const uint8_t *bimg = p.scratch + lay.bimg + (int64_t)mt * (p.k / 64) * kGemmAtomBytes;
-        const uint8_t *minb = p.scratch + lay.minb + (int64_t)mt * nb * kGemmMinBytes;
-        const uint8_t *dat = p.scratch + lay.dat + (int64_t)mt * nb * kGemmDaBytes;
+        const uint8_t *aimg = p.w_img + wlay.aimg + (int64_t)nt * (p.k / 64) * kGemmAtomBytes;
+        const uint8_t *mina = p.w_img + wlay.mina + (int64_t)nt * nb * kGemmMinBytes;
+        const uint8_t *bimg = p.act_img + alay.bimg + (int64_t)mt * (p.k / 64) * kGemmAtomBytes;
+        const uint8_t *minb = p.act_img + alay.minb + (int64_t)mt * nb * kGemmMinBytes;
+        const uint8_t *dat = p.act_img + alay.dat + (int64_t)mt * nb * kGemmDaBytes;
         bool ok = true;
         for (int b = 0; b < nb && ok; ++b) {
             for (int h = 0; h < 2 && ok; ++h) {
@@ -511,57 +518,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
-}
-
-cudaError_t gemm_launch_pair_kernel(const GemmParams &p, int max_smem, cudaStream_t stream, bool &launched);
-
-inline int gemm_launch(int w_dtype, const void *w, const void *act, float *y, int64_t m, int64_t n, int64_t k,
-                       int64_t ldy, void *workspace, int /*sm_count*/, int max_smem, cudaStream_t stream, bool &handled,
-                       int &cuda_err) {
-    handled = false;
-    if (w_dtype != LLOOM_Q4_K || m <= 8) return LLOOM_OK;
-    if (kGemmSmemBytes > max_smem) return LLOOM_OK;
-    handled = true;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
-        if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
-        configured = true;
-    }
-    const int64_t mt = gemm_m_tiles(m), nb = k / 256;
-    const int64_t ntiles = (n + kGemmBN - 1) / kGemmBN, ntiles_even = (ntiles + 1) / 2 * 2;
-    gemm_prep_kernel<<<(unsigned)(mt * nb * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)n, (int)k, (uint8_t *)workspace);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
-    constexpr int kExpandSmem = 4 * kGemmAtomBytes + kGemmMinBytes;
-    static bool expand_configured = false;
-    if (!expand_configured) {
-        e = cudaFuncSetAttribute(gemm_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpandSmem);
-        if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
-        expand_configured = true;
-    }
-    gemm_expand_kernel<<<(unsigned)(ntiles_even * nb), 128, kExpandSmem, stream>>>((const uint8_t *)w, (int)m, (int)n, (int)k, (uint8_t *)workspace);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
-    GemmParams p;
-    p.w = (const uint8_t *)w;
-    p.scratch = (const uint8_t *)workspace;
-    p.y = y;
-    p.ldy = ldy;
-    p.row_bytes = nb * Q4K_BYTES;
-    p.m = (int)m;
-    p.n = (int)n;
-    p.k = (int)k;
-    p.n_tiles = (int)ntiles;
-    p.m_tiles = (int)mt;
-    bool launched = false;
-    e = gemm_launch_pair_kernel(p, max_smem, stream, launched);  // CTA-pair kernel (gemm_q4k_2sm.cuh), opt-in
-    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
-    if (launched) return LLOOM_OK;
-    gemm_q4k_kernel<<<(unsigned)(p.n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) { cuda_err = (int)e; return LLOOM_ERR_LAUNCH; }
-    return LLOOM_OK;
 }
 
 }  // namespace lloom

@@ -11,7 +11,10 @@
 // matrix gives bit-identical rows.
 #pragma once
 
+#include <mutex>
+
 #include "common.cuh"
+#include "gemv_params.h"
 #include "quantize_act.cuh"
 
 namespace lloom {
@@ -28,22 +31,6 @@ struct ActPlanes {
     const short *sums;
     int k;
 };
-
-constexpr int kQ8KUnitStride = 256 + 16;
-constexpr int kQ8_0UnitStride = 64 + 16;
-
-__host__ __device__ inline int64_t round16(int64_t v) { return (v + 15) / 16 * 16; }
-
-__host__ __device__ inline int64_t act_qs_bytes(int w_dtype, int64_t m, int64_t k) {
-    return (w_dtype == LLOOM_Q8_0) ? m * (k / 64) * kQ8_0UnitStride : m * (k / 256) * kQ8KUnitStride;
-}
-
-__host__ __device__ inline int64_t act_plane_bytes(int w_dtype, int64_t m, int64_t k) {
-    const int64_t qs = act_qs_bytes(w_dtype, m, k);
-    const int64_t d = (w_dtype == LLOOM_Q8_0) ? m * (k / 32) * 4 : m * (k / 256) * 4;
-    const int64_t sums = (w_dtype == LLOOM_Q8_0) ? 0 : (w_dtype == LLOOM_Q4_K ? m * (k / 32) * 2 : m * (k / 16) * 2);
-    return round16(qs) + round16(d) + round16(sums);
-}
 
 // Read NWORDS 32-bit words starting at a 2-byte aligned shared-memory address.
 template <int NWORDS>
@@ -287,44 +274,14 @@ struct FmtQ8_0 {
     }
 };
 
-constexpr int kMaxPeers = 8;  // GPUs of one node
-
-struct GemvParams {
-    const uint8_t *w;    // canonical blocks, 16-byte aligned
-    const uint8_t *act;  // canonical activation blocks [m][k/block] (used when x == nullptr)
-    const float *x;      // f32 activations [m][k], 16-byte aligned: quantized in the prologue (fused forward)
+// The matrix (or row range of one) a CTA is working on: a launch has one, a grouped launch up to kMaxGroup.
+struct GemvSeg {
+    const uint8_t *w;  // first block of the matrix
+    int64_t w_bytes;   // its size (the bulk engine may touch whole 16-byte lines below this)
     float *y;
     int64_t ldy;
-    int64_t row_bytes;
-    int64_t w_bytes;  // n * row_bytes
-    int n, k, m;
-    int w_dtype;
-    int n_cwarps;      // consumer warps; blockDim.x = 32 * (n_cwarps + 1)
-    int lpr_log2;      // lanes per row = 1 << lpr_log2 (a warp handles 32 / lanes-per-row row groups)
-    int stages;
-    int stage_bytes;   // multiple of 128
-    int act_bytes;     // multiple of 16
-    int row_pitch;     // tensor-core kernel only: bytes between weight rows inside a stage
-    int act_pitch;     // tensor-core kernel only: bytes between activation rows of the code plane
-    int act_planes;    // tensor-core kernel only: `act` already holds the plane image (else canonical blocks)
-    int tile_bar_bytes;  // tensor-core kernel only: bytes of the per-item barrier array (multiple of 16)
-    int chunk_sb;        // tensor-core kernel only: superblocks of a row per stage (all of them unless K is large)
-    int nchunks;         // both kernels: pieces a row is cut into, each a stage's worth (1: whole rows)
-    int chunk_units;     // dp4a kernel, nchunks > 1: units (superblocks / pairs of Q8_0 blocks) of a row per piece
-    int unit_bytes;      // dp4a kernel: bytes of a unit (144 / 210 / 68)
-    // Fused gather: when n_peers > 0 every output value goes to the same place in each of these buffers (this GPU's
-    // own and its peers', mapped into this process) instead of `y`, so the row-sharded forward needs no separate
-    // all-gather: the stores cross NVLink while the rest of the rows are still being computed.
-    int n_peers;
-    // Fused gather with staging: bytes of the shared-memory area (after the activation planes) that collects the
-    // CTA's output rows, [m][out_pitch] floats; the CTA writes them to the peers in whole lines when it is done.
-    // 0: every value goes out on its own.
-    int out_bytes;
-    int out_pitch;
-    // Block on the store (the reference's MvStore, lloom-tensor/src/quantized/mod.rs:1668-1696):
-    // 0 plain, 1 silu(W.x), 2 dst <- dst * (W.x).
-    int store_mode;
-    float *y_peer[kMaxPeers];
+    int store;         // block on the store
+    int r_begin, r_end;  // rows of this matrix the CTA owns
 };
 
 // One output value to its destination(s).  SiLU in the reference's f32 form v / (1 + exp(-v)) (op.rs:755-757,
@@ -332,40 +289,23 @@ struct GemvParams {
 // Only the EPI = 1 kernel instances contain this code: inlined into the sixteen unrolled stores of an 8-row
 // instance it cost the plain forward 25-60 % of that instance's time, and as an out-of-line call it still cost
 // every instance 5-20 % (registers held across the call sites).
-__device__ __forceinline__ void store_out(const GemvParams &p, int64_t idx, float v) {
-    if (p.store_mode == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
+__device__ __forceinline__ void store_out(const GemvParams &p, const GemvSeg &sg, int64_t idx, float v) {
+    if (sg.store == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
     if (p.n_peers == 0) {
-        p.y[idx] = (p.store_mode == LLOOM_STORE_MUL_INTO) ? __fmul_rn(p.y[idx], v) : v;
+        sg.y[idx] = (sg.store == LLOOM_STORE_MUL_INTO) ? __fmul_rn(sg.y[idx], v) : v;
     } else {
         for (int g = 0; g < p.n_peers; ++g) p.y_peer[g][idx] = v;
     }
 }
 
-constexpr int kMaxStages = 8;
-
-#ifdef LLOOM_TRACE
-// Development build only: per-CTA timestamps (ns) of the GEMV's phases.
-__device__ unsigned long long g_trace[16][160][16];  // [launch ring][CTA][event]
-__device__ unsigned int g_trace_cnt[160];
-__shared__ unsigned int s_trace_slot;
-__device__ __forceinline__ unsigned long long trace_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define LLOOM_TRACE_MARK(slot) do { if ((threadIdx.x & 31) == 0 && blockIdx.x < 160) g_trace[s_trace_slot & 15][blockIdx.x][slot] = trace_now(); } while (0)
-#else
-#define LLOOM_TRACE_MARK(slot) do { } while (0)
-#endif
-
 // Output of row `row` (of this CTA's range starting at r_begin), activation row m: staged in shared memory when the
 // launch has a staging area, else straight to its destination(s).
-__device__ __forceinline__ void emit_out(const GemvParams &p, float *out_s, int r_begin, int m, int row, float v) {
+__device__ __forceinline__ void emit_out(const GemvParams &p, const GemvSeg &sg, float *out_s, int m, int row, float v) {
     if (p.out_bytes) {
-        if (p.store_mode == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
-        out_s[m * p.out_pitch + (row - r_begin)] = v;
+        if (sg.store == LLOOM_STORE_SILU) v = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
+        out_s[m * p.out_pitch + (row - sg.r_begin)] = v;
     } else {
-        store_out(p, (int64_t)m * p.ldy + row, v);
+        store_out(p, sg, (int64_t)m * sg.ldy + row, v);
     }
 }
 
@@ -381,6 +321,53 @@ __device__ __forceinline__ void flush_out(const GemvParams &p, const float *out_
             const float *src = out_s + m * p.out_pitch;
             for (int i = tid; i < rows; i += nthreads) dst[i] = src[i];
         }
+}
+
+// Bounded wait for a fused gather to complete on this GPU: every slot of this GPU's flag array has reached the
+// count this GPU's own GEMV published (word kMaxPeers of the array).  Every thread may call it; each polls by
+// itself (the flags sit in L2 after the first read).  On a time-out the status word is set and false returned.
+__device__ __forceinline__ bool wait_exchange(const GemvParams &p) {
+    const unsigned int *flags = p.wait_flags;
+    unsigned int want;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(want) : "l"(flags + kMaxPeers) : "memory");
+    unsigned long long t0 = 0;
+    int g = 0;
+    for (uint32_t i = 0; i < kMaxSpins; ++i) {
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + g) : "memory");
+        if ((int)(seen - want) >= 0) {
+            if (++g == p.wait_peers) return true;
+            continue;
+        }
+        if ((i & 63) == 63) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > wait_limit_ns()) break;
+        }
+        __nanosleep(100);
+    }
+    atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
+    return false;
+}
+
+// Fused gather with the cross-GPU barrier folded in (p.publish != 0): every CTA, once its peer stores
+// are issued, makes them visible system-wide and bumps this GPU's arrival counter; the CTA that arrives last
+// advances the GPU's call counter and publishes it in slot [peer_rank] of every GPU's flag array with a
+// system-scope release store.  A consumer that has seen the same count in all slots of its own flag array
+// (lloom_b200_peer_wait) may read the gathered rows.  Called by one thread per CTA after a CTA-wide barrier.
+__device__ __forceinline__ void publish_arrival(const GemvParams &p) {
+    __threadfence_system();
+    // words of this GPU's flag array: [kMaxPeers] = its call counter, [kMaxPeers + 1] = CTAs arrived so far
+    unsigned int *mine = p.peer_flags[p.peer_rank];
+    const unsigned int prev = atomicAdd(mine + kMaxPeers + 1, 1u);
+    if (prev + 1 == gridDim.x) {
+        mine[kMaxPeers + 1] = 0;  // ready for the next launch on this stream
+        const unsigned int epoch = mine[kMaxPeers] + 1;
+        mine[kMaxPeers] = epoch;
+        __threadfence_system();
+        for (int g = 0; g < p.n_peers; ++g)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(epoch) : "memory");
+    }
 }
 
 // Canonical activation blocks (global) -> planes (shared); all `nthreads` consumer threads take part.
@@ -515,55 +502,55 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
     }
 }
 
-// The producer warp's loop: streams tiles of `tile_rows` consecutive rows of [r_begin, r_end) into the stage ring.
-__device__ __forceinline__ void gemv_producer(const GemvParams &p, uint64_t *full, uint64_t *empty, uint8_t *stage0,
-                                              int tile_rows, int r_begin, int r_end, int lane) {
-    int it = 0;
-    for (int row0 = r_begin; row0 < r_end; row0 += tile_rows, ++it) {
+// The producer warp's loop over one matrix: streams tiles of `tile_rows` consecutive rows of the segment's row range
+// into the stage ring.  `it` counts the work items of the launch (it carries on across the matrices of a group).
+__device__ __forceinline__ bool gemv_producer(const GemvParams &p, const GemvSeg &sg, uint64_t *full, uint64_t *empty,
+                                              uint8_t *stage0, int tile_rows, int lane, int &it) {
+    for (int row0 = sg.r_begin; row0 < sg.r_end; row0 += tile_rows, ++it) {
         const int s = it % p.stages;
         if (it >= p.stages) {
-            if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
+            if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return false;
         }
-        const int rows = min(tile_rows, r_end - row0);
+        const int rows = min(tile_rows, sg.r_end - row0);
         const int64_t start = (int64_t)row0 * p.row_bytes;
         const int64_t end = start + (int64_t)rows * p.row_bytes;
         const int64_t a_start = start & ~(int64_t)15;
         int64_t a_end = (end + 15) & ~(int64_t)15;
-        const int64_t bulk_limit = p.w_bytes & ~(int64_t)15;  // bytes the bulk engine may touch
+        const int64_t bulk_limit = sg.w_bytes & ~(int64_t)15;  // bytes the bulk engine may touch
         if (a_end > bulk_limit) a_end = bulk_limit;
         uint8_t *dst = stage0 + (size_t)s * p.stage_bytes;
         // ragged end of the weight stream (< 16 bytes): plain loads
         if (end > a_end) {
             const int64_t from = a_end > a_start ? a_end : a_start;
-            for (int64_t i = from + lane; i < end; i += 32) dst[i - a_start] = __ldg(p.w + i);
+            for (int64_t i = from + lane; i < end; i += 32) dst[i - a_start] = __ldg(sg.w + i);
         }
         __syncwarp();
         if (lane == 0) {
             if (a_end > a_start) {
                 const uint32_t bytes = (uint32_t)(a_end - a_start);
                 mbar_arrive_expect_tx(&full[s], bytes);
-                bulk_g2s(dst, p.w + a_start, bytes, &full[s]);
+                bulk_g2s(dst, sg.w + a_start, bytes, &full[s]);
             } else {
                 mbar_arrive(&full[s]);
             }
         }
     }
+    return true;
 }
 
 // The producer loop for rows cut into pieces (long rows: a whole-row tile would not leave room for two stages in
 // the side-by-side shape).  Work items in order -- tile 0: pieces 0.., tile 1: ... -- each `chunk_units` units
 // (fewer in a row's last piece) of up to `tile_rows` rows, one bulk copy per row, the pieces of a tile's rows packed
 // `chunk_units * unit_bytes` apart.  Needs row sizes and piece sizes that are multiples of 16 bytes.
-__device__ __forceinline__ void gemv_producer_pieces(const GemvParams &p, uint64_t *full, uint64_t *empty, uint8_t *stage0,
-                                                     int tile_rows, int units, int r_begin, int r_end, int lane) {
+__device__ __forceinline__ bool gemv_producer_pieces(const GemvParams &p, const GemvSeg &sg, uint64_t *full, uint64_t *empty,
+                                                     uint8_t *stage0, int tile_rows, int units, int lane, int &it) {
     const int pitch = p.chunk_units * p.unit_bytes;
-    int it = 0;
-    for (int row0 = r_begin; row0 < r_end; row0 += tile_rows) {
-        const int rows = min(tile_rows, r_end - row0);
+    for (int row0 = sg.r_begin; row0 < sg.r_end; row0 += tile_rows) {
+        const int rows = min(tile_rows, sg.r_end - row0);
         for (int c = 0; c < p.nchunks; ++c, ++it) {
             const int s = it % p.stages;
             if (it >= p.stages) {
-                if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return;
+                if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return false;
             }
             const int u0 = c * p.chunk_units;
             const uint32_t bytes = (uint32_t)(min(p.chunk_units, units - u0) * p.unit_bytes);
@@ -571,10 +558,36 @@ __device__ __forceinline__ void gemv_producer_pieces(const GemvParams &p, uint64
             if (lane == 0) mbar_arrive_expect_tx(&full[s], (uint32_t)rows * bytes);
             __syncwarp();
             for (int r = lane; r < rows; r += 32)
-                bulk_g2s(dst + (size_t)r * pitch, p.w + (int64_t)(row0 + r) * p.row_bytes + (int64_t)u0 * p.unit_bytes, bytes,
+                bulk_g2s(dst + (size_t)r * pitch, sg.w + (int64_t)(row0 + r) * p.row_bytes + (int64_t)u0 * p.unit_bytes, bytes,
                          &full[s]);
         }
     }
+    return true;
+}
+
+// Segment g of the launch as seen by this CTA, which owns rows [r_begin, r_end) of the concatenation.
+template <bool GROUP>
+__device__ __forceinline__ GemvSeg gemv_segment(const GemvParams &p, int g, int r_begin, int r_end) {
+    GemvSeg sg;
+    if (GROUP) {
+        const int off = p.goff[g], rows = p.goff[g + 1] - off;
+        sg.w = p.gw[g];
+        sg.w_bytes = (int64_t)rows * p.row_bytes;
+        sg.y = p.gy[g];
+        sg.ldy = p.gldy[g];
+        sg.store = p.gstore[g];
+        sg.r_begin = max(r_begin - off, 0);
+        sg.r_end = min(r_end - off, rows);
+    } else {
+        sg.w = p.w;
+        sg.w_bytes = p.w_bytes;
+        sg.y = p.y;
+        sg.ldy = p.ldy;
+        sg.store = p.store_mode;
+        sg.r_begin = r_begin;
+        sg.r_end = r_end;
+    }
+    return sg;
 }
 
 // Dynamic shared memory: [barriers 128 B][act planes][staged output rows, fused gather only][stage 0][stage 1]...
@@ -587,8 +600,9 @@ __device__ __forceinline__ void gemv_producer_pieces(const GemvParams &p, uint64
 // CW = most consumer warps the instance may be launched with (8, or 12 for the side-by-side m <= 2 shapes).
 // PIECES = the instance for rows cut into pieces (p.nchunks > 1); the whole-row instances keep the loop over pieces
 // out of their code.  EPI = 1: the instance with the store blocks and the fused gather (store_out / emit_out);
-// EPI = 0 stores every value to p.y and nothing else.
-template <class Fmt, int M, int RW, int CW = 8, bool PIECES = false, int EPI = 0>
+// EPI = 0 stores every value to its matrix's y and nothing else.  GROUP = the instance that walks several matrices
+// (p.n_group of them, sharing the activations) as one concatenated row range.
+template <class Fmt, int M, int RW, int CW = 8, bool PIECES = false, int EPI = 0, bool GROUP = false>
 __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(const GemvParams p) {
     constexpr int MC = M > 4 ? (M + 1) / 2 : M;  // activation rows per pass
     constexpr int NPASS = (M + MC - 1) / MC;
@@ -605,12 +619,8 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
     // equal contiguous row ranges per CTA: HBM bytes per SM differ by at most one row
     const int r_begin = (int)(((int64_t)blockIdx.x * p.n) / gridDim.x);
     const int r_end = (int)(((int64_t)(blockIdx.x + 1) * p.n) / gridDim.x);
+    const int nseg = GROUP ? p.n_group : 1;
 
-#ifdef LLOOM_TRACE
-    if (threadIdx.x == 0) s_trace_slot = blockIdx.x < 160 ? g_trace_cnt[blockIdx.x]++ : 0;
-    __syncthreads();
-#endif
-    if (threadIdx.x == 0) LLOOM_TRACE_MARK(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
@@ -623,113 +633,120 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
 
     if (warp == p.n_cwarps) {
         // ---------------- producer warp ----------------
-        if (PIECES) gemv_producer_pieces(p, full, empty, stage0, tile_rows, p.k / Fmt::kUnitElems, r_begin, r_end, lane);
-        else gemv_producer(p, full, empty, stage0, tile_rows, r_begin, r_end, lane);
+        int it = 0;
+        for (int g = 0; g < nseg; ++g) {
+            const GemvSeg sg = gemv_segment<GROUP>(p, g, r_begin, r_end);
+            if (sg.r_begin >= sg.r_end) continue;
+            const bool ok = PIECES ? gemv_producer_pieces(p, sg, full, empty, stage0, tile_rows, p.k / Fmt::kUnitElems, lane, it)
+                                   : gemv_producer(p, sg, full, empty, stage0, tile_rows, lane, it);
+            if (!ok) break;
+        }
         return;
     }
 
     // ---------------- consumer warps ----------------
     ActPlanes planes;
+    bool ok_wait = true;
     {
         const int nthreads = p.n_cwarps * 32;
         asm volatile("griddepcontrol.wait;" ::: "memory");  // predecessor's writes (x, act blocks) are visible
-        if (threadIdx.x == 0) LLOOM_TRACE_MARK(14);
+        if (EPI != 0 && p.wait_flags) ok_wait = wait_exchange(p);  // x came out of a fused gather: all peers' rows are in
         if (p.x) quantize_acts_to_planes(p, act_smem, warp, lane, planes);
         else stage_acts(p, act_smem, threadIdx.x, nthreads, planes);
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-        if (threadIdx.x == 0) LLOOM_TRACE_MARK(1);
     }
 
     const int units = p.k / Fmt::kUnitElems;
     const int group = lane >> p.lpr_log2, lig = lane & (lpr - 1);
     float *out_s = reinterpret_cast<float *>(act_smem + p.act_bytes);
     int it = 0;  // work items so far: a tile, or one piece of a tile's rows when the rows are cut into pieces
-    bool ok = true;  // a timed-out wait ends the loop; the warp still meets the others at the flush barrier
+    bool ok = ok_wait;  // a timed-out wait ends the loop; the warp still meets the others at the flush barrier
     const int nchunks = PIECES ? p.nchunks : 1;
     const int unit_chunk = PIECES ? p.chunk_units : units;
     const int piece_pitch = unit_chunk * p.unit_bytes;
-    for (int trow = r_begin; trow < r_end && ok; trow += tile_rows) {
-        const int local0 = (warp * groups + group) * RW;
-        const int row0 = trow + local0;
-        bool valid[RW];
+    for (int g = 0; g < nseg && ok; ++g) {
+        const GemvSeg sg = gemv_segment<GROUP>(p, g, r_begin, r_end);
+        for (int trow = sg.r_begin; trow < sg.r_end && ok; trow += tile_rows) {
+            const int local0 = (warp * groups + group) * RW;
+            const int row0 = trow + local0;
+            bool valid[RW];
 #pragma unroll
-        for (int r = 0; r < RW; ++r) valid[r] = row0 + r < r_end;
-        float accs[NPASS][RW][MC];
+            for (int r = 0; r < RW; ++r) valid[r] = row0 + r < sg.r_end;
+            float accs[NPASS][RW][MC];
 #pragma unroll
-        for (int pass = 0; pass < NPASS; ++pass)
-#pragma unroll
-            for (int r = 0; r < RW; ++r)
-#pragma unroll
-                for (int m = 0; m < MC; ++m) accs[pass][r][m] = 0.0f;
-        for (int c = 0; c < nchunks; ++c, ++it) {
-            const int s = it % p.stages;
-            if (!mbar_wait(&full[s], (it / p.stages) & 1)) {
-                ok = false;
-                break;
-            }
-            if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(2 + 2 * it);
-            const uint8_t *rowp[RW];
-            const int u0 = c * unit_chunk, u1 = min(units, u0 + unit_chunk);
-            if (PIECES) {
-                // pieces packed back to back; the pointer is the row's virtual start, so that unit u sits at
-                // u * unit_bytes as in a whole row
-                const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
+            for (int pass = 0; pass < NPASS; ++pass)
 #pragma unroll
                 for (int r = 0; r < RW; ++r)
-                    rowp[r] = tile_base + (size_t)(local0 + r) * piece_pitch - (size_t)u0 * p.unit_bytes;
-            } else {
-                const int64_t start = (int64_t)trow * p.row_bytes;
-                const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
 #pragma unroll
-                for (int r = 0; r < RW; ++r) rowp[r] = tile_base + (size_t)(local0 + r) * p.row_bytes;
-            }
-            if (valid[0]) {
+                    for (int m = 0; m < MC; ++m) accs[pass][r][m] = 0.0f;
+            for (int c = 0; c < nchunks; ++c, ++it) {
+                const int s = it % p.stages;
+                if (!mbar_wait(&full[s], (it / p.stages) & 1)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t *rowp[RW];
+                const int u0 = c * unit_chunk, u1 = min(units, u0 + unit_chunk);
+                if (PIECES) {
+                    // pieces packed back to back; the pointer is the row's virtual start, so that unit u sits at
+                    // u * unit_bytes as in a whole row
+                    const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
 #pragma unroll
-                for (int pass = 0; pass < NPASS; ++pass) {
-                    const int m0 = pass * MC;
-                    // the last pass of an odd M starts at M - MC: it overlaps the previous pass instead of running past M
-                    for (int u = u0 + lig; u < u1; u += lpr) {
-                        if (m0 + MC <= M) Fmt::template unit<MC, RW>(planes, m0, u, rowp, valid, accs[pass]);
-                        else Fmt::template unit<MC, RW>(planes, M - MC, u, rowp, valid, accs[pass]);
+                    for (int r = 0; r < RW; ++r)
+                        rowp[r] = tile_base + (size_t)(local0 + r) * piece_pitch - (size_t)u0 * p.unit_bytes;
+                } else {
+                    const int64_t start = (int64_t)trow * p.row_bytes;
+                    const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
+#pragma unroll
+                    for (int r = 0; r < RW; ++r) rowp[r] = tile_base + (size_t)(local0 + r) * p.row_bytes;
+                }
+                if (valid[0]) {
+#pragma unroll
+                    for (int pass = 0; pass < NPASS; ++pass) {
+                        const int m0 = pass * MC;
+                        // the last pass of an odd M starts at M - MC: it overlaps the previous pass instead of running past M
+                        for (int u = u0 + lig; u < u1; u += lpr) {
+                            if (m0 + MC <= M) Fmt::template unit<MC, RW>(planes, m0, u, rowp, valid, accs[pass]);
+                            else Fmt::template unit<MC, RW>(planes, M - MC, u, rowp, valid, accs[pass]);
+                        }
                     }
                 }
+                // this warp is done reading the stage
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
             }
-            // this warp is done reading the stage
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            if (threadIdx.x == 0 && it < 6) LLOOM_TRACE_MARK(3 + 2 * it);
-        }
-        if (!ok) break;
-        float out[RW][M];
+            if (!ok) break;
+            float out[RW][M];
 #pragma unroll
-        for (int pass = 0; pass < NPASS; ++pass)
+            for (int pass = 0; pass < NPASS; ++pass)
 #pragma unroll
-            for (int r = 0; r < RW; ++r)
+                for (int r = 0; r < RW; ++r)
 #pragma unroll
-                for (int m = 0; m < MC; ++m) {
-                    const int m0 = pass * MC;
-                    const int mi = (m0 + MC <= M) ? m0 + m : M - MC + m;
-                    out[r][mi] = accs[pass][r][m];
-                }
+                    for (int m = 0; m < MC; ++m) {
+                        const int m0 = pass * MC;
+                        const int mi = (m0 + MC <= M) ? m0 + m : M - MC + m;
+                        out[r][mi] = accs[pass][r][m];
+                    }
 
 #pragma unroll
-        for (int r = 0; r < RW; ++r)
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-                float v = out[r][m];
-                for (int off = lpr >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-                out[r][m] = v;
-            }
-        if (lig == 0) {
-#pragma unroll
             for (int r = 0; r < RW; ++r)
-                if (valid[r]) {
 #pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        if (EPI == 0) p.y[(int64_t)m * p.ldy + row0 + r] = out[r][m];
-                        else emit_out(p, out_s, r_begin, m, row0 + r, out[r][m]);
-                    }
+                for (int m = 0; m < M; ++m) {
+                    float v = out[r][m];
+                    for (int off = lpr >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                    out[r][m] = v;
                 }
+            if (lig == 0) {
+#pragma unroll
+                for (int r = 0; r < RW; ++r)
+                    if (valid[r]) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            if (EPI == 0) sg.y[(int64_t)m * sg.ldy + row0 + r] = out[r][m];
+                            else emit_out(p, sg, out_s, m, row0 + r, out[r][m]);
+                        }
+                    }
+            }
         }
     }
     if (EPI != 0 && p.out_bytes) {
@@ -737,7 +754,115 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
         if (ok) flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);
     }
-    if (threadIdx.x == 0) LLOOM_TRACE_MARK(15);
+    if (EPI != 0 && p.publish) {
+        // every consumer thread's peer stores are issued; one thread reports the CTA (also after a timed-out wait,
+        // so that the peers' waits end with the right count and the status word tells the story)
+        const int nthreads = p.n_cwarps * 32;
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (threadIdx.x == 0) publish_arrival(p);
+    }
+}
+
+// ---- launch of one format's instances (each format is a translation unit of its own) ----
+
+struct FuncSmemConfig {  // per kernel instance: the dynamic shared memory each device has opted into
+    std::mutex mu;
+    int smem[64] = {0};
+};
+
+template <class Kern>
+static cudaError_t ensure_smem(Kern kern, FuncSmemConfig &cfg, int smem, bool carveout) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(cfg.mu);
+    if (cfg.smem[dev] >= smem) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    if (carveout) {
+        // ask for the largest shared-memory carve-out, so that two half-size CTAs really fit side by side
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+    }
+    cfg.smem[dev] = smem;
+    return cudaSuccess;
+}
+
+template <class Kern, class Params>
+static cudaError_t launch_with_overlap(Kern kern, const Params &p, int grid, int threads, int smem, bool overlap,
+                                       cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// EPI = 1 instances carry the store blocks and the fused gather; the plain forward uses the EPI = 0 instances.
+inline bool gemv_needs_epi(const GemvParams &p) {
+    if (p.n_peers != 0 || p.store_mode != LLOOM_STORE_PLAIN || p.wait_flags != nullptr) return true;
+    for (int g = 0; g < p.n_group; ++g)
+        if (p.gstore[g] != LLOOM_STORE_PLAIN) return true;
+    return false;
+}
+
+template <class Fmt, int M, int RW, int CW, bool PIECES, int EPI, bool GROUP>
+static cudaError_t launch_gemv_inst2(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    auto kern = gemv_kernel<Fmt, M, RW, CW, PIECES, EPI, GROUP>;
+    static FuncSmemConfig cfg;
+    cudaError_t e = ensure_smem(kern, cfg, smem, true);
+    if (e != cudaSuccess) return e;
+    return launch_with_overlap(kern, p, grid, 32 * (p.n_cwarps + 1), smem, overlap, stream);
+}
+
+template <class Fmt, int M, int RW, int CW = 8, bool PIECES = false, bool GROUP = false>
+static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    if (gemv_needs_epi(p)) return launch_gemv_inst2<Fmt, M, RW, CW, PIECES, 1, GROUP>(p, grid, smem, overlap, stream);
+    return launch_gemv_inst2<Fmt, M, RW, CW, PIECES, 0, GROUP>(p, grid, smem, overlap, stream);
+}
+
+template <class Fmt, int RW>
+static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+    if (p.n_group > 1) {  // grouped launch: whole rows, eight consumer warps, one row per lane, m <= 2
+        if (RW != 1 || p.nchunks > 1 || p.n_cwarps > 8) return cudaErrorInvalidValue;
+        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 8, false, true>(p, grid, smem, overlap, stream);
+        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 8, false, true>(p, grid, smem, overlap, stream);
+        return cudaErrorInvalidValue;
+    }
+    if (RW == 1 && p.nchunks > 1) {  // rows cut into pieces: side-by-side shapes with eight consumer warps, m <= 2 only
+        if (p.n_cwarps > 8) return cudaErrorInvalidValue;
+        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 8, true>(p, grid, smem, overlap, stream);
+        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 8, true>(p, grid, smem, overlap, stream);
+        return cudaErrorInvalidValue;
+    }
+    if (RW == 1 && p.n_cwarps > 8) {  // twelve-consumer-warp instances exist for m <= 2 only
+        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 12>(p, grid, smem, overlap, stream);
+        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 12>(p, grid, smem, overlap, stream);
+        return cudaErrorInvalidValue;
+    }
+    switch (p.m) {
+    case 1: return launch_gemv_inst<Fmt, 1, RW>(p, grid, smem, overlap, stream);
+    case 2: return launch_gemv_inst<Fmt, 2, RW>(p, grid, smem, overlap, stream);
+    case 3: return launch_gemv_inst<Fmt, 3, RW>(p, grid, smem, overlap, stream);
+    case 4: return launch_gemv_inst<Fmt, 4, RW>(p, grid, smem, overlap, stream);
+    case 5: return launch_gemv_inst<Fmt, 5, RW>(p, grid, smem, overlap, stream);
+    case 6: return launch_gemv_inst<Fmt, 6, RW>(p, grid, smem, overlap, stream);
+    case 7: return launch_gemv_inst<Fmt, 7, RW>(p, grid, smem, overlap, stream);
+    case 8: return launch_gemv_inst<Fmt, 8, RW>(p, grid, smem, overlap, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <class Fmt>
+static cudaError_t launch_gemv_format(const GemvParams &p, int grid, int smem, bool overlap, int rw, cudaStream_t stream) {
+    return rw == 2 ? launch_gemv_m<Fmt, 2>(p, grid, smem, overlap, stream) : launch_gemv_m<Fmt, 1>(p, grid, smem, overlap, stream);
 }
 
 }  // namespace lloom

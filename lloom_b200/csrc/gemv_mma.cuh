@@ -26,31 +26,12 @@
 
 namespace lloom {
 
-constexpr int kMmaTileRows = 16;
-// Up to this many rows the quantizer runs as the kernel's prologue (measured per forward: 10.0 us against 11.5 us
-// with the separate quantizer at M = 2; 11.6 against 11.4 at M = 4).
-constexpr int kMmaFusedMaxM = 2;
-constexpr int kMmaWarps = 16;  // consumer warps; SPLIT of them share a tile, warp j of a team takes superblocks j, j+SPLIT, ...
-constexpr int kMmaRedBytes = 2 * kMmaWarps * 32 * 16;  // double-buffered partial sums, one float4 per lane
-
-// Pitch in bytes (a multiple of 16, >= bytes) that is `want_words` 32-bit words modulo the 32 banks.
-__host__ __device__ inline int64_t bank_pitch(int64_t bytes, int want_words) {
-    const int64_t words = (bytes + 3) / 4;
-    int64_t pad = (want_words - words % 32 + 32) % 32;
-    while ((words + pad) % 4 != 0) pad += 32;  // never taken when bytes % 16 == 0 and want_words % 4 == 0
-    return (words + pad) * 4;
-}
-
 // Activation planes of the tensor-core kernel, per activation row t and superblock b:
 //   codes  [t][b][64 words]  the 256 int8 codes, words permuted so that lane (gid, tig) finds the four words of
 //                            group g it feeds to the MMAs -- low sub-block words 2tig, 2tig+1, high sub-block
 //                            words 2tig, 2tig+1 -- in one 16-byte load at word 16g + 4tig; rows act_pitch apart
 //   lh     [t][b][16 bytes]  l_j = bsum_j & 63 (j = 0..7, the 32-element sub-blocks), then h_j = bsum_j >> 6
 //   d      [t][b] f32
-__host__ __device__ inline int64_t mma_act_pitch(int64_t k) { return bank_pitch((k / 256) * 256, 16); }
-__host__ __device__ inline int64_t mma_act_bytes(int64_t m, int64_t k) {
-    return round16(m * mma_act_pitch(k) + m * (k / 256) * 16 + m * (k / 256) * 4);
-}
 
 __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile(
@@ -162,8 +143,6 @@ __device__ __forceinline__ void gemv_mma_producer(const GemvParams &p, uint64_t 
     }
 }
 
-constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image
-constexpr int kMmaMaxTiles = 512;      // per CTA; one 8-byte barrier each
 
 // Dynamic shared memory: [barriers 128 B][per-tile barriers][partial sums][act planes][staged output rows, fused
 // gather only][stage 0][stage 1]...
@@ -184,30 +163,27 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     const int total_tiles = (p.n + kMmaTileRows - 1) / kMmaTileRows;
     const int r_begin = (int)(((int64_t)blockIdx.x * total_tiles) / gridDim.x) * kMmaTileRows;
     const int r_end = min(p.n, (int)(((int64_t)(blockIdx.x + 1) * total_tiles) / gridDim.x) * kMmaTileRows);
+    const GemvSeg sg = gemv_segment<false>(p, 0, r_begin, r_end);
+    int *cta_ok = reinterpret_cast<int *>(smem + kMmaBarBytes - 8);  // cleared by a warp whose bounded wait ran out
 
-#ifdef LLOOM_TRACE
-    if (threadIdx.x == 0) s_trace_slot = blockIdx.x < 160 ? g_trace_cnt[blockIdx.x]++ : 0;
-    __syncthreads();
-#endif
-    if (threadIdx.x == 0) LLOOM_TRACE_MARK(0);
     const int ntiles = (r_end - r_begin + kMmaTileRows - 1) / kMmaTileRows;
     for (int i = threadIdx.x; i < ntiles * p.nchunks; i += blockDim.x) mbar_init(&tile_full[i], 1);
     if (threadIdx.x < p.stages) mbar_init(&empty[threadIdx.x], SPLIT);
     if (threadIdx.x == 32) mbar_init(act_bar, 1);
+    if (threadIdx.x == 0) *cta_ok = 1;
     fence_mbar_init();
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == kMmaWarps) {
         gemv_mma_producer(p, tile_full, empty, stage0, r_begin, r_end, lane);
-        LLOOM_TRACE_MARK(8);
         return;
     }
 
     constexpr int nthreads = kMmaWarps * 32;
     bool alive = true;  // after a timed-out wait the warp keeps meeting its partner at the pair barrier but computes nothing
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (threadIdx.x == 0) LLOOM_TRACE_MARK(14);
+    if (EPI != 0 && p.wait_flags) alive = wait_exchange(p);  // x came out of a fused gather: all peers' rows are in
     if (p.x) {  // quantizer as prologue: this CTA quantizes the activation rows into its own planes
         const int nbq = p.k >> 8, nblk = p.m * nbq;
         for (int blk = warp; blk < nblk; blk += kMmaWarps)
@@ -218,13 +194,12 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             mbar_arrive_expect_tx(act_bar, (uint32_t)p.act_bytes);
             bulk_g2s(act_smem, p.act, (uint32_t)p.act_bytes, act_bar);
         }
-        alive = mbar_wait(act_bar, 0);
+        alive = mbar_wait(act_bar, 0) && alive;
     } else {
         stage_acts_mma(p, act_smem, threadIdx.x, nthreads);
         asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
     }
 
-    if (threadIdx.x == 0) LLOOM_TRACE_MARK(1);
     const int nb = p.k >> 8;
     const int gid = lane >> 2, tig = lane & 3;  // MMA fragment coordinates
     // B fragments come from activation row gid (rows past m read row 0; their columns are never stored)
@@ -251,7 +226,6 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
         for (int c = 0; c < p.nchunks; ++c) {
         const int item = it * p.nchunks + c, s = item % p.stages;
         alive = alive && mbar_wait(&tile_full[item], 0);
-        if (member == 0 && c == 0 && (it == 0 || it == 5 || it == 6)) LLOOM_TRACE_MARK(it == 0 ? 2 : it == 5 ? 4 : 6);
         const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes;
         const uint8_t *rowa = tile_base + (size_t)ra * p.row_pitch, *rowb = tile_base + (size_t)rb * p.row_pitch;
         const int sb0 = c * p.chunk_sb, nsb = min(p.chunk_sb, nb - sb0);
@@ -339,19 +313,24 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             }
         } else {
             if (t0 < p.m) {
-                if (gid < rows) emit_out(p, out_s, r_begin, t0, trow + gid, out[0]);
-                if (gid + 8 < rows) emit_out(p, out_s, r_begin, t0, trow + gid + 8, out[2]);
+                if (gid < rows) emit_out(p, sg, out_s, t0, trow + gid, out[0]);
+                if (gid + 8 < rows) emit_out(p, sg, out_s, t0, trow + gid + 8, out[2]);
             }
             if (t1 < p.m) {
-                if (gid < rows) emit_out(p, out_s, r_begin, t1, trow + gid, out[1]);
-                if (gid + 8 < rows) emit_out(p, out_s, r_begin, t1, trow + gid + 8, out[3]);
+                if (gid < rows) emit_out(p, sg, out_s, t1, trow + gid, out[1]);
+                if (gid + 8 < rows) emit_out(p, sg, out_s, t1, trow + gid + 8, out[3]);
             }
         }
-        if (it == 0 || it == 5 || it == 6) LLOOM_TRACE_MARK(it == 0 ? 3 : it == 5 ? 5 : 7);
     }
-    if (EPI != 0 && p.out_bytes) {  // every consumer warp gets here, timed-out ones included
+    if (EPI != 0 && (p.out_bytes || p.publish)) {  // every consumer warp gets here, timed-out ones included
+        if (!alive) *cta_ok = 0;
         asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
-        flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);
+        // staged rows leave for the peers only if every warp finished its tiles (a timed-out warp left gaps)
+        if (p.out_bytes && *cta_ok) flush_out(p, out_s, r_begin, r_end, threadIdx.x, nthreads);
+        if (p.publish) {
+            asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
+            if (threadIdx.x == 0) publish_arrival(p);
+        }
     }
 }
 

@@ -1,10 +1,10 @@
-// C ABI of the library (see include/lloom_b200.h).  One translation unit: the kernels live in the
-// headers included below.  No entry point allocates, frees or synchronises.
+// C ABI of the library (see include/lloom_b200.h): argument checks, launch planning and dispatch.  The kernels live
+// in translation units of their own (gemv_*.cu, gemv_mma.cu, gemm.cu); this one holds the small ones (activation
+// quantizers, dequantize, the peer barrier).  No entry point on the forward path allocates, frees or synchronises.
 #include "common.cuh"
 #include "dequant.cuh"
-#include "gemm_q4k_2sm.cuh"
-#include "gemv.cuh"
-#include "gemv_mma.cuh"
+#include "gemm.h"
+#include "gemv_params.h"
 #include "quantize_act.cuh"
 
 #include <atomic>
@@ -12,8 +12,29 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace lloom {
+
+LLOOM_TU_REGISTER()
+
+// ---- translation-unit registry: every unit has its own device-side status word and wait limit ----
+namespace {
+struct TuRegistry {
+    std::mutex mu;
+    std::vector<TuHooks> hooks;
+};
+TuRegistry &tu_registry() {
+    static TuRegistry r;
+    return r;
+}
+}  // namespace
+
+void register_tu(const TuHooks &hooks) {
+    TuRegistry &r = tu_registry();
+    std::lock_guard<std::mutex> lock(r.mu);
+    r.hooks.push_back(hooks);
+}
 
 static thread_local int t_last_cuda_error = 0;
 
@@ -67,136 +88,13 @@ static int64_t weight_row_bytes(int dtype, int64_t k) {
 
 // ---- GEMV launch planning ----
 
-// EPI = 1 instances carry the store blocks and the fused gather; the plain forward uses the EPI = 0 instances.
-static bool gemv_needs_epi(const GemvParams &p) { return p.n_peers != 0 || p.store_mode != LLOOM_STORE_PLAIN; }
-
-template <class Item, int M, int RW, int CW, bool PIECES, int EPI>
-static cudaError_t launch_gemv_inst2(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_kernel<Item, M, RW, CW, PIECES, EPI>;
-    static int configured_smem[64] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_smem[dev] < smem) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        // ask for the largest shared-memory carve-out, so that two half-size CTAs really fit side by side
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return e;
-        configured_smem[dev] = smem;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(32u * (unsigned)(p.n_cwarps + 1));
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = overlap ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, p);
-}
-
-template <class Item, int M, int RW, int CW = 8, bool PIECES = false>
-static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    if (gemv_needs_epi(p)) return launch_gemv_inst2<Item, M, RW, CW, PIECES, 1>(p, grid, smem, overlap, stream);
-    return launch_gemv_inst2<Item, M, RW, CW, PIECES, 0>(p, grid, smem, overlap, stream);
-}
-
-template <class Fmt, int RW>
-static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    if (RW == 1 && p.nchunks > 1) {  // rows cut into pieces: side-by-side shapes with eight consumer warps, m <= 2 only
-        if (p.n_cwarps > 8) return cudaErrorInvalidValue;
-        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 8, true>(p, grid, smem, overlap, stream);
-        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 8, true>(p, grid, smem, overlap, stream);
-        return cudaErrorInvalidValue;
-    }
-    if (RW == 1 && p.n_cwarps > 8) {  // twelve-consumer-warp instances exist for m <= 2 only
-        if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 12>(p, grid, smem, overlap, stream);
-        if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 12>(p, grid, smem, overlap, stream);
-        return cudaErrorInvalidValue;
-    }
-    switch (p.m) {
-    case 1: return launch_gemv_inst<Fmt, 1, RW>(p, grid, smem, overlap, stream);
-    case 2: return launch_gemv_inst<Fmt, 2, RW>(p, grid, smem, overlap, stream);
-    case 3: return launch_gemv_inst<Fmt, 3, RW>(p, grid, smem, overlap, stream);
-    case 4: return launch_gemv_inst<Fmt, 4, RW>(p, grid, smem, overlap, stream);
-    case 5: return launch_gemv_inst<Fmt, 5, RW>(p, grid, smem, overlap, stream);
-    case 6: return launch_gemv_inst<Fmt, 6, RW>(p, grid, smem, overlap, stream);
-    case 7: return launch_gemv_inst<Fmt, 7, RW>(p, grid, smem, overlap, stream);
-    case 8: return launch_gemv_inst<Fmt, 8, RW>(p, grid, smem, overlap, stream);
-    }
-    return cudaErrorInvalidValue;
-}
-
-template <int RW>
-static cudaError_t launch_gemv_fmt(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
+static cudaError_t launch_gemv_dp4a(const GemvParams &p, int grid, int smem, bool overlap, int rw, cudaStream_t stream) {
     switch (p.w_dtype) {
-    case LLOOM_Q8_0: return launch_gemv_m<FmtQ8_0, RW>(p, grid, smem, overlap, stream);
-    case LLOOM_Q4_K: return launch_gemv_m<FmtQ4K, RW>(p, grid, smem, overlap, stream);
-    case LLOOM_Q6_K: return launch_gemv_m<FmtQ6K, RW>(p, grid, smem, overlap, stream);
+    case LLOOM_Q8_0: return launch_gemv_dp4a_q8_0(p, grid, smem, overlap, rw, stream);
+    case LLOOM_Q4_K: return launch_gemv_dp4a_q4k(p, grid, smem, overlap, rw, stream);
+    case LLOOM_Q6_K: return launch_gemv_dp4a_q6k(p, grid, smem, overlap, rw, stream);
     }
     return cudaErrorInvalidValue;
-}
-
-// Development knob: LLOOM_GEMV_SHAPE="<consumer warps>,<rows per lane>" pins the tile shape.
-static bool gemv_shape_override(int &cw, int &rw) {
-    static int cached = -1, ccw = 0, crw = 0;
-    if (cached < 0) {
-        const char *e = getenv("LLOOM_GEMV_SHAPE");
-        cached = (e && sscanf(e, "%d,%d", &ccw, &crw) == 2 && ccw >= 1 && ccw <= 12 && (crw == 1 || crw == 2) &&
-                  (ccw <= 8 || crw == 1))
-                     ? 1
-                     : 0;
-    }
-    cw = ccw;
-    rw = crw;
-    return cached == 1;
-}
-
-template <int SPLIT, int EPI>
-static cudaError_t launch_gemv_mma_inst(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    auto kern = gemv_mma_q4k_kernel<SPLIT, EPI>;
-    static int configured_smem[64] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_smem[dev] < smem) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured_smem[dev] = smem;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(32u * (kMmaWarps + 1));
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = overlap ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, p);
-}
-
-static cudaError_t launch_gemv_mma(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    // whole rows per stage: four teams of four warps, a tile each; rows cut into pieces: one team of sixteen, so
-    // that a piece is consumed (and its stage handed back) as fast as possible
-    if (gemv_needs_epi(p)) {
-        if (p.nchunks > 1) return launch_gemv_mma_inst<16, 1>(p, grid, smem, overlap, stream);
-        return launch_gemv_mma_inst<4, 1>(p, grid, smem, overlap, stream);
-    }
-    if (p.nchunks > 1) return launch_gemv_mma_inst<16, 0>(p, grid, smem, overlap, stream);
-    return launch_gemv_mma_inst<4, 0>(p, grid, smem, overlap, stream);
-}
-
-// Development knob: LLOOM_GEMV_MMA=0 keeps 2 <= m <= 8 on the dp4a kernel.
-static bool gemv_mma_enabled() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char *e = getenv("LLOOM_GEMV_MMA");
-        cached = (e && e[0] == '0') ? 0 : 1;
-    }
-    return cached == 1;
 }
 
 // Whether the tensor-core GEMV quantizes the activations itself (as its prologue): up to two rows, and few enough
@@ -214,7 +112,7 @@ struct MmaPlan {
 
 static MmaPlan gemv_mma_plan(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
     MmaPlan pl;
-    if (w_dtype != LLOOM_Q4_K || m < 2 || m > 8 || !gemv_mma_enabled()) return pl;
+    if (w_dtype != LLOOM_Q4_K || m < 2 || m > 8) return pl;
     const int64_t nb = k / QK_K;
     const int64_t total = (n + kMmaTileRows - 1) / kMmaTileRows;
     const int64_t grid = total < di.sm_count ? total : di.sm_count;
@@ -248,26 +146,44 @@ static bool gemv_mma_fits(const DeviceInfo &di, int w_dtype, int64_t m, int64_t 
     return gemv_mma_plan(di, w_dtype, m, n, k).ok;
 }
 
-// Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
-// quantized in the kernel's prologue) is non-null.
 struct PeerFlags {  // one flag array per GPU: kMaxPeers slots written by the peers + this GPU's call counter
     unsigned int *f[kMaxPeers];
 };
 
-struct PeerOut {  // fused gather: output buffers of all GPUs (own included), already offset to this shard's column
-    int n = 0;
+// Where the outputs go, beyond the plain y: the fused gather (output buffers of all GPUs, own included, already offset
+// to this shard's column), a block on the store, and the flag traffic of a gather with its barrier folded in.
+struct GemvOut {
+    int n_peers = 0;
     float *y[kMaxPeers] = {};
-    int store = LLOOM_STORE_PLAIN;  // block on the store (also used alone, with n == 0)
+    int store = LLOOM_STORE_PLAIN;
+    int rank = 0;
+    bool publish = false;
+    unsigned int *flags[kMaxPeers] = {};
+    const unsigned int *wait_flags = nullptr;
+    int wait_peers = 0;
 };
 
+// Several matrices of one dtype and k behind one launch (the activations are shared).
+struct GemvGroup {
+    int count = 0;
+    const uint8_t *w[kMaxGroup] = {};
+    float *y[kMaxGroup] = {};
+    int64_t n[kMaxGroup] = {};
+    int64_t ldy[kMaxGroup] = {};
+    int store[kMaxGroup] = {};
+};
+
+// Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
+// quantized in the kernel's prologue) is non-null.  With a group, w / y / n / ldy are ignored (n = total rows).
 static int gemv_launch(int w_dtype, const void *w, const void *act, const float *x, float *y, int64_t m, int64_t n,
                        int64_t k, int64_t ldy, cudaStream_t stream, bool act_planes = false,
-                       const PeerOut *peers = nullptr) {
+                       const GemvOut *out = nullptr, const GemvGroup *group = nullptr) {
     DeviceInfo di;
     int rc = device_info(di);
     if (rc != LLOOM_OK) return rc;
     if (act_planes && !gemv_mma_fits(di, w_dtype, m, n, k)) return LLOOM_ERR_SHAPE;
     GemvParams p;
+    memset(&p, 0, sizeof(p));
     p.w = (const uint8_t *)w;
     p.act = (const uint8_t *)act;
     p.x = x;
@@ -280,21 +196,37 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     p.m = (int)m;
     p.w_dtype = w_dtype;
     p.act_bytes = (int)act_plane_bytes(w_dtype, m, k);
-    p.row_pitch = 0;
-    p.act_pitch = 0;
-    p.act_planes = 0;
-    p.tile_bar_bytes = 0;
-    p.chunk_sb = 0;
     p.nchunks = 1;
-    p.chunk_units = 0;
-    p.unit_bytes = w_dtype == LLOOM_Q4_K ? Q4K_BYTES : w_dtype == LLOOM_Q6_K ? Q6K_BYTES : 2 * Q8_0_BYTES;
-    p.n_peers = peers ? peers->n : 0;
-    p.out_bytes = 0;
-    p.out_pitch = 0;
-    p.store_mode = peers ? peers->store : LLOOM_STORE_PLAIN;
-    for (int g = 0; g < kMaxPeers; ++g) p.y_peer[g] = (peers && g < peers->n) ? peers->y[g] : nullptr;
-    // lanes per row: one lane per unit (superblock, or pair of Q8_0 blocks), rounded up to a power of two
-    const int64_t units = k / (w_dtype == LLOOM_Q8_0 ? 64 : 256);
+    p.unit_bytes = (int)((act_is_q8_0(w_dtype) ? 2 : 1) * lloom_b200_block_bytes(w_dtype));
+    p.n_peers = out ? out->n_peers : 0;
+    p.store_mode = out ? out->store : LLOOM_STORE_PLAIN;
+    if (out) {
+        p.publish = out->publish ? 1 : 0;
+        p.peer_rank = out->rank;
+        p.wait_flags = out->wait_flags;
+        p.wait_peers = out->wait_peers;
+        for (int g = 0; g < kMaxPeers; ++g) {
+            p.y_peer[g] = g < out->n_peers ? out->y[g] : nullptr;
+            p.peer_flags[g] = g < out->n_peers ? out->flags[g] : nullptr;
+        }
+    }
+    if (group) {
+        p.n_group = group->count;
+        int64_t off = 0;
+        for (int g = 0; g < group->count; ++g) {
+            p.gw[g] = group->w[g];
+            p.gy[g] = group->y[g];
+            p.gldy[g] = group->ldy[g];
+            p.gstore[g] = group->store[g];
+            p.goff[g] = (int)off;
+            off += group->n[g];
+        }
+        p.goff[group->count] = (int)off;
+        p.n = (int)off;
+        n = off;
+    }
+    // lanes per row: one lane per unit (superblock, or pair of 32-element blocks), rounded up to a power of two
+    const int64_t units = k / (act_is_q8_0(w_dtype) ? 64 : 256);
     int lpr_log2 = 0;
     while ((1 << lpr_log2) < units && lpr_log2 < 5) ++lpr_log2;
     p.lpr_log2 = lpr_log2;
@@ -304,7 +236,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
     const int64_t pad = (p.row_bytes % 16 == 0) ? 16 : 48;
     int grid = di.sm_count;
     if ((int64_t)grid > n) grid = (int)n;
-    const bool overlap_on = g_launch_overlap.load(std::memory_order_relaxed) != 0;
+    const bool overlap = g_launch_overlap.load(std::memory_order_relaxed) != 0;
     // Fused gather: room to stage a CTA's output rows (so that they leave for the peers in whole lines), if small
     auto staging = [&](int64_t rows_per_cta, int &pitch) -> int64_t {
         if (p.n_peers == 0) return 0;
@@ -312,8 +244,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         const int64_t bytes = (int64_t)m * pitch * 4;
         return bytes <= 32 * 1024 ? bytes : 0;
     };
-    // 3..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
-    const MmaPlan plan = gemv_mma_plan(di, w_dtype, m, n, k);
+    // 2..8 activation rows of Q4_K: the tensor-core kernel, if two 16-row stages fit beside the activations
+    const MmaPlan plan = group ? MmaPlan() : gemv_mma_plan(di, w_dtype, m, n, k);
     if (plan.ok && (x == nullptr || gemv_mma_fused(m, k))) {
         const int64_t stage = plan.stage;
         p.act_bytes = (int)mma_act_bytes(m, k);
@@ -324,8 +256,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.chunk_sb = plan.chunk_sb;
         p.nchunks = plan.nchunks;
         const int64_t room = plan.room;
+        const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
         {
-            const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
             const int64_t g = total_tiles < grid ? total_tiles : grid;
             int pitch = 0;
             const int64_t want = staging((total_tiles + g - 1) / g * kMmaTileRows, pitch);
@@ -340,26 +272,28 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
         const int smem = kMmaBarBytes + kMmaRedBytes + p.tile_bar_bytes + p.act_bytes + p.out_bytes + (int)(stages * stage);
-        const int64_t total_tiles = (n + kMmaTileRows - 1) / kMmaTileRows;
         if (grid > total_tiles) grid = (int)total_tiles;
-        return launch_status(launch_gemv_mma(p, grid, smem, overlap_on, stream));
+        return launch_status(launch_gemv_mma(p, grid, smem, overlap, stream));
     }
-    // Tile shapes {consumer warps, rows per lane}, widest first (after an optional pinned shape); the
-    // first that leaves room for at least two stages wins.  With launch overlap on, m <= 2 tries shapes
-    // that fit two CTAs per SM first, so that consecutive launches can sit side by side.
+    // Tile shapes {consumer warps, rows per lane}, widest first; the first that leaves room for at least two stages
+    // wins.  With launch overlap on, m <= 2 tries shapes that fit two CTAs per SM first, so that consecutive
+    // launches can sit side by side.  A grouped launch runs the eight-warp, one-row-per-lane shapes only.
     struct Shape { int cw, rw; bool half; };
     Shape shapes[12];
-    int ns = 0, ocw = 0, orw = 0;
-    const bool overlap = g_launch_overlap.load(std::memory_order_relaxed) != 0;
-    if (gemv_shape_override(ocw, orw)) shapes[ns++] = {ocw, orw, overlap && orw == 1};
-    if (overlap && m <= 2) {  // HBM-bound batch sizes only: wider batches need the registers and the row tiling
-        // twelve consumer warps pay off for Q8_0 (cheap units, more of them per row); the k-quants are best at eight
-        if (w_dtype == LLOOM_Q8_0) shapes[ns++] = {12, 1, true};
-        const int half_cw[4] = {8, 4, 2, 1};
-        for (int c : half_cw) shapes[ns++] = {c, 1, true};
+    int ns = 0;
+    if (group) {
+        if (overlap) shapes[ns++] = {8, 1, true};
+        shapes[ns++] = {8, 1, false};
+    } else {
+        if (overlap && m <= 2) {  // HBM-bound batch sizes only: wider batches need the registers and the row tiling
+            // twelve consumer warps pay off for Q8_0 (cheap units, more of them per row); the k-quants are best at eight
+            if (w_dtype == LLOOM_Q8_0) shapes[ns++] = {12, 1, true};
+            const int half_cw[4] = {8, 4, 2, 1};
+            for (int c : half_cw) shapes[ns++] = {c, 1, true};
+        }
+        const int full[5][2] = {{8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};
+        for (auto &f : full) shapes[ns++] = {f[0], f[1], false};
     }
-    const int full[5][2] = {{8, 2}, {8, 1}, {4, 1}, {2, 1}, {1, 1}};
-    for (auto &f : full) shapes[ns++] = {f[0], f[1], false};
     int out_pitch = 0;
     const int64_t out_want = staging((n + grid - 1) / grid, out_pitch);
     for (int si = 0; si < ns; ++si) {
@@ -372,13 +306,13 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.chunk_units = 0;
         p.lpr_log2 = lpr_log2;
         if (budget < 2 * stage) {
-            // Long rows in a side-by-side shape: cut the rows into pieces of 16 units (32 for Q8_0), so that a stage
-            // is 16 (8) rows x one piece -- the tile the kernel streams at K = 4096 -- instead of giving up the
-            // overlap between consecutive launches for a one-CTA-per-SM shape.
-            if (!shapes[si].half || cw > 8 || p.row_bytes % 16 != 0) continue;
-            const int cu = w_dtype == LLOOM_Q8_0 ? 32 : 16;
+            // Long rows in a side-by-side shape: cut the rows into pieces of 16 units (32 for 64-element units), so
+            // that a stage is 16 (8) rows x one piece -- the tile the kernel streams at K = 4096 -- instead of giving
+            // up the overlap between consecutive launches for a one-CTA-per-SM shape.
+            if (group || !shapes[si].half || cw > 8 || p.row_bytes % 16 != 0) continue;
+            const int cu = act_is_q8_0(w_dtype) ? 32 : 16;
             if (units <= cu || ((int64_t)cu * p.unit_bytes) % 16 != 0) continue;
-            const int cl = w_dtype == LLOOM_Q8_0 ? 5 : 4;
+            const int cl = act_is_q8_0(w_dtype) ? 5 : 4;
             const int64_t pstage = round16((int64_t)cw * (32 >> cl) * rw * cu * p.unit_bytes + pad);
             if (budget < 2 * pstage) continue;
             stage = pstage;
@@ -399,9 +333,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.stages = (int)stages;
         p.stage_bytes = (int)stage;
         const int smem = 128 + p.act_bytes + p.out_bytes + (int)(stages * stage);
-        cudaError_t e = (rw == 2) ? launch_gemv_fmt<2>(p, grid, smem, overlap, stream)
-                                  : launch_gemv_fmt<1>(p, grid, smem, overlap, stream);
-        return launch_status(e);
+        return launch_status(launch_gemv_dp4a(p, grid, smem, overlap, rw, stream));
     }
     return LLOOM_ERR_SHAPE;  // one row of weights plus the activations does not fit in shared memory
 }
@@ -440,9 +372,13 @@ static int static_scratch_ptr(void **out) {
     return LLOOM_OK;
 }
 
+static int64_t act_blocks_bytes(int w_dtype, int64_t m, int64_t k) {
+    return (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
+}
+
 // Decode forward (m <= 8) after argument checks: quantizer + GEMV, outputs to `y` or to the peers' buffers.
 static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n, int64_t k,
-                      int64_t ldy, void *workspace, int64_t need, void *stream, const PeerOut *peers) {
+                      int64_t ldy, void *workspace, int64_t need, void *stream, const GemvOut *out) {
     int rc;
     {
         DeviceInfo di;
@@ -452,23 +388,50 @@ static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *
         // up to two rows: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
         // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
         if ((m <= 2 && !mma) || (mma && gemv_mma_fused(m, k)))
-            return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream, false, peers);
+            return gemv_launch(w_dtype, w_blocks, nullptr, x, y, m, n, k, ldy, (cudaStream_t)stream, false, out);
         // Q4_K batches for the tensor-core GEMV: the quantizer writes the kernel's own activation image (same
         // codes, scales and sums as the canonical blocks, laid out for its fragment loads)
         if (mma && mma_act_bytes(m, k) <= need) {
-            const int nb = (int)(k / QK_K);
-            quantize_q8k_planes_kernel<<<(unsigned)ceil_div64(m * nb * 32, 256), 256, 0, (cudaStream_t)stream>>>(
-                x, (uint8_t *)workspace, (int)m, nb, (int)mma_act_pitch(k));
-            rc = launch_status(cudaGetLastError());
+            rc = launch_status(launch_quantize_q8k_planes(x, (uint8_t *)workspace, (int)m, (int)(k / QK_K),
+                                                          (int)mma_act_pitch(k), (cudaStream_t)stream));
             if (rc != LLOOM_OK) return rc;
-            return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, true, peers);
+            return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, true, out);
         }
     }
     rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
     if (rc != LLOOM_OK) return rc;
-    return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, false, peers);
+    return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, false, out);
 }
 
+// Prefill forward (m > 8) after argument checks: canonical activation blocks are in `act`; `scratch` follows them.
+static int gemm_dispatch(int w_dtype, const void *w_blocks, const void *w_image, const void *act, float *y, int64_t m,
+                         int64_t n, int64_t k, int64_t ldy, void *scratch, void *stream) {
+    DeviceInfo di;
+    int rc = device_info(di);
+    if (rc != LLOOM_OK) return rc;
+    if (gemm_supported(w_dtype, m, k, di.max_smem_optin))
+        return launch_status(gemm_forward(w_dtype, w_blocks, w_image, act, y, m, n, k, ldy, scratch, (cudaStream_t)stream));
+    // Shapes no tensor-core kernel takes: slabs of up to 8 activation rows through the GEMV.
+    const int64_t arow = lloom_b200_act_row_bytes(w_dtype, k);
+    for (int64_t r = 0; r < m; r += 8) {
+        const int64_t mm = (m - r < 8) ? (m - r) : 8;
+        rc = gemv_launch(w_dtype, w_blocks, (const uint8_t *)act + r * arow, nullptr, y + r * ldy, mm, n, k, ldy,
+                         (cudaStream_t)stream);
+        if (rc != LLOOM_OK) return rc;
+    }
+    return LLOOM_OK;
+}
+
+static int fwd_checks(int w_dtype, const void *w_blocks, const float *x, const float *y, int64_t m, int64_t n, int64_t k,
+                      int64_t ldy, const void *workspace, int64_t workspace_bytes, int64_t need) {
+    int rc = check_common(w_dtype, m, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (ldy < n) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !x || !y) return LLOOM_ERR_NULL;
+    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    return LLOOM_OK;
+}
 
 }  // namespace lloom
 
@@ -502,15 +465,27 @@ int lloom_b200_set_launch_overlap(int enable) {
 
 int lloom_b200_device_status(int *status_out) {
     if (!status_out) return LLOOM_ERR_NULL;
-    int v = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));
-    if (e != cudaSuccess) return launch_status(e);
-    if (v != 0) {
-        int zero = 0;
-        e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    TuRegistry &r = tu_registry();
+    std::lock_guard<std::mutex> lock(r.mu);  // one reader at a time: the fetch goes through a per-unit landing word
+    int status = 0;
+    for (const TuHooks &h : r.hooks) {
+        int v = 0;
+        const cudaError_t e = h.fetch_status(&v, nullptr);  // device-side atomic exchange, then a synchronous read
+        if (e != cudaSuccess) return launch_status(e);
+        if (v != 0) status = v;
+    }
+    *status_out = status;
+    return LLOOM_OK;
+}
+
+int lloom_b200_set_wait_limit_ns(uint64_t ns) {
+    if (ns == 0) ns = kDefaultWaitNs;
+    TuRegistry &r = tu_registry();
+    std::lock_guard<std::mutex> lock(r.mu);
+    for (const TuHooks &h : r.hooks) {
+        const cudaError_t e = h.set_wait_limit((unsigned long long)ns);
         if (e != cudaSuccess) return launch_status(e);
     }
-    *status_out = v;
     return LLOOM_OK;
 }
 
@@ -548,8 +523,30 @@ int64_t lloom_b200_act_row_bytes(int w_dtype, int64_t k) {
 
 int64_t lloom_b200_workspace_bytes(int w_dtype, int64_t m, int64_t n, int64_t k) {
     if (check_common(w_dtype, m, n, k) != LLOOM_OK) return 0;
-    int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
-    return act + gemm_scratch_bytes(w_dtype, m, n, k);
+    return act_blocks_bytes(w_dtype, m, k) + gemm_scratch_bytes(w_dtype, m, n, k, false);
+}
+
+int64_t lloom_b200_workspace_bytes_with_image(int w_dtype, int64_t m, int64_t n, int64_t k) {
+    if (check_common(w_dtype, m, n, k) != LLOOM_OK) return 0;
+    return act_blocks_bytes(w_dtype, m, k) + gemm_scratch_bytes(w_dtype, m, n, k, true);
+}
+
+int64_t lloom_b200_weight_image_bytes(int w_dtype, int64_t n, int64_t k) {
+    if (check_common(w_dtype, 1, n, k) != LLOOM_OK) return 0;
+    if (!gemm_supported(w_dtype, 9, k, 1 << 30)) return 0;
+    return gemm_weight_image_bytes(w_dtype, n, k);
+}
+
+int lloom_b200_weight_image_build(int w_dtype, const void *w_blocks, int64_t n, int64_t k, void *image, int64_t image_bytes,
+                                  void *stream) {
+    int rc = check_common(w_dtype, 1, n, k);
+    if (rc != LLOOM_OK) return rc;
+    const int64_t need = lloom_b200_weight_image_bytes(w_dtype, n, k);
+    if (need <= 0) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !image) return LLOOM_ERR_NULL;
+    if (image_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(w_blocks, 16) || !aligned(image, 1024)) return LLOOM_ERR_ALIGN;
+    return launch_status(gemm_weight_image_build(w_dtype, w_blocks, n, k, image, (cudaStream_t)stream));
 }
 
 int lloom_b200_quantize_act(int w_dtype, const float *x, int64_t m, int64_t k, void *act_blocks, void *stream) {
@@ -577,62 +574,116 @@ int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, f
     if (ldy < n) return LLOOM_ERR_SHAPE;
     if (!w_blocks || !act_blocks || !y) return LLOOM_ERR_NULL;
     if (!aligned(w_blocks, 16) || !aligned(act_blocks, 4) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
-    const int64_t need = gemm_scratch_bytes(w_dtype, m, n, k);
+    const int64_t need = gemm_scratch_bytes(w_dtype, m, n, k, false);
     if (need > 0 && (!workspace || workspace_bytes < need)) return LLOOM_ERR_WORKSPACE;
     if (need > 0 && !aligned(workspace, 256)) return LLOOM_ERR_ALIGN;
-    DeviceInfo di;
-    rc = device_info(di);
-    if (rc != LLOOM_OK) return rc;
-    bool handled = false;
-    rc = gemm_launch(w_dtype, w_blocks, act_blocks, y, m, n, k, ldy, workspace, di.sm_count, di.max_smem_optin,
-                     (cudaStream_t)stream, handled, t_last_cuda_error);
-    if (handled) return rc;
-    // Shapes the tensor-core kernel does not take: slabs of up to 8 activation rows through the GEMV.
-    const int64_t arow = lloom_b200_act_row_bytes(w_dtype, k);
-    for (int64_t r = 0; r < m; r += 8) {
-        const int64_t mm = (m - r < 8) ? (m - r) : 8;
-        rc = gemv_launch(w_dtype, w_blocks, (const uint8_t *)act_blocks + r * arow, nullptr, y + r * ldy, mm, n, k, ldy,
-                         (cudaStream_t)stream);
-        if (rc != LLOOM_OK) return rc;
-    }
-    return LLOOM_OK;
+    return gemm_dispatch(w_dtype, w_blocks, nullptr, act_blocks, y, m, n, k, ldy, workspace, stream);
 }
 
 int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
                            int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes, void *stream) {
-    int rc = check_common(w_dtype, m, n, k);
-    if (rc != LLOOM_OK) return rc;
-    if (ldy < n) return LLOOM_ERR_SHAPE;
-    if (!w_blocks || !x || !y) return LLOOM_ERR_NULL;
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
-    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
-    if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
+    int rc = fwd_checks(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, workspace_bytes, need);
+    if (rc != LLOOM_OK) return rc;
     if (m <= 8) return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, nullptr);
     rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
     if (rc != LLOOM_OK) return rc;
-    const int64_t act = (m * lloom_b200_act_row_bytes(w_dtype, k) + 255) / 256 * 256;
-    return lloom_b200_gemm(w_dtype, w_blocks, workspace, y, m, n, k, ldy, (uint8_t *)workspace + act,
-                           workspace_bytes - act, stream);
+    return gemm_dispatch(w_dtype, w_blocks, nullptr, workspace, y, m, n, k, ldy,
+                         (uint8_t *)workspace + act_blocks_bytes(w_dtype, m, k), stream);
+}
+
+int lloom_b200_qmatmul_fwd_image(int w_dtype, const void *w_blocks, const void *w_image, const float *x, float *y,
+                                 int64_t m, int64_t n, int64_t k, int64_t ldy, void *workspace, int64_t workspace_bytes,
+                                 void *stream) {
+    if (!w_image) return lloom_b200_qmatmul_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, workspace_bytes, stream);
+    const int64_t need = lloom_b200_workspace_bytes_with_image(w_dtype, m, n, k);
+    int rc = fwd_checks(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, workspace_bytes, need);
+    if (rc != LLOOM_OK) return rc;
+    if (!aligned(w_image, 1024)) return LLOOM_ERR_ALIGN;
+    if (m <= 8) return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, nullptr);
+    if (lloom_b200_weight_image_bytes(w_dtype, n, k) <= 0) return LLOOM_ERR_SHAPE;  // no image exists for this shape
+    rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
+    if (rc != LLOOM_OK) return rc;
+    return gemm_dispatch(w_dtype, w_blocks, w_image, workspace, y, m, n, k, ldy,
+                         (uint8_t *)workspace + act_blocks_bytes(w_dtype, m, k), stream);
 }
 
 int lloom_b200_qmatmul_fwd_store(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
                                  int64_t k, int64_t ldy, int store, void *workspace, int64_t workspace_bytes,
                                  void *stream) {
-    int rc = check_common(w_dtype, m, n, k);
-    if (rc != LLOOM_OK) return rc;
-    if (m > 8 || ldy < n || store < LLOOM_STORE_PLAIN || store > LLOOM_STORE_MUL_INTO) return LLOOM_ERR_SHAPE;
-    if (!w_blocks || !x || !y) return LLOOM_ERR_NULL;
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
-    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
-    if (!aligned(workspace, 256) || !aligned(w_blocks, 16) || !aligned(x, 16) || !aligned(y, 4)) return LLOOM_ERR_ALIGN;
-    PeerOut out;
+    int rc = fwd_checks(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, workspace_bytes, need);
+    if (rc != LLOOM_OK) return rc;
+    if (m > 8 || store < LLOOM_STORE_PLAIN || store > LLOOM_STORE_MUL_INTO) return LLOOM_ERR_SHAPE;
+    GemvOut out;
     out.store = store;
     return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, &out);
 }
 
-int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard, int64_t k,
-                                  int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, void *workspace,
-                                  int64_t workspace_bytes, void *stream) {
+int lloom_b200_qmatmul_fwd_group(int w_dtype, int n_mats, const void *const *w_blocks, const float *x, float *const *ys,
+                                 const int64_t *ns, const int64_t *ldys, const int *stores, int64_t m, int64_t k,
+                                 void *workspace, int64_t workspace_bytes, void *stream) {
+    if (n_mats < 1 || n_mats > kMaxGroup) return LLOOM_ERR_SHAPE;
+    if (!w_blocks || !x || !ys || !ns || !ldys) return LLOOM_ERR_NULL;
+    if (m > 8) return LLOOM_ERR_SHAPE;
+    GemvGroup group;
+    group.count = n_mats;
+    int64_t n_max = 0, n_total = 0;
+    for (int g = 0; g < n_mats; ++g) {
+        int rc = check_common(w_dtype, m, ns[g], k);
+        if (rc != LLOOM_OK) return rc;
+        if (ldys[g] < ns[g]) return LLOOM_ERR_SHAPE;
+        if (!w_blocks[g] || !ys[g]) return LLOOM_ERR_NULL;
+        if (!aligned(w_blocks[g], 16) || !aligned(ys[g], 4)) return LLOOM_ERR_ALIGN;
+        const int store = stores ? stores[g] : LLOOM_STORE_PLAIN;
+        if (store < LLOOM_STORE_PLAIN || store > LLOOM_STORE_MUL_INTO) return LLOOM_ERR_SHAPE;
+        group.w[g] = (const uint8_t *)w_blocks[g];
+        group.y[g] = ys[g];
+        group.n[g] = ns[g];
+        group.ldy[g] = ldys[g];
+        group.store[g] = store;
+        if (ns[g] > n_max) n_max = ns[g];
+        n_total += ns[g];
+    }
+    if (n_total > (1ll << 30)) return LLOOM_ERR_SHAPE;
+    const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n_max, k);
+    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(workspace, 256) || !aligned(x, 16)) return LLOOM_ERR_ALIGN;
+    DeviceInfo di;
+    int rc = device_info(di);
+    if (rc != LLOOM_OK) return rc;
+    // One launch for the whole group where the dp4a kernel with its quantizer prologue is the decode path anyway
+    // (one row; two rows of the formats without a tensor-core GEMV) and whole rows fit its stages.
+    const bool one_launch = n_mats > 1 && (m == 1 || (m == 2 && !gemv_mma_fits(di, w_dtype, m, n_max, k)));
+    if (one_launch) {
+        rc = gemv_launch(w_dtype, nullptr, nullptr, x, nullptr, m, 0, k, 0, (cudaStream_t)stream, false, nullptr, &group);
+        if (rc != LLOOM_ERR_SHAPE) return rc;  // rows too long for whole-row stages: matrix by matrix below
+    }
+    // Otherwise the activations are quantized once and every matrix gets its own GEMV launch.
+    const bool mma = gemv_mma_fits(di, w_dtype, m, n_max, k);
+    bool all_mma = mma;
+    for (int g = 0; g < n_mats && all_mma; ++g) all_mma = gemv_mma_fits(di, w_dtype, m, ns[g], k);
+    if (all_mma && mma_act_bytes(m, k) <= need) {
+        rc = launch_status(launch_quantize_q8k_planes(x, (uint8_t *)workspace, (int)m, (int)(k / QK_K), (int)mma_act_pitch(k),
+                                                      (cudaStream_t)stream));
+    } else {
+        all_mma = false;
+        rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
+    }
+    if (rc != LLOOM_OK) return rc;
+    for (int g = 0; g < n_mats; ++g) {
+        GemvOut out;
+        out.store = group.store[g];
+        rc = gemv_launch(w_dtype, group.w[g], workspace, nullptr, group.y[g], m, group.n[g], k, group.ldy[g],
+                         (cudaStream_t)stream, all_mma, &out);
+        if (rc != LLOOM_OK) return rc;
+    }
+    return LLOOM_OK;
+}
+
+static int gather_common(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard, int64_t k,
+                         int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, void *workspace,
+                         int64_t workspace_bytes, void *stream, GemvOut &peers) {
     int rc = check_common(w_dtype, m, n_shard, k);
     if (rc != LLOOM_OK) return rc;
     if (m > 8 || n_peers < 1 || n_peers > kMaxPeers || col0 < 0 || ldy < col0 + n_shard) return LLOOM_ERR_SHAPE;
@@ -640,14 +691,79 @@ int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float 
     const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n_shard, k);
     if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
     if (!aligned(workspace, 256) || !aligned(w_shard, 16) || !aligned(x, 16)) return LLOOM_ERR_ALIGN;
-    PeerOut peers;
-    peers.n = n_peers;
+    peers.n_peers = n_peers;
     for (int g = 0; g < n_peers; ++g) {
         if (!y_peers[g]) return LLOOM_ERR_NULL;
         if (!aligned(y_peers[g], 4)) return LLOOM_ERR_ALIGN;
         peers.y[g] = y_peers[g] + col0;
     }
     return decode_fwd(w_dtype, w_shard, x, peers.y[0], m, n_shard, k, ldy, workspace, need, stream, &peers);
+}
+
+int lloom_b200_qmatmul_fwd_gather(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard, int64_t k,
+                                  int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, void *workspace,
+                                  int64_t workspace_bytes, void *stream) {
+    GemvOut peers;
+    return gather_common(w_dtype, w_shard, x, m, n_shard, k, ldy, col0, y_peers, n_peers, workspace, workspace_bytes, stream,
+                         peers);
+}
+
+int lloom_b200_qmatmul_fwd_gather_sync(int w_dtype, const void *w_shard, const float *x, int64_t m, int64_t n_shard,
+                                       int64_t k, int64_t ldy, int64_t col0, float *const *y_peers, int n_peers, int rank,
+                                       unsigned int *const *flag_peers, const unsigned int *wait_flags, void *workspace,
+                                       int64_t workspace_bytes, void *stream) {
+    if (n_peers < 1 || n_peers > kMaxPeers || rank < 0 || rank >= n_peers) return LLOOM_ERR_SHAPE;
+    if (!flag_peers) return LLOOM_ERR_NULL;
+    if (wait_flags && m > 2) return LLOOM_ERR_SHAPE;  // the wait sits in the GEMV's own quantizer prologue (m <= 2)
+    GemvOut peers;
+    peers.publish = true;
+    peers.rank = rank;
+    for (int g = 0; g < n_peers; ++g) {
+        if (!flag_peers[g]) return LLOOM_ERR_NULL;
+        if (!aligned(flag_peers[g], 4)) return LLOOM_ERR_ALIGN;
+        peers.flags[g] = flag_peers[g];
+    }
+    peers.wait_flags = wait_flags;
+    peers.wait_peers = wait_flags ? n_peers : 0;
+    return gather_common(w_dtype, w_shard, x, m, n_shard, k, ldy, col0, y_peers, n_peers, workspace, workspace_bytes, stream,
+                         peers);
+}
+
+int lloom_b200_qmatmul_fwd_after_gather(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
+                                        int64_t k, int64_t ldy, const unsigned int *wait_flags, int n_peers,
+                                        void *workspace, int64_t workspace_bytes, void *stream) {
+    const int64_t need = lloom_b200_workspace_bytes(w_dtype, m, n, k);
+    int rc = fwd_checks(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, workspace_bytes, need);
+    if (rc != LLOOM_OK) return rc;
+    if (m > 2 || n_peers < 1 || n_peers > kMaxPeers) return LLOOM_ERR_SHAPE;  // served where the quantizer is the GEMV's prologue
+    if (!wait_flags) return LLOOM_ERR_NULL;
+    GemvOut out;
+    out.wait_flags = wait_flags;
+    out.wait_peers = n_peers;
+    return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, &out);
+}
+
+// Waits (bounded) until every slot of this GPU's flag array has reached the GPU's own call counter: the gathered
+// rows of the last lloom_b200_qmatmul_fwd_gather_sync on this stream are complete.  One warp, lane g polls slot g.
+__global__ void peer_wait_kernel(int n_peers, const unsigned int *flags) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int g = threadIdx.x;
+    if (g >= n_peers) return;
+    unsigned int want;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(want) : "l"(flags + kMaxPeers) : "memory");
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; i < kMaxSpins; ++i) {
+        unsigned int seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + g) : "memory");
+        if ((int)(seen - want) >= 0) return;
+        if ((i & 63) == 63) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > wait_limit_ns()) break;
+        }
+        __nanosleep(100);
+    }
+    atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
 }
 
 // Cross-GPU barrier after a fused gather: one small kernel per GPU.  Each GPU bumps its own epoch, publishes it in
@@ -678,11 +794,30 @@ __global__ void peer_barrier_kernel(int rank, int n_peers, PeerFlags flags) {
         if ((i & 63) == 63) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kMaxWaitNs) break;
+            else if (now - t0 > wait_limit_ns()) break;
         }
         __nanosleep(100);
     }
     atomicExch(&g_device_status, LLOOM_ERR_TIMEOUT);
+}
+
+static cudaError_t launch_one_warp(void (*kern)(int, const unsigned int *), int a, const unsigned int *b, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_launch_overlap.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, a, b);
+}
+
+int lloom_b200_peer_wait(int n_peers, const unsigned int *flags_own, void *stream) {
+    if (n_peers < 1 || n_peers > kMaxPeers) return LLOOM_ERR_SHAPE;
+    if (!flags_own) return LLOOM_ERR_NULL;
+    return launch_status(launch_one_warp(peer_wait_kernel, n_peers, flags_own, (cudaStream_t)stream));
 }
 
 int lloom_b200_peer_barrier(int rank, int n_peers, unsigned int *const *flag_peers, void *stream) {
@@ -748,17 +883,6 @@ int lloom_b200_qmatmul_fwd_static(int w_dtype, const void *w_blocks, const float
     if (rc != LLOOM_OK) return rc;
     return gemv_launch(w_dtype, w_blocks, scratch, nullptr, y, m, n, k, ldy, (cudaStream_t)stream);
 }
-
-#ifdef LLOOM_TRACE
-int lloom_b200_read_trace(unsigned long long *out, unsigned int *cnt) {  // development build only
-    cudaMemcpyFromSymbol(cnt, g_trace_cnt, sizeof(g_trace_cnt));
-    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
-}
-int lloom_b200_read_gemm2_trace(long long *out) {  // development build only
-    return (int)cudaMemcpyFromSymbol(out, g_gemm2_trace, sizeof(g_gemm2_trace));
-}
-
-#endif
 
 int lloom_b200_dequantize(int dtype, const void *blocks, int64_t elem_count, void *out, int out_is_f16,
                           void *stream) {

@@ -99,7 +99,7 @@ __device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
 }
 
 // Stand-alone Q8_0 quantizer: canonical 34-byte blocks {f16 d; i8 qs[32]}.  A warp covers 8 blocks.
-__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+static __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
                                                             int64_t total_blocks) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV behind may start streaming weights
     const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restr
 }
 
 // Stand-alone Q8_K quantizer: canonical 292-byte blocks {f32 d; i8 qs[256]; i16 bsums[16]}.
-__global__ void __launch_bounds__(256) quantize_q8k_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+static __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
                                                            int64_t total_blocks) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMV behind may start streaming weights
     const int lane = threadIdx.x & 31;
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float *__restri
     if (lane == 0) *reinterpret_cast<float *>(dst) = d;
 }
 
-inline cudaError_t launch_quantize_act(int w_dtype, const float *x, int64_t m, int64_t k, void *out,
+static inline cudaError_t launch_quantize_act(int w_dtype, const float *x, int64_t m, int64_t k, void *out,
                                        cudaStream_t stream) {
     if (w_dtype == LLOOM_Q8_0) {
         int64_t blocks = m * (k / QK8_0);

@@ -51,17 +51,24 @@ def _stream_ptr(device: torch.device) -> int:
 
 
 class _Workspace:
-    """Grow-only per-device scratch, the role of fast_mmvq.rs:44-81 / fast_mmq.rs:135-174."""
+    """Grow-only scratch per (device, stream), the role of fast_mmvq.rs:44-81 / fast_mmq.rs:135-174.
 
-    _bufs: dict[int, torch.Tensor] = {}
+    Launches on different streams never share a buffer.  A buffer that has been outgrown is kept alive for the
+    life of the process instead of being freed: a CUDA graph captured earlier may still hold its address."""
+
+    _bufs: dict[tuple[int, int], torch.Tensor] = {}
+    _retired: list[torch.Tensor] = []
 
     @classmethod
     def get(cls, device: torch.device, nbytes: int) -> torch.Tensor:
         idx = device.index if device.index is not None else torch.cuda.current_device()
-        buf = cls._bufs.get(idx)
+        key = (idx, torch.cuda.current_stream(device).cuda_stream)
+        buf = cls._bufs.get(key)
         if buf is None or buf.numel() < nbytes:
+            if buf is not None:
+                cls._retired.append(buf)
             buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-            cls._bufs[idx] = buf
+            cls._bufs[key] = buf
         return buf
 
 
@@ -72,6 +79,7 @@ class QCudaStorage:
         self._data = data  # uint8, padded
         self._len = nbytes
         self._dtype = dtype
+        self._image = None  # optional prebuilt f16 operand image for the prefill GEMM (build_prefill_image)
 
     # cuda.rs:1005-1024 load_quantized: one H2D copy of the raw block bytes, no repack, zero padding.
     @classmethod
@@ -117,6 +125,27 @@ class QCudaStorage:
     # cuda.rs:894-900 data(): the exact packed bytes.
     def data(self) -> bytes:
         return self._data[: self._len].cpu().numpy().tobytes()
+
+    def build_prefill_image(self, self_shape: Sequence[int]) -> bool:
+        """Builds, once, the f16 operand image the tensor-core GEMM reads (``lloom_b200_weight_image_build``) and keeps
+        it beside the packed blocks: later forwards with more than 8 rows skip the per-call expansion.  Costs about
+        4x the packed bytes of device memory.  Returns False (and keeps nothing) when no GEMM exists for the shape."""
+        n, k = int(self_shape[0]), int(self_shape[1])
+        L = _lib.lib()
+        nbytes = int(L.lloom_b200_weight_image_bytes(int(self._dtype), n, k))
+        if nbytes <= 0:
+            return False
+        dev = self.device()
+        img = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
+        off = (-img.data_ptr()) % 1024
+        with torch.cuda.device(dev):
+            check(L.lloom_b200_weight_image_build(int(self._dtype), self._data.data_ptr(), n, k, img.data_ptr() + off, nbytes,
+                                                  _stream_ptr(dev)), "weight_image_build")
+        self._image = (img, off)
+        return True
+
+    def drop_prefill_image(self) -> None:
+        self._image = None
 
     # cuda.rs:647-718 dequantize / dequantize_f16
     def dequantize(self, elem_count: int) -> torch.Tensor:
@@ -184,11 +213,17 @@ class QCudaStorage:
             else:  # caller-provided [m, ld] buffer: write columns [off, off+n) (row-sharded weights)
                 y = out
                 ldy, yptr = out.stride(-2) if out.dim() >= 2 else out.numel(), out.data_ptr() + 4 * out_col_offset
-            ws_bytes = int(L.lloom_b200_workspace_bytes(int(self._dtype), m, n, k))
+            image = self._image if m > 8 else None
+            ws_bytes = int((L.lloom_b200_workspace_bytes_with_image if image else L.lloom_b200_workspace_bytes)(
+                int(self._dtype), m, n, k))
             if ws_bytes <= 0:
                 raise LloomError(_lib.ERR_SHAPE, "fwd", f"unsupported shape m={m} n={n} k={k} for {self._dtype!r}")
             ws = _Workspace.get(dev, ws_bytes)
-            if store:
+            if image is not None and not store:
+                check(L.lloom_b200_qmatmul_fwd_image(int(self._dtype), self._data.data_ptr(),
+                                                     image[0].data_ptr() + image[1], x.data_ptr(), yptr, m, n, k, ldy,
+                                                     ws.data_ptr(), ws.numel(), _stream_ptr(dev)), "qmatmul_fwd_image")
+            elif store:
                 if store == 2 and out is None:
                     raise LloomError(_lib.ERR_NULL, "fwd", "the multiply-into store needs the destination buffer")
                 check(L.lloom_b200_qmatmul_fwd_store(int(self._dtype), self._data.data_ptr(), x.data_ptr(), yptr, m, n, k,
@@ -311,6 +346,42 @@ class QMatMul:
         return gate
 
 
+def forward_group(mats: Sequence["QMatMul"], xs: torch.Tensor, stores: Sequence[int] | None = None,
+                  outs: Sequence[torch.Tensor] | None = None) -> list[torch.Tensor]:
+    """Decode forward of several ``QMatMul`` that share the input ``xs`` (gate|up, q|k|v) through
+    ``lloom_b200_qmatmul_fwd_group``: one activation read and, for a single row, one launch for all of them.
+    All weights must have the same dtype, k and device; at most 8 rows.  ``stores[g]``: block on matrix g's store
+    (0 plain, 1 SiLU, 2 multiply into ``outs[g]``).  Each result equals that matrix's own ``forward`` bit for bit."""
+    import ctypes as C
+
+    if not 1 <= len(mats) <= 4:
+        raise LloomError(_lib.ERR_SHAPE, "forward_group", "1 to 4 matrices")
+    st0 = mats[0].qtensor.storage
+    dt, dev = st0.dtype(), st0.device()
+    k = mats[0].qtensor.shape[1]
+    if any(mm.qtensor.storage.dtype() != dt or mm.qtensor.shape[1] != k or mm.qtensor.device() != dev for mm in mats):
+        raise LloomError(_lib.ERR_SHAPE, "forward_group", "matrices of a group share dtype, k and device")
+    if xs.dtype != torch.float32 or not xs.is_contiguous() or xs.dim() < 2 or xs.shape[-1] != k or xs.device != dev:
+        raise LloomError(_lib.ERR_SHAPE, "forward_group", f"input {tuple(xs.shape)} {xs.dtype}")
+    m = xs.numel() // k
+    ns = [mm.qtensor.shape[0] for mm in mats]
+    if outs is None:
+        outs = [torch.empty(*xs.shape[:-1], n, dtype=torch.float32, device=dev) for n in ns]
+    G = len(mats)
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        ws_bytes = int(L.lloom_b200_workspace_bytes(int(dt), m, max(ns), k))
+        ws = _Workspace.get(dev, ws_bytes)
+        w_arr = (C.c_void_p * G)(*[mm.qtensor.device_ptr() for mm in mats])
+        y_arr = (C.c_void_p * G)(*[o.data_ptr() for o in outs])
+        n_arr = (C.c_int64 * G)(*ns)
+        ld_arr = (C.c_int64 * G)(*[o.stride(-2) if o.dim() >= 2 else o.numel() for o in outs])
+        st_arr = (C.c_int * G)(*([int(s) for s in stores] if stores is not None else [0] * G))
+        check(L.lloom_b200_qmatmul_fwd_group(int(dt), G, w_arr, xs.data_ptr(), y_arr, n_arr, ld_arr, st_arr, m, k,
+                                             ws.data_ptr(), ws.numel(), _stream_ptr(dev)), "qmatmul_fwd_group")
+    return list(outs)
+
+
 def quantize_weights_host(src, dtype: GgmlDType, nthreads: int = 0) -> np.ndarray:
     """CPU ``T::from_float`` over the rows of ``src`` through the library's host layer; uint8 [rows, row_bytes]."""
     import os
@@ -374,3 +445,8 @@ def device_status() -> int:
     v = _lib.C.c_int(0)
     check(_lib.lib().lloom_b200_device_status(_lib.C.byref(v)), "device_status")
     return v.value
+
+
+def set_wait_limit_ns(ns: int) -> None:
+    """Time limit of the kernels' bounded waits on the current device (0: the default, 2 s)."""
+    check(_lib.lib().lloom_b200_set_wait_limit_ns(int(ns)), "set_wait_limit_ns")

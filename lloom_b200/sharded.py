@@ -153,19 +153,24 @@ class ShardedQMatMul:
         mm = QMatMul.from_qtensor(QTensor.from_data(np.ascontiguousarray(raw[lo:hi]), dtype, (rows, k), device))
         return cls(lambda x: mm.forward(x.reshape(-1, k)), plan, group, local=mm)
 
-    def enable_fused_gather(self, max_m: int = 8) -> bool:
+    def enable_fused_gather(self, max_m: int = 8, sync: str = "fused") -> bool:
         """Collective.  Prepares the peer-store path for batches of up to ``max_m`` (<= 8) rows: two output buffers
         per rank (alternated call by call, so a buffer is rewritten only two forwards later) and one flag array,
-        all mapped into every process.  Returns False, changing nothing, when some rank holds no rows or the
-        group has more than eight ranks."""
+        all mapped into every process.  ``sync``: "fused" -- the GEMV's last CTA publishes the completion flags and
+        the consumer waits (``lloom_b200_qmatmul_fwd_gather_sync``); "barrier" -- a separate barrier kernel after
+        the GEMV (``lloom_b200_peer_barrier``).  Returns False, changing nothing, when some rank holds no rows or
+        the group has more than eight ranks."""
         world = self.plan.world
         if world > 8 or any(self.plan.rows_of(r) == 0 for r in range(world)) or self._local is None:
             return False
+        if sync not in ("fused", "barrier"):
+            raise ValueError(sync)
         max_m = max(1, min(8, int(max_m)))
         dev = self._local.qtensor.device()
         outs = [PeerBuffer(4 * max_m * self.plan.n, dev, self.group) for _ in range(2)]
         flags = PeerBuffer(256, dev, self.group)
-        self._fused = {"max_m": max_m, "outs": outs, "flags": flags, "turn": 0,
+        self._fused = {"max_m": max_m, "outs": outs, "flags": flags, "turn": 0, "sync": sync,
+                       "stream": torch.cuda.current_stream(dev).cuda_stream,
                        "views": [o.own_tensor().view(torch.float32) for o in outs]}
         return True
 
@@ -175,7 +180,12 @@ class ShardedQMatMul:
                 b.close(self.group)
             self._fused = None
 
-    def _forward_fused(self, x2: torch.Tensor) -> torch.Tensor:
+    def own_flags_ptr(self) -> int:
+        """Device address of this rank's flag array of the fused gather (what a consumer's prologue waits on)."""
+        f = self._fused
+        return f["flags"].ptrs[dist.get_rank(self.group)]
+
+    def _forward_fused(self, x2: torch.Tensor, after: "Optional[ShardedQMatMul]", wait: bool) -> torch.Tensor:
         from . import _lib
         from .quantized import _Workspace, _stream_ptr
 
@@ -188,22 +198,70 @@ class ShardedQMatMul:
         out, view = f["outs"][f["turn"]], f["views"][f["turn"]]
         f["turn"] ^= 1
         dev = st.device()
+        stream = _stream_ptr(dev)
+        if stream != f["stream"]:
+            raise RuntimeError("the fused gather must run on the stream it was enabled on: the two output buffers and "
+                               "the flag array are ordered by that stream alone")
         with torch.cuda.device(dev):
             ws_bytes = int(L.lloom_b200_workspace_bytes(int(st.dtype()), m, rows, k))
             ws = _Workspace.get(dev, ws_bytes)
-            _lib.check(L.lloom_b200_qmatmul_fwd_gather(int(st.dtype()), st.device_ptr(), x2.data_ptr(), m, rows, k, n, lo,
-                                                       out.array, self.plan.world, ws.data_ptr(), ws.numel(),
-                                                       _stream_ptr(dev)), "qmatmul_fwd_gather")
-            _lib.check(L.lloom_b200_peer_barrier(rank, self.plan.world, f["flags"].array, _stream_ptr(dev)), "peer_barrier")
+            if f["sync"] == "barrier":
+                _lib.check(L.lloom_b200_qmatmul_fwd_gather(int(st.dtype()), st.device_ptr(), x2.data_ptr(), m, rows, k, n,
+                                                           lo, out.array, self.plan.world, ws.data_ptr(), ws.numel(), stream),
+                           "qmatmul_fwd_gather")
+                _lib.check(L.lloom_b200_peer_barrier(rank, self.plan.world, f["flags"].array, stream), "peer_barrier")
+            else:
+                wait_flags = after.own_flags_ptr() if after is not None else None
+                _lib.check(L.lloom_b200_qmatmul_fwd_gather_sync(int(st.dtype()), st.device_ptr(), x2.data_ptr(), m, rows, k,
+                                                                n, lo, out.array, self.plan.world, rank, f["flags"].array,
+                                                                wait_flags, ws.data_ptr(), ws.numel(), stream),
+                           "qmatmul_fwd_gather_sync")
+                if wait:
+                    _lib.check(L.lloom_b200_peer_wait(self.plan.world, self.own_flags_ptr(), stream), "peer_wait")
         return view[: m * n].view(m, n)
 
-    def forward(self, xs: torch.Tensor) -> torch.Tensor:
+    def forward(self, xs: torch.Tensor, after: "Optional[ShardedQMatMul]" = None, wait: bool = True) -> torch.Tensor:
+        """``xs @ W^T`` with the rows of ``W`` split over the ranks; every rank gets the full ``[.., n]`` result.
+
+        With the fused gather enabled (and at most ``max_m`` contiguous f32 rows) the result is a *view* into this
+        rank's peer-mapped output buffer: it stays valid until the second-next fused forward of this object, and
+        every consumer of it must be ordered on the stream the gather was enabled on (each rank's next gather on
+        that stream is what tells the peers that the buffer may be rewritten).  Clone it to keep it longer.
+
+        ``wait=False`` (fused sync only) leaves out the wait kernel: the returned rows may then only be read by a
+        forward that is told so -- ``other.forward(y, after=this)`` or ``forward_after_gather`` -- whose own
+        prologue waits for all ranks' rows.  ``after``: the ShardedQMatMul whose un-waited output ``xs`` is
+        (batches of up to two rows)."""
         lead = xs.shape[:-1]
         x2 = xs.reshape(-1, xs.shape[-1])
         if (self._fused is not None and x2.shape[0] <= self._fused["max_m"] and x2.dtype == torch.float32
                 and x2.is_contiguous()):
-            return self._forward_fused(x2).reshape(*lead, self.plan.n)
+            return self._forward_fused(x2, after, wait).reshape(*lead, self.plan.n)
+        if after is not None or not wait:
+            raise RuntimeError("after= / wait=False need the fused gather")
         y_local = self._fwd(x2)
         return gather_rows(y_local, self.plan, self.group).reshape(*lead, self.plan.n)
 
     __call__ = forward
+
+
+def forward_after_gather(mm, xs: torch.Tensor, producer: ShardedQMatMul, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A replicated ``QMatMul`` forward (at most two rows) whose input is the un-waited output of ``producer``'s fused
+    gather: the GEMV waits for the gather's completion flags in its own prologue (``lloom_b200_qmatmul_fwd_after_gather``)."""
+    from . import _lib
+    from .quantized import _Workspace, _stream_ptr
+
+    L = _lib.lib()
+    st = mm.qtensor.storage
+    n, k = mm.qtensor.shape
+    x2 = xs.reshape(-1, k)
+    m = x2.shape[0]
+    dev = st.device()
+    y = out if out is not None else torch.empty(m, n, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        ws_bytes = int(L.lloom_b200_workspace_bytes(int(st.dtype()), m, n, k))
+        ws = _Workspace.get(dev, ws_bytes)
+        _lib.check(L.lloom_b200_qmatmul_fwd_after_gather(int(st.dtype()), st.device_ptr(), x2.data_ptr(), y.data_ptr(), m, n, k,
+                                                         y.stride(0), producer.own_flags_ptr(), producer.plan.world,
+                                                         ws.data_ptr(), ws.numel(), _stream_ptr(dev)), "qmatmul_fwd_after_gather")
+    return y

@@ -4,12 +4,14 @@ golden fixtures.
 Tolerances (stated here, used everywhere below):
   * quantized activation blocks: bit-exact (byte equality).
   * dequantize / get_rows: bit-exact.
-  * f32 matmul outputs: |got - ref| <= 1e-5 * A, where A is the sum of the magnitudes of the f32
+  * f32 matmul outputs: |got - ref| <= 1e-6 * A, where A is the sum of the magnitudes of the f32
     summands the reference's AVX2 arm adds for that element (eight lane terms per block, plus the four
     min-lane terms of Q4_K) -- the scale any re-ordered f32 summation, the reference's own included, is
-    bounded by -- and plain relative error |got - ref| <= 1e-5 * |ref| for every element that is not a
-    cancellation (|ref| >= A / 32).  Integer block sums are exact on both sides; only the f32
-    summation order differs from the reference's AVX2 arm.
+    bounded by (measured: 2-5e-7 for the GEMVs, below 1e-7 for the tensor-core GEMMs; the reference's own
+    scalar and AVX2 arms differ by up to 8e-8 * A) -- and plain relative error |got - ref| <= 1e-5 * |ref|
+    (the figure the specification names) for every element that is not a cancellation (|ref| >= A / 32;
+    with N(0, 0.02) weights most Q4_K outputs do cancel below that: the min term eats the main term).
+    Integer block sums are exact on both sides; only the f32 summation order differs from the AVX2 arm.
 """
 import os
 
@@ -21,7 +23,8 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-REL_TOL = 1e-5
+REL_TOL = 1e-5   # plain relative error, outputs that are not cancellations
+A_TOL = 1e-6     # |err| / A, every output
 DT_NAMES = {8: "Q8_0", 12: "Q4K", 14: "Q6K"}
 
 
@@ -36,7 +39,7 @@ def assert_matmul_close(got, ref, absum, what=""):
     assert got.shape == ref.shape
     err = np.abs(got - ref)
     scaled = err / np.maximum(absum, 1e-30)
-    assert scaled.max() <= REL_TOL, f"{what}: max |err|/A = {scaled.max():.3e}"
+    assert scaled.max() <= A_TOL, f"{what}: max |err|/A = {scaled.max():.3e}"
     solid = np.abs(ref) >= absum / 32
     if solid.any():
         rel = err[solid] / np.abs(ref[solid])
@@ -234,7 +237,7 @@ def test_gemm_q4k_prefill_config(dev, oracle):
     gemv = run_fwd(dev, 12, wq, n, k, x[:8])  # the same first eight tokens through the decode kernel
     absum8 = oracle.matmul_absum(12, x[:8], np.ascontiguousarray(wq[:4096]), 4096, nthreads=8)
     err = np.abs(gemv[:, :4096].astype(np.float64) - got[:8, :4096]) / np.maximum(absum8, 1e-30)
-    assert err.max() <= REL_TOL
+    assert err.max() <= 2 * A_TOL
     assert Q.device_status() == 0
 
 
@@ -291,39 +294,6 @@ def test_fwd_shape_rules_and_errors(dev, oracle):
     assert yh.cpu().numpy().tobytes() == ref.cpu().numpy().tobytes()
 
 
-def test_gemm_q4k_cta_pair_kernel(oracle):
-    """The opt-in CTA-pair (tcgen05 cta_group::2) GEMM kernel against the oracle, in a process of its own (the
-    switch is read once per process): ragged tiles, an odd number of 128-row weight tiles, 1..16 superblocks."""
-    import subprocess
-    import sys
-
-    code = r"""
-import sys, numpy as np, torch
-sys.path.insert(0, '.')
-from oracle import oracle as O
-import lloom_b200 as lb
-from lloom_b200 import quantized as Q
-dev = torch.device('cuda:0')
-for (n, k, m) in [(128, 256, 128), (130, 512, 70), (384, 2048, 96), (1000, 4096, 200)]:
-    rng = np.random.default_rng(n + k + m)
-    w = rng.standard_normal((n, k)).astype(np.float32) * np.float32(0.02)
-    x = rng.standard_normal((m, k)).astype(np.float32)
-    wq = Q.quantize_weights_host(w, 12)
-    qt = lb.QTensor.from_data(wq, 12, (n, k), dev)
-    got = lb.QMatMul.from_qtensor(qt).forward(torch.from_numpy(x).to(dev)).cpu().numpy()
-    assert Q.device_status() == 0
-    ref = O.matmul(12, x, wq, n, nthreads=8); A = O.matmul_absum(12, x, wq, n, nthreads=8)
-    err = np.abs(got.astype(np.float64) - ref)
-    assert (err <= 1e-5 * A + 1e-30).all(), (n, k, m, float((err / np.maximum(A, 1e-30)).max()))
-print("pair-ok")
-"""
-    import os
-    env = dict(os.environ, LLOOM_GEMM_2SM="1")
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
-    assert res.returncode == 0 and "pair-ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
-
-
 @pytest.mark.parametrize("dt,n,k", [(12, 520, 1024), (14, 300, 512), (8, 257, 256)])
 def test_store_blocks_silu_and_mul_into(dev, oracle, dt, n, k):
     """forward_silu / forward_mul_into (mod.rs:2105-2155): the product is the plain forward's, bit for bit; SiLU is
@@ -364,3 +334,235 @@ def test_q4k_long_rows(dev, oracle, n, m):
     assert run_fwd(dev, 12, wq, n, k, x).tobytes() == got.tobytes()  # run-to-run bit-stable
     half = n // 2  # a row shard gives the same bits for its rows
     assert run_fwd(dev, 12, np.ascontiguousarray(wq[half:]), n - half, k, x).tobytes() == np.ascontiguousarray(got[:, half:]).tobytes()
+
+
+def test_gemm_q4k_prefill_config_m2048(dev, oracle):
+    """C4 at M = 2048 (the size the prefill throughput is quoted on): oracle parity on a sample of rows and
+    columns, every output finite, and the prebuilt weight image gives the same bits as the per-call expansion."""
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+    from lloom_b200 import synthetic as S
+
+    n, k, m = 14336, 4096, 2048
+    wq = S.quantized_matrix(6, n, k, 12)
+    x = S.activations(7, m, k)
+    qt = lb.QTensor.from_data(wq, 12, (n, k), dev)
+    xt = torch.from_numpy(x).to(dev)
+    got_t = lb.QMatMul.from_qtensor(qt).forward(xt)
+    got = got_t.cpu().numpy()
+    assert np.isfinite(got).all()
+    rng = np.random.default_rng(11)
+    rows = np.sort(rng.choice(m, 16, replace=False))
+    cols = np.sort(rng.choice(n, 2048, replace=False))
+    wsub = np.ascontiguousarray(wq[cols])
+    ref = oracle.matmul(12, x[rows], wsub, len(cols), nthreads=8)
+    absum = oracle.matmul_absum(12, x[rows], wsub, len(cols), nthreads=8)
+    assert_matmul_close(got[np.ix_(rows, cols)], ref, absum, "C4 M=2048 sample")
+    assert qt.storage.build_prefill_image(qt.shape)
+    again = lb.QMatMul.from_qtensor(qt).forward(xt)
+    assert torch.equal(again, got_t)
+    assert Q.device_status() == 0
+
+
+def test_lm_head_q6k_full_size_and_shard(dev, oracle):
+    """C3 at full size, Q6_K [128256, 4096], M = 1: oracle parity on a row sample, and the 16032-row shard of one of
+    eight GPUs computed alone equals the same rows of the full product bit for bit."""
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+    from lloom_b200 import synthetic as S
+
+    n, k = 128256, 4096
+    wq = S.quantized_matrix(4, n, k, 14)
+    x = S.activations(5, 1, k)
+    xt = torch.from_numpy(x).to(dev)
+    full = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq, 14, (n, k), dev)).forward(xt)
+    got = full.cpu().numpy()
+    rng = np.random.default_rng(3)
+    sample = np.sort(rng.choice(n, 4096, replace=False))
+    wsub = np.ascontiguousarray(wq[sample])
+    ref = oracle.matmul(14, x, wsub, len(sample), nthreads=8)
+    absum = oracle.matmul_absum(14, x, wsub, len(sample), nthreads=8)
+    assert_matmul_close(got[:, sample], ref, absum, "C3 sample")
+    rows = n // 8
+    for g in (0, 5, 7):
+        shard = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq[g * rows:(g + 1) * rows], 14, (rows, k), dev)).forward(xt)
+        assert torch.equal(shard, full[:, g * rows:(g + 1) * rows]), g
+    assert Q.device_status() == 0
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("m", [1, 8])
+def test_decode_stack_shapes_q4k(dev, oracle, n, k, m):
+    """The Q4_K shapes of the decode matmul stack (q/o, k/v, gate/up, down) at M = 1 and 8 against the oracle (row sample
+    for the large ones)."""
+    from lloom_b200 import synthetic as S
+
+    wq = S.quantized_matrix(1000 + n % 7, n, k, 12)
+    x = S.activations(9001, m, k)
+    got = run_fwd(dev, 12, wq, n, k, x)
+    sample = np.sort(np.random.default_rng(n + k).choice(n, min(n, 1024), replace=False))
+    wsub = np.ascontiguousarray(wq[sample])
+    ref = oracle.matmul(12, x, wsub, len(sample), nthreads=8)
+    absum = oracle.matmul_absum(12, x, wsub, len(sample), nthreads=8)
+    assert_matmul_close(got[:, sample], ref, absum, f"stack shape n={n} k={k} m={m}")
+
+
+@pytest.mark.parametrize("dt,n,k,m", [(8, 128, 128, 128), (8, 130, 256, 9), (8, 300, 1024, 64), (8, 8192, 2048, 512),
+                                      (8, 77, 2048, 200), (14, 128, 256, 128), (14, 130, 512, 9), (14, 300, 1024, 64),
+                                      (14, 2004, 4096, 512), (14, 77, 2048, 200), (8, 64, 192, 40)])
+def test_gemm_q8_0_q6k_tensor_core_path(dev, oracle, dt, n, k, m):
+    """Prefill GEMM (m > 8) for Q8_0 and Q6_K on the tcgen05 kernel: ragged tiles in both directions, one to many
+    drain groups; (Q8_0 with k not a multiple of 128 runs as slabs of the GEMV)."""
+    from lloom_b200 import quantized as Q
+
+    _, x, wq = make_case(oracle, dt, n, k, m, seed=dt + n + k + m)
+    ref = oracle.matmul(dt, x, wq, n, nthreads=8)
+    absum = oracle.matmul_absum(dt, x, wq, n, nthreads=8)
+    got = run_fwd(dev, dt, wq, n, k, x)
+    assert_matmul_close(got, ref, absum, f"{DT_NAMES[dt]} gemm n={n} k={k} m={m}")
+    assert run_fwd(dev, dt, wq, n, k, x).tobytes() == got.tobytes()  # run-to-run bit-stable
+    assert Q.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [8, 12, 14])
+def test_prefill_image_same_bits(dev, oracle, dt):
+    """A forward with the prebuilt weight image equals the per-call expansion bit for bit (m > 8), and decode batches
+    ignore the image."""
+    import lloom_b200 as lb
+
+    n, k = 520, 2048
+    _, x, wq = make_case(oracle, dt, n, k, 70, seed=dt)
+    qt = lb.QTensor.from_data(wq.tobytes(), dt, (n, k), dev)
+    mm = lb.QMatMul.from_qtensor(qt)
+    xt = torch.from_numpy(x).to(dev)
+    plain, plain8 = mm.forward(xt), mm.forward(xt[:8])
+    assert qt.storage.build_prefill_image(qt.shape)
+    assert torch.equal(mm.forward(xt), plain) and torch.equal(mm.forward(xt[:8]), plain8)
+
+
+@pytest.mark.parametrize("dt,k", [(12, 4096), (14, 1024), (8, 2048)])
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+def test_grouped_forward_same_bits(dev, oracle, dt, k, m):
+    """lloom_b200_qmatmul_fwd_group (gate|up, q|k|v behind one activation read): each matrix's rows equal its own
+    forward bit for bit, with and without launch overlap, plain and with the store blocks."""
+    import lloom_b200 as lb
+    from lloom_b200 import _lib
+    from lloom_b200 import quantized as Q
+
+    ns = (1030, 257, 520)
+    mats = []
+    for i, n in enumerate(ns):
+        _, _, wq = make_case(oracle, dt, n, k, 1, seed=dt + 10 * i)
+        mats.append(lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq.tobytes(), dt, (n, k), dev)))
+    xt = torch.from_numpy(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32)).to(dev)
+    want = [mm.forward(xt) for mm in mats]
+    for overlap in (0, 1):
+        prev = _lib.lib().lloom_b200_set_launch_overlap(overlap)
+        try:
+            got = Q.forward_group(mats, xt)
+            for g, w in zip(got, want):
+                assert torch.equal(g, w)
+            got2 = Q.forward_group(mats[:2], xt)
+            assert torch.equal(got2[0], want[0]) and torch.equal(got2[1], want[1])
+            # SwiGLU through the group: silu on the first, multiply-into on a copy of it afterwards
+            gate = Q.forward_group(mats[:1], xt, stores=[1])[0]
+            assert torch.equal(gate, mats[0].forward_silu(xt))
+        finally:
+            _lib.lib().lloom_b200_set_launch_overlap(prev)
+    assert Q.device_status() == 0
+
+
+def test_bounded_wait_runs_out_and_context_survives(dev, oracle):
+    """A device-side wait that nothing satisfies: the peer wait on a flag array whose second slot is never published.
+    With the limit lowered to 50 ms the kernel returns by itself, the status word reads LLOOM_ERR_TIMEOUT once and
+    then 0 again, and a forward launched afterwards is still correct.  Nothing faults and nothing hangs."""
+    import ctypes as C
+    import time
+
+    from lloom_b200 import _lib
+    from lloom_b200 import quantized as Q
+
+    L = _lib.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    assert Q.device_status() == 0
+    Q.set_wait_limit_ns(50_000_000)
+    try:
+        flags = torch.zeros(16, dtype=torch.int32, device=dev)
+        flags[8] = 1   # this GPU's own call counter: one gather published ...
+        flags[0] = 1   # ... its own slot has arrived, slot 1 (a peer that does not exist) never will
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        assert L.lloom_b200_peer_wait(2, flags.data_ptr(), stream) == _lib.OK
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        assert 0.03 < waited < 1.5, waited
+        assert Q.device_status() == _lib.ERR_TIMEOUT
+        assert Q.device_status() == 0  # read-and-clear
+        # the barrier kernel's wait, same way: rank 0 of 2 on two local flag arrays, slot 1 never published
+        fl = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
+        ptrs = (C.c_void_p * 2)(fl[0].data_ptr(), fl[1].data_ptr())
+        assert L.lloom_b200_peer_barrier(0, 2, ptrs, stream) == _lib.OK
+        torch.cuda.synchronize()
+        assert Q.device_status() == _lib.ERR_TIMEOUT
+    finally:
+        Q.set_wait_limit_ns(0)
+    # the context is intact: an ordinary forward still matches the oracle
+    _, x, wq = make_case(oracle, 12, 300, 1024, 3, seed=77)
+    got = run_fwd(dev, 12, wq, 300, 1024, x)
+    assert_matmul_close(got, oracle.matmul(12, x, wq, 300), oracle.matmul_absum(12, x, wq, 300), "after time-out")
+    assert Q.device_status() == 0
+
+
+def test_abi_from_several_host_threads(dev, oracle):
+    """QTensor is shared across threads in the reference (Arc): forwards issued from several host threads, each on its
+    own stream with its own workspace, all give the single-threaded bits."""
+    import threading
+
+    import lloom_b200 as lb
+
+    cases = [(12, 777, 2048, 1), (14, 300, 1024, 4), (8, 515, 2048, 2), (12, 260, 1024, 40)]
+    mats, xs, want = [], [], []
+    for dt, n, k, m in cases:
+        _, x, wq = make_case(oracle, dt, n, k, m, seed=dt + m)
+        mats.append(lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq.tobytes(), dt, (n, k), dev)))
+        xs.append(torch.from_numpy(x).to(dev))
+        want.append(mats[-1].forward(xs[-1]).cpu())
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(tid):
+        try:
+            st = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(st):
+                for rep in range(20):
+                    i = (tid + rep) % len(cases)
+                    y = mats[i].forward(xs[i])
+                    st.synchronize()
+                    if not torch.equal(y.cpu(), want[i]):
+                        errors.append((tid, rep, i))
+        except Exception as e:  # noqa: BLE001
+            errors.append((tid, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(6)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:4]
+
+
+def test_second_device_in_one_process(oracle):
+    """Per-device launch configuration: a prefill GEMM and a decode GEMV on cuda:1 after the process has already run
+    them on cuda:0 (the shared-memory opt-in of a kernel is per device)."""
+    import lloom_b200 as lb
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _, x, wq = make_case(oracle, 12, 384, 1024, 40, seed=5)
+    outs = []
+    for d in (0, 1):
+        dv = torch.device("cuda", d)
+        mm = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq.tobytes(), 12, (384, 1024), dv))
+        xt = torch.from_numpy(x).to(dv)
+        outs.append((mm.forward(xt).cpu(), mm.forward(xt[:1]).cpu()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])

@@ -38,18 +38,50 @@ def _worker(rank, world, port, out_dir):
             else:       # a shard changes the GEMM's tile boundaries, not the per-element arithmetic
                 assert y.cpu().numpy().tobytes() == full.cpu().numpy().tobytes(), (rank, dt, n, k, m)
             if m <= 8:
-                # gather fused into the GEMV: peer stores + barrier kernel, no collective call; several forwards
-                # in a row (the two output buffers alternate), each on a fresh activation
-                assert sharded.enable_fused_gather(8)
-                for it in range(5):
-                    xi = x + float(it)
-                    yi = sharded.forward(xi).clone()
-                    fi = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq, dt, (n, k), dev)).forward(xi)
-                    torch.cuda.synchronize()
-                    assert yi.cpu().numpy().tobytes() == fi.cpu().numpy().tobytes(), (rank, dt, n, k, m, it, "fused")
+                # gather fused into the GEMV: peer stores, no collective call; several forwards in a row (the two
+                # output buffers alternate), each on a fresh activation.  Both completion protocols: flags published
+                # by the GEMV's last CTA + a wait kernel, and the separate barrier kernel.
                 from lloom_b200.quantized import device_status
-                assert device_status() == 0
-                sharded.close()
+                ref_mm = lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq, dt, (n, k), dev))
+                for sync in ("fused", "barrier"):
+                    assert sharded.enable_fused_gather(8, sync=sync)
+                    for it in range(5):
+                        xi = x + float(it)
+                        yi = sharded.forward(xi).clone()
+                        fi = ref_mm.forward(xi)
+                        torch.cuda.synchronize()
+                        assert yi.cpu().numpy().tobytes() == fi.cpu().numpy().tobytes(), (rank, dt, n, k, m, it, sync)
+                    assert device_status() == 0
+                    sharded.close()
+        # a chain without wait kernels: sharded up-projection -> replicated square matrix -> sharded down-projection,
+        # each consumer waiting for its producer's completion flags in its own prologue (one row)
+        from lloom_b200.sharded import forward_after_gather
+        rng = np.random.default_rng(99)
+        k0, n1 = 1024, 2048
+        w_up = quantize_weights_host(rng.standard_normal((n1, k0)).astype(np.float32) * np.float32(0.02), 12)
+        w_mid = quantize_weights_host(rng.standard_normal((n1, n1)).astype(np.float32) * np.float32(0.02), 12)
+        w_down = quantize_weights_host(rng.standard_normal((k0, n1)).astype(np.float32) * np.float32(0.02), 12)
+        up = ShardedQMatMul.from_data(w_up, 12, (n1, k0), dev)
+        down = ShardedQMatMul.from_data(w_down, 12, (k0, n1), dev)
+        mid = lb.QMatMul.from_qtensor(lb.QTensor.from_data(w_mid, 12, (n1, n1), dev))
+        full_up = lb.QMatMul.from_qtensor(lb.QTensor.from_data(w_up, 12, (n1, k0), dev))
+        full_down = lb.QMatMul.from_qtensor(lb.QTensor.from_data(w_down, 12, (k0, n1), dev))
+        assert up.enable_fused_gather(1) and down.enable_fused_gather(1)
+        x0 = torch.from_numpy(rng.standard_normal((1, k0)).astype(np.float32)).to(dev)
+        for it in range(4):
+            xi = x0 + float(it)
+            h = up.forward(xi, wait=False)
+            h2 = forward_after_gather(mid, h, up)
+            y = down.forward(h, after=up, wait=True)
+            torch.cuda.synchronize()
+            want_h = full_up.forward(xi)
+            assert torch.equal(h, want_h), (rank, it, "up")
+            assert torch.equal(h2, mid.forward(want_h)), (rank, it, "mid")
+            assert torch.equal(y, full_down.forward(want_h)), (rank, it, "down")
+        from lloom_b200.quantized import device_status
+        assert device_status() == 0
+        up.close()
+        down.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
@@ -105,6 +137,28 @@ def test_fused_gather_entry_one_gpu(cuda_lib, oracle):
         torch.cuda.synchronize()
         assert device_status() == 0
         assert int(flags[0].item()) == 1 and int(flags[8].item()) == 1  # slot of rank 0 and the call counter
+        # the same gather with the completion flags published by the GEMV itself (a group of one GPU: its own slot),
+        # then the wait kernel, then a forward that waits for those flags in its prologue
+        if True:
+            flags2 = torch.zeros(16, dtype=torch.int32, device=dev)
+            f2 = (C.c_void_p * 1)(flags2.data_ptr())
+            one = (C.c_void_p * 1)(bufs[0].data_ptr())
+            bufs[0].fill_(-7.0)
+            for call in (1, 2):
+                assert L.lloom_b200_qmatmul_fwd_gather_sync(dt, qt.device_ptr(), x.data_ptr(), m, n, k, ldy, col0, one, 1, 0,
+                                                            f2, None, ws.data_ptr(), ws.numel(), stream) == 0
+                assert L.lloom_b200_peer_wait(1, flags2.data_ptr(), stream) == 0
+                torch.cuda.synchronize()
+                assert device_status() == 0
+                assert int(flags2[0].item()) == call and int(flags2[8].item()) == call and int(flags2[9].item()) == 0
+            assert bufs[0].cpu().numpy()[:, col0:col0 + n].tobytes() == full.cpu().numpy().tobytes(), (dt, n, k, m, "sync")
+        if m <= 2:
+            y2 = torch.empty(m, n, dtype=torch.float32, device=dev)
+            assert L.lloom_b200_qmatmul_fwd_after_gather(dt, qt.device_ptr(), x.data_ptr(), y2.data_ptr(), m, n, k, n,
+                                                         flags2.data_ptr(), 1, ws.data_ptr(), ws.numel(), stream) == 0
+            torch.cuda.synchronize()
+            assert device_status() == 0
+            assert torch.equal(y2, full)
         for b in bufs:
             got = b.cpu().numpy()
             assert got[:, col0:col0 + n].tobytes() == full.cpu().numpy().tobytes(), (dt, n, k, m)
