@@ -15,12 +15,18 @@ constexpr int Q8_0_BYTES = 34;
 constexpr int Q4K_BYTES = 144;
 constexpr int Q6K_BYTES = 210;
 constexpr int Q8K_BYTES = 292;
+constexpr int Q4_0_BYTES = 18;
+constexpr int Q5_0_BYTES = 22;
+constexpr int Q5K_BYTES = 176;
 
 // Field offsets inside the canonical blocks (lloom-tensor/src/quantized/k_quants.rs:155-159, 217-223, 255-261, 265-270).
 // Q8_0 : f16 d @0, i8 qs[32] @2
 // Q4_K : f16 d @0, f16 dmin @2, u8 scales[12] @4, u8 qs[128] @16
 // Q6_K : u8 ql[128] @0, u8 qh[64] @128, i8 scales[16] @192, f16 d @208
 // Q8_K : f32 d @0, i8 qs[256] @4, i16 bsums[16] @260
+// Q4_0 : f16 d @0, u8 qs[16] @2                                   (k_quants.rs:84-91)
+// Q5_0 : f16 d @0, u8 qh[4] @2, u8 qs[16] @6                      (k_quants.rs:117-125)
+// Q5_K : f16 d @0, f16 dmin @2, u8 scales[12] @4, u8 qh[32] @16, u8 qs[128] @48   (k_quants.rs:184-192)
 
 // Device-side status word: 0, or LLOOM_ERR_TIMEOUT once a bounded wait gave up, and the time limit of those
 // waits.  The library is several translation units compiled without relocatable device code, so each unit has

@@ -1,4 +1,4 @@
-// Dequantize and row gather (embedding) for Q8_0 / Q4_K / Q6_K, exact T::to_float arithmetic.
+// Dequantize and row gather (embedding) for the six weight formats, exact T::to_float arithmetic.
 // Bandwidth kernels: one thread produces four consecutive elements (one 16-byte store).
 #pragma once
 
@@ -35,6 +35,46 @@ __device__ __forceinline__ float4 dequant4(int dtype, const uint8_t *__restrict_
         for (int i = 0; i < 4; ++i) {
             const int q = (qw >> (8 * i + 4 * hi)) & 0xF;
             r[i] = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        }
+    } else if (dtype == LLOOM_Q4_0) {
+        // k_quants.rs:299-318   y = (nibble - 8) as f32 * d; low nibbles are elements 0..15, high 16..31
+        const uint8_t *blk = row + (e >> 5) * Q4_0_BYTES;
+        const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(blk));
+        const int w = (int)(e & 31);
+        const uint8_t *q = blk + 2 + (w & 15);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = __fmul_rn((float)(((w & 16) ? (q[i] >> 4) : (q[i] & 0xF)) - 8), d);
+    } else if (dtype == LLOOM_Q5_0) {
+        // k_quants.rs:578-600   y = ((nibble | fifth bit << 4) - 16) as f32 * d
+        const uint8_t *blk = row + (e >> 5) * Q5_0_BYTES;
+        const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(blk));
+        const uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+        const int w = (int)(e & 31);
+        const uint8_t *q = blk + 6 + (w & 15);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int nib = (w & 16) ? (q[i] >> 4) : (q[i] & 0xF);
+            r[i] = __fmul_rn((float)((nib | (int)(((qh >> (w + i)) & 1u) << 4)) - 16), d);
+        }
+    } else if (dtype == LLOOM_Q5_K) {
+        // k_quants.rs:2043-2076   y = (d*sc) * (nibble + 16 * fifth bit) - (dmin*m), the code summed in f32
+        const uint8_t *blk = row + (e >> 8) * Q5K_BYTES;
+        const int w = (int)(e & 255);
+        const int g = w >> 6, hi = (w >> 5) & 1, t = w & 31;
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
+        const float d = f16_bits_to_f32(dd & 0xffffu), dmin = f16_bits_to_f32(dd >> 16);
+        const uint32_t s[3] = {*reinterpret_cast<const uint32_t *>(blk + 4), *reinterpret_cast<const uint32_t *>(blk + 8),
+                               *reinterpret_cast<const uint32_t *>(blk + 12)};
+        int sc, mn;
+        q4k_scale_min(s, 2 * g + hi, sc, mn);
+        const float d1 = __fmul_rn(d, (float)sc), m1 = __fmul_rn(dmin, (float)mn);
+        const uint32_t qw = *reinterpret_cast<const uint32_t *>(blk + 48 + 32 * g + t);
+        const uint32_t hw = *reinterpret_cast<const uint32_t *>(blk + 16 + t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int q = (qw >> (8 * i + 4 * hi)) & 0xF;
+            const float add = ((hw >> (8 * i + 2 * g + hi)) & 1u) ? 16.0f : 0.0f;
+            r[i] = __fsub_rn(__fmul_rn(d1, __fadd_rn((float)q, add)), m1);
         }
     } else {
         // k_quants.rs:2327-2358   y = d * sc * q   (left to right)

@@ -274,6 +274,168 @@ struct FmtQ8_0 {
     }
 };
 
+// Q5_K x Q8_K (k_quants.rs:1795-1880, avx.rs:528-640): Q4_K's scale scheme with a fifth code bit per element in
+// qh (bit 2g of qh[t]: element 64g + t, bit 2g + 1: element 64g + 32 + t), per superblock:
+//   out += (d_a*d_w) * sum_j sc_j * dot32(q5_j, q8_j)  +  (-d_a*dmin_w) * sum_j m_j * (bsums[2j]+bsums[2j+1])
+// Block: f16 d @0, f16 dmin @2, scales[12] @4, qh[32] @16, qs[128] @48 (176 bytes, rows stay 16-byte multiples).
+struct FmtQ5K {
+    static constexpr int kUnitElems = 256;
+    template <int MC, int RW>
+    __device__ static __forceinline__ void unit(const ActPlanes &p, int m0, int b, const uint8_t *const (&rowp)[RW],
+                                                const bool (&valid)[RW], float (&acc)[RW][MC]) {
+        float dw[RW], dminw[RW];
+        uint32_t scw[RW][2], mnw[RW][2];
+        uint4 qh[RW][2];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            if (valid[r]) {
+                const uint4 *bp = reinterpret_cast<const uint4 *>(rowp[r] + (size_t)b * Q5K_BYTES);
+                const uint4 h = bp[0];
+                qh[r][0] = bp[1];
+                qh[r][1] = bp[2];
+                dw[r] = f16_bits_to_f32(h.x & 0xffffu);
+                dminw[r] = f16_bits_to_f32(h.x >> 16);
+                scw[r][0] = h.y & 0x3f3f3f3fu;
+                scw[r][1] = (h.w & 0x0f0f0f0fu) | (((h.y >> 6) & 0x03030303u) << 4);
+                mnw[r][0] = h.z & 0x3f3f3f3fu;
+                mnw[r][1] = ((h.w >> 4) & 0x0f0f0f0fu) | (((h.z >> 6) & 0x03030303u) << 4);
+            } else {
+                dw[r] = dminw[r] = 0.0f;
+                scw[r][0] = scw[r][1] = mnw[r][0] = mnw[r][1] = 0;
+                qh[r][0] = qh[r][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        int S[RW][MC];
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int m = 0; m < MC; ++m) S[r][m] = 0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            uint4 alo[MC][2], ahi[MC][2];
+#pragma unroll
+            for (int m = 0; m < MC; ++m) {
+                const uint4 *q = reinterpret_cast<const uint4 *>(
+                    p.qs + ((size_t)(m0 + m) * (p.k >> 8) + b) * kQ8KUnitStride + g * 64);
+                alo[m][0] = q[0]; alo[m][1] = q[1];
+                ahi[m][0] = q[2]; ahi[m][1] = q[3];
+            }
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                if (!valid[r]) continue;
+                const uint4 *qp = reinterpret_cast<const uint4 *>(rowp[r] + (size_t)b * Q5K_BYTES + 48 + g * 32);
+                const uint4 q0 = qp[0], q1 = qp[1];
+                const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                const uint32_t hw[8] = {qh[r][0].x, qh[r][0].y, qh[r][0].z, qh[r][0].w,
+                                        qh[r][1].x, qh[r][1].y, qh[r][1].z, qh[r][1].w};
+                uint32_t lo[8], hi[8];
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    lo[w] = (qw[w] & 0x0f0f0f0fu) | (((hw[w] >> (2 * g)) & 0x01010101u) << 4);
+                    hi[w] = ((qw[w] >> 4) & 0x0f0f0f0fu) | (((hw[w] >> (2 * g + 1)) & 0x01010101u) << 4);
+                }
+                const uint4 l0 = make_uint4(lo[0], lo[1], lo[2], lo[3]), l1 = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                const uint4 h0 = make_uint4(hi[0], hi[1], hi[2], hi[3]), h1 = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                const int sc_lo = (scw[r][g >> 1] >> (16 * (g & 1))) & 0xff;
+                const int sc_hi = (scw[r][g >> 1] >> (16 * (g & 1) + 8)) & 0xff;
+#pragma unroll
+                for (int m = 0; m < MC; ++m) {
+                    const int pl = dot16(l1, alo[m][1], dot16(l0, alo[m][0], 0));
+                    const int ph = dot16(h1, ahi[m][1], dot16(h0, ahi[m][0], 0));
+                    S[r][m] += sc_lo * pl + sc_hi * ph;
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MC; ++m) {
+            const uint4 sp = *reinterpret_cast<const uint4 *>(p.sums + (size_t)(m0 + m) * (p.k >> 5) + b * 8);
+            const float da = p.d[(m0 + m) * (p.k >> 8) + b];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                int mv = __dp2a_lo((int)sp.x, (int)mnw[r][0], 0);
+                mv = __dp2a_hi((int)sp.y, (int)mnw[r][0], mv);
+                mv = __dp2a_lo((int)sp.z, (int)mnw[r][1], mv);
+                mv = __dp2a_hi((int)sp.w, (int)mnw[r][1], mv);
+                acc[r][m] = fmaf(__fmul_rn(da, dw[r]), (float)S[r][m], acc[r][m]);
+                acc[r][m] = fmaf(__fmul_rn(-da, dminw[r]), (float)mv, acc[r][m]);
+            }
+        }
+    }
+};
+
+// Q4_0 x Q8_0 (k_quants.rs:371-391, avx.rs:50-69) and Q5_0 x Q8_0 (k_quants.rs:500-534), per 32-element block:
+//   Q4_0: out += (d_w*d_a) * dot32(nibble - 8, q_a)            (the AVX2 arm's one product d = d_w*d_a, then fma)
+//   Q5_0: out += ((dot32(code5 - 16, q_a) * d_w) * d_a)        (the scalar arm, the only one this format has)
+// Low nibble j = element j, high nibble j = element j + 16; Q5_0's fifth bits: qh bit j / bit j + 16.
+// The offset comes out of the sum: dot(code - o, q_a) = dot(code, q_a) - o * sum(q_a), with the block sums of the
+// activations precomputed in the planes.  unit = two consecutive blocks (k must be a multiple of 64).
+template <bool FIVE_BIT>
+struct FmtQ4or5_0 {
+    static constexpr int kUnitElems = 64;
+    static constexpr int kBlockBytes = FIVE_BIT ? Q5_0_BYTES : Q4_0_BYTES;
+    template <int MC, int RW>
+    __device__ static __forceinline__ void unit(const ActPlanes &p, int m0, int u, const uint8_t *const (&rowp)[RW],
+                                                const bool (&valid)[RW], float (&acc)[RW][MC]) {
+        uint4 aq[MC][4];
+        float da[MC][2];
+        int asum[MC][2];
+        const int *sums32 = reinterpret_cast<const int *>(p.sums);
+#pragma unroll
+        for (int m = 0; m < MC; ++m) {
+            const uint4 *q = reinterpret_cast<const uint4 *>(
+                p.qs + ((size_t)(m0 + m) * (p.k >> 6) + u) * kQ8_0UnitStride);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) aq[m][i] = q[i];
+            const float2 dd = *reinterpret_cast<const float2 *>(p.d + (size_t)(m0 + m) * (p.k >> 5) + u * 2);
+            da[m][0] = dd.x;
+            da[m][1] = dd.y;
+            const int2 ss = *reinterpret_cast<const int2 *>(sums32 + (size_t)(m0 + m) * (p.k >> 5) + u * 2);
+            asum[m][0] = ss.x;
+            asum[m][1] = ss.y;
+        }
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            if (!valid[r]) continue;
+            const uint8_t *blk = rowp[r] + (size_t)u * (2 * kBlockBytes);  // 2-byte aligned
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint8_t *bp = blk + half * kBlockBytes;
+                const float dw = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(bp));
+                uint32_t lo[4], hi[4];
+                if (FIVE_BIT) {
+                    uint32_t w[5];  // qh, then the 16 nibble bytes
+                    lds_words_unaligned<5>(bp + 2, w);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t hb_lo = (((w[0] >> (4 * i)) & 0xFu) * 0x00204081u) & 0x01010101u;
+                        const uint32_t hb_hi = (((w[0] >> (16 + 4 * i)) & 0xFu) * 0x00204081u) & 0x01010101u;
+                        lo[i] = (w[1 + i] & 0x0f0f0f0fu) | (hb_lo << 4);
+                        hi[i] = ((w[1 + i] >> 4) & 0x0f0f0f0fu) | (hb_hi << 4);
+                    }
+                } else {
+                    uint32_t w[4];
+                    lds_words_unaligned<4>(bp + 2, w);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        lo[i] = w[i] & 0x0f0f0f0fu;
+                        hi[i] = (w[i] >> 4) & 0x0f0f0f0fu;
+                    }
+                }
+                const uint4 l4 = make_uint4(lo[0], lo[1], lo[2], lo[3]), h4 = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+#pragma unroll
+                for (int m = 0; m < MC; ++m) {
+                    const int pi = dot16(h4, aq[m][2 * half + 1], dot16(l4, aq[m][2 * half], 0)) -
+                                   (FIVE_BIT ? 16 : 8) * asum[m][half];
+                    if (FIVE_BIT) acc[r][m] = __fadd_rn(acc[r][m], __fmul_rn(__fmul_rn((float)pi, dw), da[m][half]));
+                    else acc[r][m] = fmaf(__fmul_rn(dw, da[m][half]), (float)pi, acc[r][m]);
+                }
+            }
+        }
+    }
+};
+using FmtQ4_0 = FmtQ4or5_0<false>;
+using FmtQ5_0 = FmtQ4or5_0<true>;
+
 // The matrix (or row range of one) a CTA is working on: a launch has one, a grouped launch up to kMaxGroup.
 struct GemvSeg {
     const uint8_t *w;  // first block of the matrix
@@ -379,11 +541,26 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
     planes.d = dpl;
     planes.k = p.k;
     constexpr int kUnroll = 4;
-    if (p.w_dtype == LLOOM_Q8_0) {
+    if (act_is_q8_0(p.w_dtype)) {
         // 17 half-words per block: [0] = f16 d, [1..16] = 32 int8
         const unsigned short *src = reinterpret_cast<const unsigned short *>(p.act);
         unsigned short *q16 = reinterpret_cast<unsigned short *>(act_smem);
         const int total = p.m * (p.k / 32) * 17;
+        if (p.w_dtype != LLOOM_Q8_0) {
+            // Q4_0 / Q5_0 weights: the sum of each block's 32 codes (the code offset comes out of the dot product)
+            int *sums32 = reinterpret_cast<int *>(act_smem + qs_bytes + round16((int64_t)p.m * (p.k / 32) * 4));
+            for (int blk = tid; blk < p.m * (p.k / 32); blk += nthreads) {
+                int s = 0;
+                for (int i = 1; i <= 16; ++i) {
+                    const unsigned short v = __ldg(src + blk * 17 + i);
+                    s += (int)(int8_t)(v & 0xff) + (int)(int8_t)(v >> 8);
+                }
+                sums32[blk] = s;
+            }
+            planes.sums = reinterpret_cast<const short *>(sums32);
+        } else {
+            planes.sums = nullptr;
+        }
         for (int base = tid; base < total; base += nthreads * kUnroll) {
             unsigned short v[kUnroll];
 #pragma unroll
@@ -401,14 +578,13 @@ __device__ __forceinline__ void stage_acts(const GemvParams &p, uint8_t *act_sme
                 }
             }
         }
-        planes.sums = nullptr;
     } else {
         // 73 words per block: [0] = f32 d, [1..64] = 256 int8, [65..72] = 16 int16 bsums
         const int nb = p.k / 256;
         short *sums = reinterpret_cast<short *>(act_smem + qs_bytes + round16((int64_t)p.m * nb * 4));
         const uint32_t *src = reinterpret_cast<const uint32_t *>(p.act);
         uint32_t *q32 = reinterpret_cast<uint32_t *>(act_smem);
-        const bool pair = p.w_dtype == LLOOM_Q4_K;
+        const bool pair = p.w_dtype != LLOOM_Q6_K;  // Q4_K / Q5_K: one sum per 32-element sub-block
         const int total = p.m * nb * 73;
         for (int base = tid; base < total; base += nthreads * kUnroll) {
             uint32_t v[kUnroll];
@@ -446,8 +622,9 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
     planes.qs = reinterpret_cast<const int8_t *>(act_smem);
     planes.d = dpl;
     planes.k = p.k;
-    if (p.w_dtype == LLOOM_Q8_0) {
+    if (act_is_q8_0(p.w_dtype)) {
         const int total = p.m * (p.k / 32);
+        int *sums32 = reinterpret_cast<int *>(act_smem + qs_bytes + round16((int64_t)total * 4));
         for (int base = warp * 8; base < total; base += p.n_cwarps * 8) {
             const int blk = base + (lane >> 2), part = lane & 3;
             const bool live = blk < total;
@@ -466,8 +643,14 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
                 dst[1] = q_hi;
                 if (part == 0) dpl[blk] = __half2float(__ushort_as_half(d16));
             }
+            if (p.w_dtype != LLOOM_Q8_0) {  // block sums of the codes, for the formats with an offset code
+                int s = __dp4a((int)q_lo, 0x01010101, __dp4a((int)q_hi, 0x01010101, 0));
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if (live && part == 0) sums32[blk] = s;
+            }
         }
-        planes.sums = nullptr;
+        planes.sums = p.w_dtype != LLOOM_Q8_0 ? reinterpret_cast<const short *>(sums32) : nullptr;
     } else {
         const int nb = p.k / 256;
         short *sums = reinterpret_cast<short *>(act_smem + qs_bytes + round16((int64_t)p.m * nb * 4));
@@ -489,7 +672,7 @@ __device__ __forceinline__ void quantize_acts_to_planes(const GemvParams &p, uin
                 q32[blk * (kQ8KUnitStride / 4) + lane * 2] = q_lo;
                 q32[blk * (kQ8KUnitStride / 4) + lane * 2 + 1] = q_hi;
                 if (lane == 0) dpl[blk] = d;
-                if (p.w_dtype == LLOOM_Q4_K) {
+                if (p.w_dtype != LLOOM_Q6_K) {
                     const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
                     if ((lane & 3) == 0) sums[blk * 8 + (lane >> 2)] = (short)sum32;
                 } else if ((lane & 1) == 0) {

@@ -119,8 +119,8 @@ void quantize_q8_0(const float *x, uint8_t *out, int64_t k) {
 }
 
 // ---- Q4_K: k_quants.rs:1622-1680 + utils.rs:227-284 (make_qkx1_quants(15, 5, .)) ----
-void qkx1(const float *x, float &scale_out, float &min_out) {
-    constexpr int n = 32, nmax = 15, ntry = 5;
+void qkx1(const float *x, float &scale_out, float &min_out, int nmax = 15) {
+    constexpr int n = 32, ntry = 5;
     uint8_t L[n] = {0};
     float mn = x[0], mx = x[0];
     for (int i = 1; i < n; ++i) { mn = std::min(mn, x[i]); mx = std::max(mx, x[i]); }
@@ -188,6 +188,104 @@ void quantize_q4k(const float *x, uint8_t *out, int64_t k) {
         }
         for (int g = 0; g < 4; ++g)
             for (int t = 0; t < 32; ++t) qs[32 * g + t] = (uint8_t)(L[64 * g + t] | (L[64 * g + 32 + t] << 4));
+    }
+}
+
+// ---- Q5_K: k_quants.rs:1883-1968 (make_qkx1_quants(31, 5, .), the Q4_K scale scheme, a fifth bit in qh) ----
+void quantize_q5k(const float *x, uint8_t *out, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, x += 256, out += 176) {
+        std::memset(out, 0, 176);
+        uint8_t *scales = out + 4, *qh = out + 16, *qs = out + 48;
+        float mins[8], sc[8];
+        for (int j = 0; j < 8; ++j) qkx1(x + 32 * j, sc[j], mins[j], 31);
+        float max_scale = 0.0f, max_min = 0.0f;
+        for (int j = 0; j < 8; ++j) { max_scale = std::max(sc[j], max_scale); max_min = std::max(mins[j], max_min); }
+        const float inv_scale = max_scale > 0.0f ? 63.0f / max_scale : 0.0f;
+        const float inv_min = max_min > 0.0f ? 63.0f / max_min : 0.0f;
+        for (int j = 0; j < 8; ++j) {
+            const uint8_t ls = (uint8_t)std::min(nearest_int(inv_scale * sc[j]), 63);
+            const uint8_t lm = (uint8_t)std::min(nearest_int(inv_min * mins[j]), 63);
+            if (j < 4) { scales[j] = ls; scales[j + 4] = lm; }
+            else {
+                scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                scales[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        const uint16_t hd = f32_to_f16(max_scale / 63.0f), hm = f32_to_f16(max_min / 63.0f);
+        std::memcpy(out, &hd, 2);
+        std::memcpy(out + 2, &hm, 2);
+        const float d = f16_to_f32(hd), dmin = f16_to_f32(hm);
+        uint8_t L[256] = {0};
+        for (int j = 0; j < 8; ++j) {
+            uint8_t s, m;
+            scale_min_k4(j, scales, s, m);
+            const float dj = d * (float)s;
+            if (dj == 0.0f) continue;
+            const float dm = dmin * (float)m;
+            for (int t = 0; t < 32; ++t) L[32 * j + t] = (uint8_t)clampi(nearest_int((x[32 * j + t] + dm) / dj), 0, 31);
+        }
+        uint8_t m1 = 1, m2 = 2;
+        for (int g = 0; g < 4; ++g) {
+            for (int t = 0; t < 32; ++t) {
+                uint8_t l1 = L[64 * g + t], l2 = L[64 * g + 32 + t];
+                if (l1 > 15) { l1 -= 16; qh[t] |= m1; }
+                if (l2 > 15) { l2 -= 16; qh[t] |= m2; }
+                qs[32 * g + t] = (uint8_t)(l1 | (l2 << 4));
+            }
+            m1 <<= 2;
+            m2 <<= 2;
+        }
+    }
+}
+
+// Rust `f32 as u8` / `as i8`: truncation toward zero, saturating, NaN -> 0.
+uint8_t trunc_u8(float v) {
+    if (std::isnan(v) || v <= 0.0f) return 0;
+    return v >= 255.0f ? 255 : (uint8_t)v;
+}
+int8_t trunc_i8(float v) {
+    if (std::isnan(v)) return 0;
+    if (v <= -128.0f) return -128;
+    return v >= 127.0f ? 127 : (int8_t)v;
+}
+// The element of largest magnitude, first one on ties (`if amax < x.abs()`).
+float first_max_by_abs(const float *x, int n) {
+    float amax = 0.0f, mx = 0.0f;
+    for (int i = 0; i < n; ++i)
+        if (amax < std::fabs(x[i])) { amax = std::fabs(x[i]); mx = x[i]; }
+    return mx;
+}
+// ---- Q4_0: k_quants.rs:320-352 ----
+void quantize_q4_0(const float *x, uint8_t *out, int64_t k) {
+    for (int64_t b = 0; b < k / 32; ++b, x += 32, out += 18) {
+        const float d = first_max_by_abs(x, 32) / -8.0f;
+        const float id = d != 0.0f ? 1.0f / d : 0.0f;
+        const uint16_t hd = f32_to_f16(d);
+        std::memcpy(out, &hd, 2);
+        for (int j = 0; j < 16; ++j) {
+            const uint8_t xi0 = std::min<uint8_t>(15, trunc_u8(x[j] * id + 8.5f));
+            const uint8_t xi1 = std::min<uint8_t>(15, trunc_u8(x[16 + j] * id + 8.5f));
+            out[2 + j] = (uint8_t)(xi0 | (xi1 << 4));
+        }
+    }
+}
+// ---- Q5_0: k_quants.rs:536-575 ----
+void quantize_q5_0(const float *x, uint8_t *out, int64_t k) {
+    for (int64_t b = 0; b < k / 32; ++b, x += 32, out += 22) {
+        const float d = first_max_by_abs(x, 32) / -16.0f;
+        const float id = d != 0.0f ? 1.0f / d : 0.0f;
+        const uint16_t hd = f32_to_f16(d);
+        std::memcpy(out, &hd, 2);
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            const uint8_t xi0 = (uint8_t)std::min<int8_t>(trunc_i8(x[j] * id + 16.5f), 31);
+            const uint8_t xi1 = (uint8_t)std::min<int8_t>(trunc_i8(x[j + 16] * id + 16.5f), 31);
+            out[6 + j] = (uint8_t)((xi0 & 0x0F) | ((xi1 & 0x0F) << 4));
+            qh |= (((uint32_t)xi0 & 0x10u) >> 4) << j;
+            qh |= (((uint32_t)xi1 & 0x10u) >> 4) << (j + 16);
+        }
+        std::memcpy(out + 2, &qh, 4);  // little-endian host, as LittleEndian::write_u32
     }
 }
 
@@ -294,6 +392,9 @@ void quantize_row(GgmlDType t, const float *x, uint8_t *out, int64_t k) {
     case GgmlDType::Q8_0: quantize_q8_0(x, out, k); return;
     case GgmlDType::Q4K: quantize_q4k(x, out, k); return;
     case GgmlDType::Q6K: quantize_q6k(x, out, k); return;
+    case GgmlDType::Q5K: quantize_q5k(x, out, k); return;
+    case GgmlDType::Q4_0: quantize_q4_0(x, out, k); return;
+    case GgmlDType::Q5_0: quantize_q5_0(x, out, k); return;
     default: throw Error(LLOOM_ERR_DTYPE, "quantize: not a weight type of this backend");
     }
 }
@@ -304,7 +405,8 @@ int64_t block_size(GgmlDType t) { return lloom_b200_block_elems((int)t); }
 int64_t type_size(GgmlDType t) { return lloom_b200_block_bytes((int)t); }
 
 void quantize_rows(GgmlDType t, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads) {
-    if (t != GgmlDType::Q8_0 && t != GgmlDType::Q4K && t != GgmlDType::Q6K)
+    if (t != GgmlDType::Q8_0 && t != GgmlDType::Q4K && t != GgmlDType::Q6K && t != GgmlDType::Q5K &&
+        t != GgmlDType::Q4_0 && t != GgmlDType::Q5_0)
         throw Error(LLOOM_ERR_DTYPE, "quantize: not a weight type of this backend");
     if (k <= 0 || k % block_size(t) != 0) throw Error(LLOOM_ERR_SHAPE, "quantize: k is not a whole number of blocks");
     const int64_t row_bytes = k / block_size(t) * type_size(t);

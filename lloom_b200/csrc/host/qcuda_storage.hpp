@@ -14,7 +14,7 @@
 namespace lloom {
 namespace host {
 
-enum class GgmlDType : int { Q8_0 = 8, Q4K = 12, Q6K = 14, Q8K = 15 };
+enum class GgmlDType : int { Q4_0 = 2, Q5_0 = 6, Q8_0 = 8, Q4K = 12, Q5K = 13, Q6K = 14, Q8K = 15 };
 
 int64_t block_size(GgmlDType t);  // elements per block
 int64_t type_size(GgmlDType t);   // bytes per block

@@ -44,7 +44,12 @@ static int launch_status(cudaError_t e) {
     return LLOOM_ERR_LAUNCH;
 }
 
-static bool supported_weight(int dtype) { return dtype == LLOOM_Q8_0 || dtype == LLOOM_Q4_K || dtype == LLOOM_Q6_K; }
+static bool supported_weight(int dtype) {
+    switch (dtype) {
+    case LLOOM_Q8_0: case LLOOM_Q4_K: case LLOOM_Q6_K: case LLOOM_Q4_0: case LLOOM_Q5_0: case LLOOM_Q5_K: return true;
+    }
+    return false;
+}
 
 struct DeviceInfo {
     int sm_count = 0;
@@ -93,6 +98,9 @@ static cudaError_t launch_gemv_dp4a(const GemvParams &p, int grid, int smem, boo
     case LLOOM_Q8_0: return launch_gemv_dp4a_q8_0(p, grid, smem, overlap, rw, stream);
     case LLOOM_Q4_K: return launch_gemv_dp4a_q4k(p, grid, smem, overlap, rw, stream);
     case LLOOM_Q6_K: return launch_gemv_dp4a_q6k(p, grid, smem, overlap, rw, stream);
+    case LLOOM_Q5_K: return launch_gemv_dp4a_q5k(p, grid, smem, overlap, rw, stream);
+    case LLOOM_Q4_0: return launch_gemv_dp4a_q4_0(p, grid, smem, overlap, rw, stream);
+    case LLOOM_Q5_0: return launch_gemv_dp4a_q5_0(p, grid, smem, overlap, rw, stream);
     }
     return cudaErrorInvalidValue;
 }
@@ -444,7 +452,7 @@ int lloom_b200_version(void) { return LLOOM_B200_VERSION; }
 const char *lloom_b200_error_string(int status) {
     switch (status) {
     case LLOOM_OK: return "ok";
-    case LLOOM_ERR_DTYPE: return "unsupported GgmlDType (only Q8_0, Q4_K, Q6_K weights)";
+    case LLOOM_ERR_DTYPE: return "unsupported GgmlDType (weights: Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K)";
     case LLOOM_ERR_SHAPE: return "bad shape";
     case LLOOM_ERR_ALIGN: return "misaligned pointer";
     case LLOOM_ERR_NULL: return "null pointer";
@@ -491,8 +499,8 @@ int lloom_b200_set_wait_limit_ns(uint64_t ns) {
 
 int64_t lloom_b200_block_elems(int dtype) {
     switch (dtype) {
-    case LLOOM_Q8_0: return QK8_0;
-    case LLOOM_Q4_K: case LLOOM_Q6_K: case LLOOM_Q8_K: return QK_K;
+    case LLOOM_Q8_0: case LLOOM_Q4_0: case LLOOM_Q5_0: return QK8_0;
+    case LLOOM_Q4_K: case LLOOM_Q5_K: case LLOOM_Q6_K: case LLOOM_Q8_K: return QK_K;
     }
     return 0;
 }
@@ -503,14 +511,17 @@ int64_t lloom_b200_block_bytes(int dtype) {
     case LLOOM_Q4_K: return Q4K_BYTES;
     case LLOOM_Q6_K: return Q6K_BYTES;
     case LLOOM_Q8_K: return Q8K_BYTES;
+    case LLOOM_Q4_0: return Q4_0_BYTES;
+    case LLOOM_Q5_0: return Q5_0_BYTES;
+    case LLOOM_Q5_K: return Q5K_BYTES;
     }
     return 0;
 }
 
 int lloom_b200_act_dtype(int w_dtype) {
     switch (w_dtype) {
-    case LLOOM_Q8_0: return LLOOM_Q8_0;
-    case LLOOM_Q4_K: case LLOOM_Q6_K: return LLOOM_Q8_K;
+    case LLOOM_Q8_0: case LLOOM_Q4_0: case LLOOM_Q5_0: return LLOOM_Q8_0;
+    case LLOOM_Q4_K: case LLOOM_Q5_K: case LLOOM_Q6_K: return LLOOM_Q8_K;
     }
     return 0;
 }

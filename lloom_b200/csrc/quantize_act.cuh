@@ -148,7 +148,7 @@ static __global__ void __launch_bounds__(256) quantize_q8k_kernel(const float *_
 
 static inline cudaError_t launch_quantize_act(int w_dtype, const float *x, int64_t m, int64_t k, void *out,
                                        cudaStream_t stream) {
-    if (w_dtype == LLOOM_Q8_0) {
+    if (w_dtype == LLOOM_Q8_0 || w_dtype == LLOOM_Q4_0 || w_dtype == LLOOM_Q5_0) {  // VecDotType = BlockQ8_0
         int64_t blocks = m * (k / QK8_0);
         int64_t threads = blocks * 4;
         quantize_q8_0_kernel<<<(unsigned)ceil_div64(threads, 256), 256, 0, stream>>>(x, (uint8_t *)out, blocks);

@@ -20,8 +20,11 @@ from ._lib import LloomError, check
 class GgmlDType(enum.IntEnum):
     """GGUF type ids of the formats this backend implements (mod.rs:505-568)."""
 
+    Q4_0 = 2
+    Q5_0 = 6
     Q8_0 = 8
     Q4K = 12
+    Q5K = 13
     Q6K = 14
     Q8K = 15  # activation-only (mod.rs:448-451)
 
@@ -41,7 +44,7 @@ class GgmlDType(enum.IntEnum):
             raise LloomError(_lib.ERR_DTYPE, "GgmlDType.from_u32", f"unsupported dtype id {u}") from None
 
 
-_WEIGHT_TYPES = (GgmlDType.Q8_0, GgmlDType.Q4K, GgmlDType.Q6K)
+_WEIGHT_TYPES = (GgmlDType.Q4_0, GgmlDType.Q5_0, GgmlDType.Q8_0, GgmlDType.Q4K, GgmlDType.Q5K, GgmlDType.Q6K)
 # The reference pads device weight buffers by 512 elements' worth of blocks (cuda.rs MATRIX_ROW_PADDING).
 MATRIX_ROW_PADDING = 512
 

@@ -37,17 +37,24 @@ typedef struct { uint16_t d; int8_t qs[QK8_0]; } blk_q8_0;                      
 typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qs[QK_K / 2]; } blk_q4k; /* 144 B */
 typedef struct { uint8_t ql[QK_K / 2]; uint8_t qh[QK_K / 4]; int8_t scales[QK_K / 16]; uint16_t d; } blk_q6k; /* 210 B */
 typedef struct { float d; int8_t qs[QK_K]; int16_t bsums[QK_K / 16]; } blk_q8k;     /* 292 B */
+/* k_quants.rs:84-131 (Q4_0, Q5_0), 184-192 (Q5K) */
+typedef struct { uint16_t d; uint8_t qs[16]; } blk_q4_0;                            /* 18 B  */
+typedef struct { uint16_t d; uint8_t qh[4]; uint8_t qs[16]; } blk_q5_0;             /* 22 B  */
+typedef struct { uint16_t d, dmin; uint8_t scales[12]; uint8_t qh[QK_K / 8]; uint8_t qs[QK_K / 2]; } blk_q5k; /* 176 B */
 #pragma pack(pop)
 
 _Static_assert(sizeof(blk_q8_0) == 34, "Q8_0 block");
 _Static_assert(sizeof(blk_q4k) == 144, "Q4_K block");
 _Static_assert(sizeof(blk_q6k) == 210, "Q6_K block");
 _Static_assert(sizeof(blk_q8k) == 292, "Q8_K block");
+_Static_assert(sizeof(blk_q4_0) == 18, "Q4_0 block");
+_Static_assert(sizeof(blk_q5_0) == 22, "Q5_0 block");
+_Static_assert(sizeof(blk_q5k) == 176, "Q5_K block");
 
 int64_t lo_block_elems(int dtype) {
     switch (dtype) {
-    case LO_Q8_0: return QK8_0;
-    case LO_Q4_K: case LO_Q6_K: case LO_Q8_K: return QK_K;
+    case LO_Q8_0: case LO_Q4_0: case LO_Q5_0: return QK8_0;
+    case LO_Q4_K: case LO_Q5_K: case LO_Q6_K: case LO_Q8_K: return QK_K;
     default: return 0;
     }
 }
@@ -57,6 +64,9 @@ int64_t lo_block_bytes(int dtype) {
     case LO_Q4_K: return sizeof(blk_q4k);
     case LO_Q6_K: return sizeof(blk_q6k);
     case LO_Q8_K: return sizeof(blk_q8k);
+    case LO_Q4_0: return sizeof(blk_q4_0);
+    case LO_Q5_0: return sizeof(blk_q5_0);
+    case LO_Q5_K: return sizeof(blk_q5k);
     default: return 0;
     }
 }
@@ -458,6 +468,199 @@ static void dequantize_row_q6k(const blk_q6k *x, float *y, int64_t k) {
     }
 }
 
+/* ---- Q4_0 (k_quants.rs:293-392), Q5_0 (k_quants.rs:495-600), Q5_K (k_quants.rs:1778-2077) ---- */
+
+/* Rust `f32 as u8`: truncation toward zero, saturating, NaN -> 0 */
+static inline uint8_t sat_u8_trunc(float v) {
+    if (!(v == v)) return 0;
+    if (v <= 0.0f) return 0;
+    if (v >= 255.0f) return 255;
+    return (uint8_t)v;
+}
+/* Rust `f32 as i8`: truncation toward zero, saturating, NaN -> 0 */
+static inline int8_t sat_i8_trunc(float v) {
+    if (!(v == v)) return 0;
+    if (v <= -128.0f) return -128;
+    if (v >= 127.0f) return 127;
+    return (int8_t)v;
+}
+
+/* BlockQ4_0::from_float, k_quants.rs:320-352 */
+static void quantize_row_q4_0(const float *x, blk_q4_0 *y, int64_t k) {
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        const float *xb = x + i * QK8_0;
+        float amax = 0.0f, max = 0.0f;
+        for (int j = 0; j < QK8_0; ++j)
+            if (amax < fabsf(xb[j])) { amax = fabsf(xb[j]); max = xb[j]; }
+        float d = max / -8.0f;
+        float id = d != 0.0f ? 1.0f / d : 0.0f;
+        y[i].d = lo_f32_to_f16(d);
+        for (int j = 0; j < 16; ++j) {
+            float x0 = xb[j] * id, x1 = xb[16 + j] * id;
+            uint8_t xi0 = sat_u8_trunc(x0 + 8.5f), xi1 = sat_u8_trunc(x1 + 8.5f);
+            if (xi0 > 15) xi0 = 15;
+            if (xi1 > 15) xi1 = 15;
+            y[i].qs[j] = (uint8_t)(xi0 | (xi1 << 4));
+        }
+    }
+}
+
+/* BlockQ4_0::to_float, k_quants.rs:299-318 */
+static void dequantize_row_q4_0(const blk_q4_0 *x, float *y, int64_t k) {
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        float d = lo_f16_to_f32(x[i].d);
+        for (int j = 0; j < 16; ++j) {
+            int x0 = (x[i].qs[j] & 0x0F) - 8, x1 = (x[i].qs[j] >> 4) - 8;
+            y[i * QK8_0 + j] = (float)x0 * d;
+            y[i * QK8_0 + j + 16] = (float)x1 * d;
+        }
+    }
+}
+
+/* BlockQ5_0::from_float, k_quants.rs:536-575 */
+static void quantize_row_q5_0(const float *x, blk_q5_0 *y, int64_t k) {
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        const float *xb = x + i * QK8_0;
+        float amax = 0.0f, max = 0.0f;
+        for (int j = 0; j < QK8_0; ++j)
+            if (amax < fabsf(xb[j])) { amax = fabsf(xb[j]); max = xb[j]; }
+        float d = max / -16.0f;
+        float id = d != 0.0f ? 1.0f / d : 0.0f;
+        y[i].d = lo_f32_to_f16(d);
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            float x0 = xb[j] * id, x1 = xb[j + 16] * id;
+            int8_t s0 = sat_i8_trunc(x0 + 16.5f), s1 = sat_i8_trunc(x1 + 16.5f);
+            uint8_t xi0 = (uint8_t)(s0 < 31 ? s0 : 31), xi1 = (uint8_t)(s1 < 31 ? s1 : 31);
+            y[i].qs[j] = (uint8_t)((xi0 & 0x0F) | ((xi1 & 0x0F) << 4));
+            qh |= (((uint32_t)xi0 & 0x10u) >> 4) << j;
+            qh |= (((uint32_t)xi1 & 0x10u) >> 4) << (j + 16);
+        }
+        y[i].qh[0] = (uint8_t)qh; y[i].qh[1] = (uint8_t)(qh >> 8); y[i].qh[2] = (uint8_t)(qh >> 16); y[i].qh[3] = (uint8_t)(qh >> 24);
+    }
+}
+
+static inline uint32_t q5_0_qh(const blk_q5_0 *b) {
+    return (uint32_t)b->qh[0] | ((uint32_t)b->qh[1] << 8) | ((uint32_t)b->qh[2] << 16) | ((uint32_t)b->qh[3] << 24);
+}
+
+/* BlockQ5_0::to_float, k_quants.rs:578-600 */
+static void dequantize_row_q5_0(const blk_q5_0 *x, float *y, int64_t k) {
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        float d = lo_f16_to_f32(x[i].d);
+        uint32_t qh = q5_0_qh(&x[i]);
+        for (int j = 0; j < 16; ++j) {
+            uint8_t xh_0 = (uint8_t)(((qh >> j) << 4) & 0x10), xh_1 = (uint8_t)((qh >> (j + 12)) & 0x10);
+            int x0 = (int)((x[i].qs[j] & 0x0F) | xh_0) - 16, x1 = (int)((x[i].qs[j] >> 4) | xh_1) - 16;
+            y[i * QK8_0 + j] = (float)x0 * d;
+            y[i * QK8_0 + j + 16] = (float)x1 * d;
+        }
+    }
+}
+
+/* the 32 signed codes of a Q4_0 / Q5_0 block in element order */
+static inline void q4_0_codes(const blk_q4_0 *b, int8_t *c) {
+    for (int j = 0; j < 16; ++j) { c[j] = (int8_t)((b->qs[j] & 0x0F) - 8); c[j + 16] = (int8_t)((b->qs[j] >> 4) - 8); }
+}
+static inline void q5_0_codes(const blk_q5_0 *b, int8_t *c) {
+    uint32_t qh = q5_0_qh(b);
+    for (int j = 0; j < 16; ++j) {
+        uint8_t xh_0 = (uint8_t)(((qh & (1u << j)) >> j) << 4), xh_1 = (uint8_t)((qh & (1u << (j + 16))) >> (j + 12));
+        c[j] = (int8_t)((int)((b->qs[j] & 0x0F) | xh_0) - 16);
+        c[j + 16] = (int8_t)((int)((b->qs[j] >> 4) | xh_1) - 16);
+    }
+}
+
+/* BlockQ5K::from_float, k_quants.rs:1883-1968 */
+static void quantize_row_q5k(const float *x, blk_q5k *y, int64_t k) {
+    for (int64_t i = 0; i < k / QK_K; ++i) {
+        const float *xb = x + i * QK_K;
+        blk_q5k *b = &y[i];
+        memset(b, 0, sizeof(*b));
+        float mins[8], scales[8];
+        for (int j = 0; j < 8; ++j) make_qkx1_quants(31, 5, xb + 32 * j, 32, &scales[j], &mins[j]);
+        float max_scale = 0.0f, max_min = 0.0f;
+        for (int j = 0; j < 8; ++j) { max_scale = rmaxf(scales[j], max_scale); max_min = rmaxf(mins[j], max_min); }
+        float inv_scale = max_scale > 0.0f ? 63.0f / max_scale : 0.0f;
+        float inv_min = max_min > 0.0f ? 63.0f / max_min : 0.0f;
+        for (int j = 0; j < 8; ++j) {
+            int32_t lsi = nearest_int(inv_scale * scales[j]);
+            int32_t lmi = nearest_int(inv_min * mins[j]);
+            uint8_t ls = (uint8_t)(lsi < 63 ? lsi : 63);
+            uint8_t lm = (uint8_t)(lmi < 63 ? lmi : 63);
+            if (j < 4) {
+                b->scales[j] = ls;
+                b->scales[j + 4] = lm;
+            } else {
+                b->scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                b->scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                b->scales[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        b->d = lo_f32_to_f16(max_scale / 63.0f);
+        b->dmin = lo_f32_to_f16(max_min / 63.0f);
+        uint8_t L[QK_K];
+        memset(L, 0, sizeof(L));
+        float bd = lo_f16_to_f32(b->d), bdmin = lo_f16_to_f32(b->dmin);
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, m;
+            scale_min_k4(j, b->scales, &sc, &m);
+            float d = bd * (float)sc;
+            if (d == 0.0f) continue;
+            float dm = bdmin * (float)m;
+            for (int t = 0; t < 32; ++t) L[32 * j + t] = (uint8_t)clampi(nearest_int((xb[32 * j + t] + dm) / d), 0, 31);
+        }
+        uint8_t m1 = 1, m2 = 2;
+        for (int n = 0; n < QK_K; n += 64) {
+            int off = (n / 64) * 32;
+            for (int j = 0; j < 32; ++j) {
+                uint8_t l1 = L[n + j], l2 = L[n + j + 32];
+                if (l1 > 15) { l1 -= 16; b->qh[j] |= m1; }
+                if (l2 > 15) { l2 -= 16; b->qh[j] |= m2; }
+                b->qs[off + j] = (uint8_t)(l1 | (l2 << 4));
+            }
+            m1 <<= 2;
+            m2 <<= 2;
+        }
+    }
+}
+
+/* BlockQ5K::to_float, k_quants.rs:2043-2076 */
+static void dequantize_row_q5k(const blk_q5k *x, float *y, int64_t k) {
+    for (int64_t i = 0; i < k / QK_K; ++i) {
+        const blk_q5k *b = &x[i];
+        float d = lo_f16_to_f32(b->d), min = lo_f16_to_f32(b->dmin);
+        float *yb = y + i * QK_K;
+        uint8_t u1 = 1, u2 = 2;
+        for (int g = 0; g < 4; ++g) {
+            uint8_t sc, m;
+            scale_min_k4(2 * g, b->scales, &sc, &m);
+            float d1 = d * (float)sc, m1 = min * (float)m;
+            scale_min_k4(2 * g + 1, b->scales, &sc, &m);
+            float d2 = d * (float)sc, m2 = min * (float)m;
+            const uint8_t *q = b->qs + 32 * g;
+            for (int t = 0; t < 32; ++t) yb[64 * g + t] = d1 * ((float)(q[t] & 0xF) + ((b->qh[t] & u1) ? 16.0f : 0.0f)) - m1;
+            for (int t = 0; t < 32; ++t) yb[64 * g + 32 + t] = d2 * ((float)(q[t] >> 4) + ((b->qh[t] & u2) ? 16.0f : 0.0f)) - m2;
+            u1 <<= 2;
+            u2 <<= 2;
+        }
+    }
+}
+
+/* the 256 unsigned 5-bit codes of a Q5_K block in element order, and its (scale, min) pairs */
+static inline void q5k_codes(const blk_q5k *b, int8_t *a) {
+    uint8_t m = 1;
+    for (int g = 0; g < 4; ++g) {
+        for (int t = 0; t < 32; ++t) a[64 * g + t] = (int8_t)((b->qs[32 * g + t] & 0xF) + ((b->qh[t] & m) ? 16 : 0));
+        m <<= 1;
+        for (int t = 0; t < 32; ++t) a[64 * g + 32 + t] = (int8_t)((b->qs[32 * g + t] >> 4) + ((b->qh[t] & m) ? 16 : 0));
+        m <<= 1;
+    }
+}
+static inline void q5k_scales_mins(const blk_q5k *b, uint8_t *sc, uint8_t *mn) {
+    for (int j = 0; j < 8; ++j) scale_min_k4(j, b->scales, &sc[j], &mn[j]);
+}
+
 /* ---- vec_dot, scalar generic order (vec_dot_unopt) ---- */
 
 /* BlockQ8_0::vec_dot_unopt, k_quants.rs:800-818 */
@@ -490,6 +693,58 @@ static float vec_dot_q4k_unopt(int64_t k, const blk_q4k *x, const blk_q8k *y) {
             }
         uint8_t sc[8], mn[8];
         q4k_scales_mins(b, sc, mn);
+        int32_t sumi = 0;
+        for (int j = 0; j < 16; ++j) sumi += (int32_t)y[i].bsums[j] * (int32_t)mn[j / 2];
+        int32_t aux32[8] = {0};
+        for (int j = 0; j < 8; ++j)
+            for (int t = 0; t < 32; ++t)
+                aux32[t & 7] += (int32_t)sc[j] * (int32_t)(int16_t)((int16_t)y[i].qs[32 * j + t] * (int16_t)a[32 * j + t]);
+        float d = lo_f16_to_f32(b->d) * y[i].d;
+        for (int l = 0; l < 8; ++l) sums[l] += d * (float)aux32[l];
+        float dmin = lo_f16_to_f32(b->dmin) * y[i].d;
+        sumf -= dmin * (float)sumi;
+    }
+    float s = 0.0f;
+    for (int l = 0; l < 8; ++l) s += sums[l];
+    return sumf + s;
+}
+
+/* BlockQ4_0::vec_dot_unopt, k_quants.rs:371-391 */
+static float vec_dot_q4_0_unopt(int64_t k, const blk_q4_0 *x, const blk_q8_0 *y) {
+    float sumf = 0.0f;
+    int8_t c[32];
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        q4_0_codes(&x[i], c);
+        int32_t s = 0;
+        for (int j = 0; j < 16; ++j) s += (int32_t)c[j] * y[i].qs[j] + (int32_t)c[j + 16] * y[i].qs[j + 16];
+        sumf += (float)s * lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d);
+    }
+    return sumf;
+}
+
+/* BlockQ5_0::vec_dot == vec_dot_unopt on every target, k_quants.rs:500-534 */
+static float vec_dot_q5_0_unopt(int64_t k, const blk_q5_0 *x, const blk_q8_0 *y) {
+    float sumf = 0.0f;
+    int8_t c[32];
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        q5_0_codes(&x[i], c);
+        int32_t s = 0;
+        for (int j = 0; j < 16; ++j) s += (int32_t)c[j] * y[i].qs[j] + (int32_t)c[j + 16] * y[i].qs[j + 16];
+        sumf += (float)s * lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d);
+    }
+    return sumf;
+}
+
+/* BlockQ5K::vec_dot_unopt, k_quants.rs:1795-1880 */
+static float vec_dot_q5k_unopt(int64_t k, const blk_q5k *x, const blk_q8k *y) {
+    float sums[8] = {0};
+    float sumf = 0.0f;
+    int8_t a[QK_K];
+    for (int64_t i = 0; i < k / QK_K; ++i) {
+        const blk_q5k *b = &x[i];
+        q5k_codes(b, a);
+        uint8_t sc[8], mn[8];
+        q5k_scales_mins(b, sc, mn);
         int32_t sumi = 0;
         for (int j = 0; j < 16; ++j) sumi += (int32_t)y[i].bsums[j] * (int32_t)mn[j / 2];
         int32_t aux32[8] = {0};
@@ -583,6 +838,50 @@ static float vec_dot_q4k_avx2_emu(int64_t k, const blk_q4k *x, const blk_q8k *y)
     }
     float m0 = acc_m[0] + acc_m[2], m1 = acc_m[1] + acc_m[3];
     return hsum8_order(acc) + (m0 + m1);
+}
+
+/* avx.rs:50-69 vec_dot_q4_0_q8_0: lane i = bytes 4i..4i+3 of (nibble - 8) * q8; acc = fma(dx*dy, lane, acc) */
+static float vec_dot_q4_0_avx2_emu(int64_t k, const blk_q4_0 *x, const blk_q8_0 *y) {
+    float acc[8] = {0};
+    int8_t c[32];
+    for (int64_t i = 0; i < k / QK8_0; ++i) {
+        float d = lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d);
+        q4_0_codes(&x[i], c);
+        for (int l = 0; l < 8; ++l) {
+            int32_t s = 0;
+            for (int t = 0; t < 4; ++t) s += (int32_t)c[4 * l + t] * (int32_t)y[i].qs[4 * l + t];
+            acc[l] = fmaf(d, (float)s, acc[l]);
+        }
+    }
+    return hsum8_order(acc);
+}
+
+/* avx.rs:528-640 vec_dot_q5k_q8k: eight int32 lanes of scale-weighted products, one fma per superblock; the min
+ * term is one scalar product per superblock added to a scalar f32 */
+static float vec_dot_q5k_avx2_emu(int64_t k, const blk_q5k *x, const blk_q8k *y) {
+    float acc[8] = {0};
+    float summs = 0.0f;
+    int8_t a[QK_K];
+    for (int64_t i = 0; i < k / QK_K; ++i) {
+        const blk_q5k *b = &x[i];
+        float d = y[i].d * lo_f16_to_f32(b->d);
+        float dmin = -y[i].d * lo_f16_to_f32(b->dmin);
+        uint8_t sc[8], mn[8];
+        q5k_scales_mins(b, sc, mn);
+        int32_t msum = 0;
+        for (int j = 0; j < 8; ++j) msum += (int32_t)mn[j] * (int32_t)(int16_t)(y[i].bsums[2 * j] + y[i].bsums[2 * j + 1]);
+        summs += dmin * (float)msum;
+        q5k_codes(b, a);
+        int32_t sumi[8] = {0};
+        for (int j = 0; j < 8; ++j)
+            for (int l = 0; l < 8; ++l) {
+                int32_t p = 0;
+                for (int t = 0; t < 4; ++t) p += (int32_t)a[32 * j + 4 * l + t] * (int32_t)y[i].qs[32 * j + 4 * l + t];
+                sumi[l] += (int32_t)sc[j] * p;
+            }
+        for (int l = 0; l < 8; ++l) acc[l] = fmaf(d, (float)sumi[l], acc[l]);
+    }
+    return hsum8_order(acc) + summs;
 }
 
 /* avx.rs:131-216 vec_dot_q6k_q8k */
@@ -754,6 +1053,53 @@ static float vec_dot_absum(int w_dtype, int64_t k, const void *w, const void *ac
                 a += fabsf(d * (float)sumi);
             }
         }
+    } else if (w_dtype == LO_Q4_0) {
+        const blk_q4_0 *x = w;
+        const blk_q8_0 *y = act;
+        int8_t c[32];
+        for (int64_t i = 0; i < k / QK8_0; ++i) {
+            float d = lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d);
+            q4_0_codes(&x[i], c);
+            for (int l = 0; l < 8; ++l) {
+                int32_t s = 0;
+                for (int t = 0; t < 4; ++t) s += (int32_t)c[4 * l + t] * (int32_t)y[i].qs[4 * l + t];
+                a += fabsf(d * (float)s);
+            }
+        }
+    } else if (w_dtype == LO_Q5_0) { /* scalar arm: one f32 summand per block */
+        const blk_q5_0 *x = w;
+        const blk_q8_0 *y = act;
+        int8_t c[32];
+        for (int64_t i = 0; i < k / QK8_0; ++i) {
+            q5_0_codes(&x[i], c);
+            int32_t s = 0;
+            for (int j = 0; j < 32; ++j) s += (int32_t)c[j] * (int32_t)y[i].qs[j];
+            a += fabsf((float)s * lo_f16_to_f32(x[i].d) * lo_f16_to_f32(y[i].d));
+        }
+    } else if (w_dtype == LO_Q5_K) {
+        const blk_q5k *x = w;
+        const blk_q8k *y = act;
+        int8_t c5[QK_K];
+        for (int64_t i = 0; i < k / QK_K; ++i) {
+            const blk_q5k *b = &x[i];
+            float d = y[i].d * lo_f16_to_f32(b->d);
+            float dmin = y[i].d * lo_f16_to_f32(b->dmin);
+            uint8_t sc[8], mn[8];
+            q5k_scales_mins(b, sc, mn);
+            int32_t msum = 0;
+            for (int j = 0; j < 8; ++j) msum += (int32_t)mn[j] * ((int32_t)y[i].bsums[2 * j] + y[i].bsums[2 * j + 1]);
+            a += fabsf(dmin * (float)msum);
+            q5k_codes(b, c5);
+            for (int l = 0; l < 8; ++l) {
+                int32_t sumi = 0;
+                for (int j = 0; j < 8; ++j) {
+                    int32_t p = 0;
+                    for (int t = 0; t < 4; ++t) p += (int32_t)c5[32 * j + 4 * l + t] * (int32_t)y[i].qs[32 * j + 4 * l + t];
+                    sumi += (int32_t)sc[j] * p;
+                }
+                a += fabsf(d * (float)sumi);
+            }
+        }
     } else if (w_dtype == LO_Q6_K) {
         const blk_q6k *x = w;
         const blk_q8k *y = act;
@@ -866,6 +1212,9 @@ int lo_quantize_row(int dtype, const float *x, void *blocks, int64_t k) {
     case LO_Q4_K: quantize_row_q4k(x, blocks, k); return 0;
     case LO_Q6_K: quantize_row_q6k(x, blocks, k); return 0;
     case LO_Q8_K: quantize_row_q8k(x, blocks, k); return 0;
+    case LO_Q4_0: quantize_row_q4_0(x, blocks, k); return 0;
+    case LO_Q5_0: quantize_row_q5_0(x, blocks, k); return 0;
+    case LO_Q5_K: quantize_row_q5k(x, blocks, k); return 0;
     }
     return -2;
 }
@@ -896,6 +1245,9 @@ int lo_dequantize_row(int dtype, const void *blocks, float *y, int64_t k) {
     case LO_Q4_K: dequantize_row_q4k(blocks, y, k); return 0;
     case LO_Q6_K: dequantize_row_q6k(blocks, y, k); return 0;
     case LO_Q8_K: dequantize_row_q8k(blocks, y, k); return 0;
+    case LO_Q4_0: dequantize_row_q4_0(blocks, y, k); return 0;
+    case LO_Q5_0: dequantize_row_q5_0(blocks, y, k); return 0;
+    case LO_Q5_K: dequantize_row_q5k(blocks, y, k); return 0;
     }
     return -2;
 }
@@ -903,6 +1255,10 @@ int lo_dequantize_row(int dtype, const void *blocks, float *y, int64_t k) {
 typedef float (*dot_fn)(int64_t, const void *, const void *);
 
 static dot_fn pick_dot(int w_dtype, int order) {
+    /* Q5_0 has no vectorised arm: vec_dot is vec_dot_unopt on every target (k_quants.rs:500-513).  Q4_0 and Q5_K
+     * have AVX2 arms (avx.rs:50-69, 528-640); the oracle holds their lane order in portable C only. */
+    if (w_dtype == LO_Q5_0) return (dot_fn)vec_dot_q5_0_unopt;
+    if (order == LO_ORDER_AVX2 && (w_dtype == LO_Q4_0 || w_dtype == LO_Q5_K)) order = LO_ORDER_AVX2_EMU;
 #ifdef LO_X86
     if (order == LO_ORDER_AVX2) {
         if (!lo_has_avx2()) return 0;
@@ -919,11 +1275,15 @@ static dot_fn pick_dot(int w_dtype, int order) {
         case LO_Q8_0: return (dot_fn)vec_dot_q8_0_avx2_emu;
         case LO_Q4_K: return (dot_fn)vec_dot_q4k_avx2_emu;
         case LO_Q6_K: return (dot_fn)vec_dot_q6k_avx2_emu;
+        case LO_Q4_0: return (dot_fn)vec_dot_q4_0_avx2_emu;
+        case LO_Q5_K: return (dot_fn)vec_dot_q5k_avx2_emu;
         }
         return 0;
     }
     if (order == LO_ORDER_UNOPT) {
         switch (w_dtype) {
+        case LO_Q4_0: return (dot_fn)vec_dot_q4_0_unopt;
+        case LO_Q5_K: return (dot_fn)vec_dot_q5k_unopt;
         case LO_Q8_0: return (dot_fn)vec_dot_q8_0_unopt;
         case LO_Q4_K: return (dot_fn)vec_dot_q4k_unopt;
         case LO_Q6_K: return (dot_fn)vec_dot_q6k_unopt;
@@ -945,8 +1305,8 @@ float lo_vec_dot_absum(int w_dtype, int64_t k, const void *w, const void *act) {
 /* VecDotType of each weight type: k_quants.rs:717 (Q8_0 -> Q8_0), 1507 (Q4K -> Q8K), 2082 (Q6K -> Q8K) */
 static int act_dtype_of(int w_dtype) {
     switch (w_dtype) {
-    case LO_Q8_0: return LO_Q8_0;
-    case LO_Q4_K: case LO_Q6_K: return LO_Q8_K;
+    case LO_Q8_0: case LO_Q4_0: case LO_Q5_0: return LO_Q8_0;   /* k_quants.rs:296, 498 */
+    case LO_Q4_K: case LO_Q5_K: case LO_Q6_K: return LO_Q8_K;   /* k_quants.rs:1781 */
     }
     return 0;
 }

@@ -1,6 +1,6 @@
 /*
- * CPU oracle for lloom-tensor's quantized matmul (Q8_0, Q4_K, Q6_K weights;
- * Q8_0 / Q8_K activations).
+ * CPU oracle for lloom-tensor's quantized matmul (Q8_0, Q4_K, Q6_K weights, and the
+ * formats that ride the same two activation arms: Q4_0, Q5_0, Q5_K; Q8_0 / Q8_K activations).
  *
  * TEST INFRASTRUCTURE ONLY.  This library restates, in plain C, the reference's
  * CPU algorithm so that the CUDA kernels can be checked against it and so that
@@ -13,7 +13,7 @@
  * block sizes, the GEMM-equals-GEMV bit identity); see tests/test_oracle_golden.py.
  *
  * dtype codes are the GGUF type ids the reference uses
- * (lloom-tensor/src/quantized/mod.rs:505-568): Q8_0 = 8, Q4_K = 12, Q6_K = 14, Q8_K = 15.
+ * (lloom-tensor/src/quantized/mod.rs:505-568): Q4_0 = 2, Q5_0 = 6, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, Q8_K = 15.
  */
 #ifndef LLOOM_ORACLE_H
 #define LLOOM_ORACLE_H
@@ -24,8 +24,11 @@
 extern "C" {
 #endif
 
+#define LO_Q4_0 2
+#define LO_Q5_0 6
 #define LO_Q8_0 8
 #define LO_Q4_K 12
+#define LO_Q5_K 13
 #define LO_Q6_K 14
 #define LO_Q8_K 15
 

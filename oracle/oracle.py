@@ -17,6 +17,7 @@ import subprocess
 import numpy as np
 
 Q8_0, Q4_K, Q6_K, Q8_K = 8, 12, 14, 15
+Q4_0, Q5_0, Q5_K = 2, 6, 13
 ORDER_UNOPT, ORDER_AVX2_EMU, ORDER_AVX2 = 0, 1, 2
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -82,7 +83,7 @@ def row_bytes(dtype: int, k: int) -> int:
 
 def act_dtype(w_dtype: int) -> int:
     """VecDotType of a weight type (k_quants.rs:717, 1507, 2082)."""
-    return Q8_0 if w_dtype == Q8_0 else Q8_K
+    return Q8_0 if w_dtype in (Q8_0, Q4_0, Q5_0) else Q8_K
 
 
 def best_order() -> int:

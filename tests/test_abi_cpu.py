@@ -31,11 +31,12 @@ def test_header_and_binding_agree(cuda_lib):
 
 def test_version_and_format_tables(cuda_lib):
     assert cuda_lib.lloom_b200_version() == 100
-    sizes = {8: (32, 34), 12: (256, 144), 14: (256, 210), 15: (256, 292)}  # mod.rs:663-715
+    sizes = {8: (32, 34), 12: (256, 144), 14: (256, 210), 15: (256, 292), 2: (32, 18), 6: (32, 22), 13: (256, 176)}  # mod.rs:663-715
     for dt, (elems, nbytes) in sizes.items():
         assert cuda_lib.lloom_b200_block_elems(dt) == elems
         assert cuda_lib.lloom_b200_block_bytes(dt) == nbytes
-    assert cuda_lib.lloom_b200_block_elems(2) == 0  # Q4_0: not implemented, no fallback
+    assert cuda_lib.lloom_b200_block_elems(3) == 0  # Q4_1: not implemented, no fallback
+    assert cuda_lib.lloom_b200_act_dtype(2) == 8 and cuda_lib.lloom_b200_act_dtype(6) == 8 and cuda_lib.lloom_b200_act_dtype(13) == 15
     assert cuda_lib.lloom_b200_act_dtype(8) == 8 and cuda_lib.lloom_b200_act_dtype(12) == 15
     assert cuda_lib.lloom_b200_act_dtype(14) == 15 and cuda_lib.lloom_b200_act_dtype(0) == 0
     assert cuda_lib.lloom_b200_act_row_bytes(12, 4096) == 16 * 292
@@ -54,7 +55,7 @@ def test_argument_validation_happens_before_any_launch(cuda_lib):
     p = C.addressof(buf)
     p16 = (p + 15) & ~15
     # unsupported dtypes are refused by name, never routed elsewhere (mod.rs:206-221)
-    assert L.lloom_b200_gemv(2, p16, p16, p16, 1, 4, 256, 4, None) == _lib.ERR_DTYPE
+    assert L.lloom_b200_gemv(3, p16, p16, p16, 1, 4, 256, 4, None) == _lib.ERR_DTYPE
     assert L.lloom_b200_qmatmul_fwd(10, p16, p16, p16, 1, 4, 256, 4, p16, 4096, None) == _lib.ERR_DTYPE
     assert L.lloom_b200_dequantize(3, p16, 256, p16, 0, None) == _lib.ERR_DTYPE
     # shapes
@@ -88,10 +89,42 @@ def test_host_mirror_metadata(cuda_lib):
     assert GgmlDType.Q4K.block_size() == 256 and GgmlDType.Q4K.type_size() == 144
     assert GgmlDType.from_u32(14) is GgmlDType.Q6K
     with pytest.raises(LloomError):
-        GgmlDType.from_u32(2)
+        GgmlDType.from_u32(3)
 
 
-@pytest.mark.parametrize("dt", [8, 12, 14])
+def test_abi_is_reentrant_from_host_threads(cuda_lib):
+    """The entry points that need no device (tables, planning, argument checks) called from eight host threads at
+    once: same answers as single-threaded (QTensor is shared across threads in the reference, mod.rs:1700)."""
+    import threading
+
+    from lloom_b200 import _lib
+
+    L = cuda_lib
+    want = [(dt, m, int(L.lloom_b200_workspace_bytes(dt, m, 4096, 4096)), int(L.lloom_b200_weight_image_bytes(dt, 4096, 4096)))
+            for dt in (2, 6, 8, 12, 13, 14) for m in (1, 8, 64, 512)]
+    buf = (C.c_uint8 * 4096)()
+    p16 = (C.addressof(buf) + 15) & ~15
+    bad = []
+
+    def worker():
+        for _ in range(200):
+            for dt, m, ws, img in want:
+                if int(L.lloom_b200_workspace_bytes(dt, m, 4096, 4096)) != ws or int(L.lloom_b200_weight_image_bytes(dt, 4096, 4096)) != img:
+                    bad.append((dt, m))
+            if L.lloom_b200_gemv(3, p16, p16, p16, 1, 4, 256, 4, None) != _lib.ERR_DTYPE:
+                bad.append("dtype")
+            if L.lloom_b200_qmatmul_fwd(12, p16, p16, p16, 1, 4, 256, 4, None, 0, None) != _lib.ERR_WORKSPACE:
+                bad.append("workspace")
+
+    threads = [threading.Thread(target=worker) for _ in range(8)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not bad, bad[:5]
+
+
+@pytest.mark.parametrize("dt", [8, 12, 14, 2, 6, 13])
 def test_host_weight_quantizer_matches_oracle(cuda_lib, oracle, dt):
     """The host layer's CPU weight quantizer (what QCudaStorage::quantize runs before the upload) is
     byte-identical with the oracle's restatement of T::from_float, including all-zero blocks."""

@@ -25,7 +25,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 REL_TOL = 1e-5   # plain relative error, outputs that are not cancellations
 A_TOL = 1e-6     # |err| / A, every output
-DT_NAMES = {8: "Q8_0", 12: "Q4K", 14: "Q6K"}
+DT_NAMES = {8: "Q8_0", 12: "Q4K", 14: "Q6K", 2: "Q4_0", 6: "Q5_0", 13: "Q5K"}
+ALL_DT = [8, 12, 14, 2, 6, 13]
 
 
 @pytest.fixture(scope="module")
@@ -79,7 +80,7 @@ def test_golden_fixtures(dev):
     assert Q.device_status() == 0
 
 
-@pytest.mark.parametrize("dt", [8, 12, 14])
+@pytest.mark.parametrize("dt", ALL_DT)
 def test_activation_quantizer_bit_exact(dev, oracle, dt):
     """Seeded normals plus adversarial rows: ties, zeros, denormals, huge values, infinities, NaN."""
     import lloom_b200 as lb
@@ -109,7 +110,7 @@ def test_activation_quantizer_bit_exact(dev, oracle, dt):
     np.testing.assert_array_equal(got, ref)
 
 
-@pytest.mark.parametrize("dt", [8, 12, 14])
+@pytest.mark.parametrize("dt", ALL_DT)
 def test_gemv_exhaustive_small_shapes(dev, oracle, dt):
     """k in {256,512,768}, n in {1..9,65}, m in 1..8: ragged tiles, partial warps, unaligned rows."""
     for k in (256, 512, 768):
@@ -122,7 +123,9 @@ def test_gemv_exhaustive_small_shapes(dev, oracle, dt):
                 assert_matmul_close(got, ref, absum, f"{DT_NAMES[dt]} n={n} k={k} m={m}")
 
 
-@pytest.mark.parametrize("dt,n,k", [(8, 8192, 2048), (12, 1792, 4096), (14, 2004, 4096), (12, 512, 14336)])
+@pytest.mark.parametrize("dt,n,k", [(8, 8192, 2048), (12, 1792, 4096), (14, 2004, 4096), (12, 512, 14336),
+                                    (13, 1792, 4096), (2, 2048, 4096), (6, 2048, 4096), (13, 300, 14336), (2, 300, 14336),
+                                    (6, 257, 11008)])
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 def test_gemv_config_shapes(dev, oracle, dt, n, k, m):
     """Row counts and K of the decode configurations (full C1; one 8-GPU shard of C2/C3; the down projection)."""
@@ -136,7 +139,7 @@ def test_gemv_config_shapes(dev, oracle, dt, n, k, m):
 def test_reference_integer_pattern_inputs(dev, oracle):
     """Inputs of cpu_prompt_gemm_is_bit_identical_to_decode_rows (quantized_tests.rs:1816-1823): each row
     of a batch equals the same row run alone, bit for bit, and matches the oracle within tolerance."""
-    for dt in (8, 12, 14):
+    for dt in ALL_DT:
         for m in (2, 8, 17, 33):
             for n in (1, 3, 7, 65):
                 for k in (256, 768):
@@ -241,7 +244,7 @@ def test_gemm_q4k_prefill_config(dev, oracle):
     assert Q.device_status() == 0
 
 
-@pytest.mark.parametrize("dt", [8, 12, 14])
+@pytest.mark.parametrize("dt", ALL_DT)
 def test_dequantize_and_embedding_bit_exact(dev, oracle, dt):
     """T::to_float parity (f32 and f16) and the embedding gather (run_quantized_embedding, :304-315)."""
     import lloom_b200 as lb
@@ -294,7 +297,7 @@ def test_fwd_shape_rules_and_errors(dev, oracle):
     assert yh.cpu().numpy().tobytes() == ref.cpu().numpy().tobytes()
 
 
-@pytest.mark.parametrize("dt,n,k", [(12, 520, 1024), (14, 300, 512), (8, 257, 256)])
+@pytest.mark.parametrize("dt,n,k", [(12, 520, 1024), (14, 300, 512), (8, 257, 256), (13, 300, 512), (2, 257, 256), (6, 130, 512)])
 def test_store_blocks_silu_and_mul_into(dev, oracle, dt, n, k):
     """forward_silu / forward_mul_into (mod.rs:2105-2155): the product is the plain forward's, bit for bit; SiLU is
     v / (1 + exp(-v)) in f32 (exp within a few ulp of the host's); the multiply-into is one exact f32 product."""
@@ -440,7 +443,7 @@ def test_prefill_image_same_bits(dev, oracle, dt):
     assert torch.equal(mm.forward(xt), plain) and torch.equal(mm.forward(xt[:8]), plain8)
 
 
-@pytest.mark.parametrize("dt,k", [(12, 4096), (14, 1024), (8, 2048)])
+@pytest.mark.parametrize("dt,k", [(12, 4096), (14, 1024), (8, 2048), (13, 2048), (2, 1024), (6, 2048)])
 @pytest.mark.parametrize("m", [1, 2, 5, 8])
 def test_grouped_forward_same_bits(dev, oracle, dt, k, m):
     """lloom_b200_qmatmul_fwd_group (gate|up, q|k|v behind one activation read): each matrix's rows equal its own

@@ -40,7 +40,7 @@ def ggml_like(offset):
     return (np.float32(0.1) + np.float32(2.0) * np.cos(i + np.float32(offset))).astype(np.float32)
 
 
-DT = {"Q8_0": 8, "Q4K": 12, "Q6K": 14, "Q8K": 15}
+DT = {"Q8_0": 8, "Q4K": 12, "Q6K": 14, "Q8K": 15, "Q4_0": 2, "Q5_0": 6, "Q5K": 13}
 
 
 def test_block_sizes(oracle):
@@ -73,9 +73,20 @@ def test_literal_block_images(oracle):
     np.testing.assert_array_equal(got, exp)
 
 
-@pytest.mark.parametrize("name", ["Q4K", "Q6K", "Q8K"])
+def test_q4_0_q5_0_ramp_pins(oracle):
+    """quantize_q4_0 / quantize_q5_0 (quantized_tests.rs:361-393, 428-459): the ramp 0..127 through quantize and
+    dequantize, all 128 values (Q4_0 exactly, Q5_0 to three decimals as the reference rounds them)."""
+    src = np.arange(128, dtype=np.float32)
+    d4 = oracle.dequantize(2, oracle.quantize(2, src), 128)[0]
+    np.testing.assert_array_equal(d4, np.array(GOLD["ramp_0_127"]["Q4_0"], np.float32))
+    assert np.signbit(d4[0]) and np.signbit(d4[1])  # the reference's -0.0
+    d5 = oracle.dequantize(6, oracle.quantize(6, src), 128)[0]
+    np.testing.assert_array_equal(round3(d5), np.array(GOLD["ramp_0_127"]["Q5_0"], np.float32))
+
+
+@pytest.mark.parametrize("name", ["Q4K", "Q5K", "Q6K", "Q8K"])
 def test_quantize_ramp_pins(oracle, name):
-    """quantize_q4k / _q6k / _q8k (quantized_tests.rs:862-1048)."""
+    """quantize_q4k / _q5k / _q6k / _q8k (quantized_tests.rs:862-1048)."""
     g = GOLD["quantize_ramp"][name]
     dt = DT[name]
     src = test_vector2(0.5, 1024)
@@ -89,7 +100,7 @@ def test_quantize_ramp_pins(oracle, name):
     assert np.abs(dbig - big).max() < g["max_err_big"]
 
 
-@pytest.mark.parametrize("name", ["Q8_0", "Q4K", "Q6K", "Q8K"])
+@pytest.mark.parametrize("name", ["Q8_0", "Q4K", "Q6K", "Q8K", "Q4_0", "Q5_0", "Q5K"])
 def test_ggml_quantization_error(oracle, name):
     """ggml_quantization_error_test (:545-568): RMSE/len on 0.1 + 2cos(i) stays under 0.002."""
     src = ggml_like(0.0)
@@ -99,7 +110,7 @@ def test_ggml_quantization_error(oracle, name):
     assert rmse <= GOLD["max_quantization_total_error"]
 
 
-@pytest.mark.parametrize("name", ["Q8_0", "Q4K", "Q6K"])
+@pytest.mark.parametrize("name", ["Q8_0", "Q4K", "Q6K", "Q4_0", "Q5_0", "Q5K"])
 def test_ggml_matmul_error(oracle, name):
     """ggml_matmul_error_test (:1157-1222) on the cosine vectors and on the ramp."""
     dt = DT[name]
@@ -124,7 +135,7 @@ def test_ggml_matmul_error(oracle, name):
             assert oracle.vec_dot(dt, n, wq, aq, oracle.ORDER_AVX2) == opt
 
 
-@pytest.mark.parametrize("name", ["Q8_0", "Q4K", "Q6K"])
+@pytest.mark.parametrize("name", ["Q8_0", "Q4K", "Q6K", "Q4_0", "Q5_0", "Q5K"])
 def test_prompt_gemm_is_bit_identical_to_decode_rows(oracle, name):
     """cpu_prompt_gemm_is_bit_identical_to_decode_rows (:1769-1903): integer-pattern inputs."""
     dt = DT[name]
@@ -197,7 +208,7 @@ def test_avx2_arm_equals_lane_emulation(oracle):
 def test_special_blocks(oracle):
     """All-zero blocks and blocks with a tie for the largest magnitude (first occurrence wins)."""
     z = np.zeros(256, np.float32)
-    for dt in (8, 12, 14, 15):
+    for dt in (8, 12, 14, 15, 2, 6, 13):
         q = oracle.quantize(dt, z)
         np.testing.assert_array_equal(oracle.dequantize(dt, q, 256)[0], z)
     q6 = oracle.quantize(14, z)[0]
@@ -221,7 +232,8 @@ def test_gguf_package_layout_crosscheck(oracle):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((4, 512)).astype(np.float32)
     for dt, qt in ((8, gguf.GGMLQuantizationType.Q8_0), (12, gguf.GGMLQuantizationType.Q4_K),
-                   (14, gguf.GGMLQuantizationType.Q6_K)):
+                   (14, gguf.GGMLQuantizationType.Q6_K), (2, gguf.GGMLQuantizationType.Q4_0),
+                   (6, gguf.GGMLQuantizationType.Q5_0), (13, gguf.GGMLQuantizationType.Q5_K)):
         q = oracle.quantize(dt, x)
         theirs = quants.dequantize(q, qt).astype(np.float32)
         mine = oracle.dequantize(dt, q, 512)
