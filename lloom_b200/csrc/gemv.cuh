@@ -518,17 +518,21 @@ __device__ __forceinline__ bool wait_exchange(const GemvParams &p) {
 // system-scope release store.  A consumer that has seen the same count in all slots of its own flag array
 // (lloom_b200_peer_wait) may read the gathered rows.  Called by one thread per CTA after a CTA-wide barrier.
 __device__ __forceinline__ void publish_arrival(const GemvParams &p) {
-    __threadfence_system();
     // words of this GPU's flag array: [kMaxPeers] = its call counter, [kMaxPeers + 1] = CTAs arrived so far
     unsigned int *mine = p.peer_flags[p.peer_rank];
-    const unsigned int prev = atomicAdd(mine + kMaxPeers + 1, 1u);
+    // This CTA's peer stores (ordered before this thread by the CTA barrier) become visible device-wide, then the
+    // arrival is counted.  Only the CTA that arrives last pays for a system-scope fence: it has observed every other
+    // CTA's arrival (acquire on the counter), so its release at system scope covers their stores as well.
+    __threadfence();
+    unsigned int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prev) : "l"(mine + kMaxPeers + 1) : "memory");
     if (prev + 1 == gridDim.x) {
         mine[kMaxPeers + 1] = 0;  // ready for the next launch on this stream
         const unsigned int epoch = mine[kMaxPeers] + 1;
         mine[kMaxPeers] = epoch;
         __threadfence_system();
         for (int g = 0; g < p.n_peers; ++g)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(epoch) : "memory");
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[g] + p.peer_rank), "r"(epoch) : "memory");
     }
 }
 

@@ -757,6 +757,9 @@ int lloom_b200_qmatmul_fwd_after_gather(int w_dtype, const void *w_blocks, const
 // Waits (bounded) until every slot of this GPU's flag array has reached the GPU's own call counter: the gathered
 // rows of the last lloom_b200_qmatmul_fwd_gather_sync on this stream are complete.  One warp, lane g polls slot g.
 __global__ void peer_wait_kernel(int n_peers, const unsigned int *flags) {
+    // let the stream's next kernel become resident (a GEMV starts streaming its weights) while this one waits for
+    // the GEMV before it and then for the peers; that kernel's own griddepcontrol.wait holds it until this one is done
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int g = threadIdx.x;
     if (g >= n_peers) return;
@@ -784,7 +787,8 @@ __global__ void peer_wait_kernel(int n_peers, const unsigned int *flags) {
 __global__ void peer_barrier_kernel(int rank, int n_peers, PeerFlags flags) {
     __shared__ unsigned int s_epoch;
     // launched with programmatic serialization when launch overlap is on: resident early, it waits here for the
-    // GEMV before it (and that GEMV's peer stores) to finish
+    // GEMV before it (and that GEMV's peer stores) to finish; the kernel behind it may become resident meanwhile
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     unsigned int *mine = flags.f[rank];
     if (threadIdx.x == 0) {
