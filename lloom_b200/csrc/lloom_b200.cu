@@ -7,6 +7,7 @@
 #include "gemv_params.h"
 #include "quantize_act.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
