@@ -191,10 +191,24 @@ int lloom_b200_qmatmul_fwd_store(int w_dtype, const void *w_blocks, const float 
  * ys[g] f32 [m][ldys[g]], ns[g] rows of matrix g, stores[g] one of LLOOM_STORE_* (NULL = all plain; MUL_INTO reads
  * and writes ys[g]).  Each matrix's result is bit-identical to its own lloom_b200_qmatmul_fwd.  m <= 8.
  * workspace: lloom_b200_workspace_bytes(w_dtype, m, max ns, k). */
-#define LLOOM_B200_MAX_GROUP 4
+#define LLOOM_B200_MAX_GROUP 8
 int lloom_b200_qmatmul_fwd_group(int w_dtype, int n_mats, const void *const *w_blocks, const float *x, float *const *ys,
                                  const int64_t *ns, const int64_t *ldys, const int *stores, int64_t m, int64_t k,
                                  void *workspace, int64_t workspace_bytes, void *stream);
+
+/* ---- Routed mixture-of-experts forward: QCudaStorage::indexed_moe_forward (cuda.rs:505-622) ----
+ * w_experts: [n_experts][n][k / block] canonical blocks (one stacked tensor, 16-byte aligned); x f32 [batch][in_dim1][k] with in_dim1 == 1 or topk; ids u32 [batch][topk] ON THE DEVICE;
+ * out f32 [batch][topk][n]:  out[b][t] = W[ids[b][t]] . x[b][in_dim1 == 1 ? 0 : t].
+ * Each (token, expert) product is bit-identical to lloom_b200_qmatmul_fwd of that expert's matrix on that row (the
+ * activations are quantized to Q8_0 / Q8_K as on the dense path, where the reference's CUDA arm uses Q8_1).  One
+ * persistent launch per token walks that token's topk experts behind one activation read (in_dim1 == 1; topk <=
+ * LLOOM_B200_MAX_GROUP), else one launch per (token, expert); the expert ids are read on the device, after the
+ * kernel before this one in the stream has finished.  An id >= n_experts is clamped to the last expert and sets the
+ * device status word to LLOOM_ERR_SHAPE (lloom_b200_device_status).  Meant for decode-sized batches.
+ * workspace: lloom_b200_workspace_bytes(w_dtype, 1, n, k). */
+int lloom_b200_indexed_moe_forward(int w_dtype, const void *w_experts, int64_t n_experts, int64_t n, int64_t k,
+                                   const float *x, int64_t batch, int64_t in_dim1, const uint32_t *ids, int64_t topk,
+                                   float *out, void *workspace, int64_t workspace_bytes, void *stream);
 
 /* ---- Row-sharded forward with the all-gather fused into the GEMV (one node, up to 8 GPUs) ----
  *

@@ -24,6 +24,13 @@ const char *lloom_b200_host_last_error(void);
  * QCudaStorage::quantize runs before uploading (cuda.rs:720-741).  Host pointers. */
 int lloom_b200_host_quantize_rows(int dtype, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads);
 
+/* T::from_float_imatrix per row (k_quants.rs:1682-1745, 1959-2041, 2246-2325): importance-weighted quantization,
+ * `imatrix` holds k weights (one per column); Q4_K, Q5_K and Q6_K only, other types fail as in the reference. */
+int lloom_b200_host_quantize_rows_imatrix(int dtype, const float *x, const float *imatrix, void *blocks, int64_t rows,
+                                          int64_t k, int nthreads);
+/* QTensor::quantize_imatrix / quantize_imatrix_onto (mod.rs:940-1020, cuda.rs:743-790). */
+int lloom_b200_host_qtensor_quantize_imatrix(int device, void *stream, const float *src, const float *imatrix, int64_t n,
+                                             int64_t k, int dtype, int nthreads, void **out);
 /* QTensor::quantize (mod.rs:919-938): host f32 [n,k] -> packed blocks on `device`. */
 int lloom_b200_host_qtensor_quantize(int device, void *stream, const float *src, int64_t n, int64_t k, int dtype,
                                      int nthreads, void **out);

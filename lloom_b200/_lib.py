@@ -28,6 +28,7 @@ SYMBOLS = [
     ("lloom_b200_qmatmul_fwd_image", _int, [_int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd_group", _int, [_int, _int, C.POINTER(_vp), _vp, C.POINTER(_vp), C.POINTER(_i64),
                                             C.POINTER(_i64), C.POINTER(_int), _i64, _i64, _vp, _i64, _vp]),
+    ("lloom_b200_indexed_moe_forward", _int, [_int, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd_gather_sync", _int, [_int, _vp, _vp, _i64, _i64, _i64, _i64, _i64, C.POINTER(_vp), _int, _int,
                                                   C.POINTER(_vp), _vp, _vp, _i64, _vp]),
     ("lloom_b200_qmatmul_fwd_after_gather", _int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _vp, _i64, _vp]),
@@ -55,6 +56,8 @@ SYMBOLS = [
     # include/lloom_b200_host.h: C view of the C++ host layer
     ("lloom_b200_host_last_error", C.c_char_p, []),
     ("lloom_b200_host_quantize_rows", _int, [_int, _vp, _vp, _i64, _i64, _int]),
+    ("lloom_b200_host_quantize_rows_imatrix", _int, [_int, _vp, _vp, _vp, _i64, _i64, _int]),
+    ("lloom_b200_host_qtensor_quantize_imatrix", _int, [_int, _vp, _vp, _vp, _i64, _i64, _int, _int, C.POINTER(_vp)]),
     ("lloom_b200_host_qtensor_quantize", _int, [_int, _vp, _vp, _i64, _i64, _int, _int, C.POINTER(_vp)]),
     ("lloom_b200_host_qtensor_from_data", _int, [_int, _vp, _vp, _i64, _int, _i64, _i64, C.POINTER(_vp)]),
     ("lloom_b200_host_qtensor_free", None, [_vp]),

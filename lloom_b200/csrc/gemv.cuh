@@ -444,6 +444,8 @@ struct GemvSeg {
     int64_t ldy;
     int store;         // block on the store
     int r_begin, r_end;  // rows of this matrix the CTA owns
+    int64_t row_base;  // rows between `w` and the matrix's first row (routed experts: `w` is the whole stack, so that
+                       // an expert whose byte offset is not a multiple of 16 still streams from an aligned base)
 };
 
 // One output value to its destination(s).  SiLU in the reference's f32 form v / (1 + exp(-v)) (op.rs:755-757,
@@ -699,7 +701,7 @@ __device__ __forceinline__ bool gemv_producer(const GemvParams &p, const GemvSeg
             if (!mbar_wait(&empty[s], ((it / p.stages) - 1) & 1)) return false;
         }
         const int rows = min(tile_rows, sg.r_end - row0);
-        const int64_t start = (int64_t)row0 * p.row_bytes;
+        const int64_t start = (sg.row_base + row0) * p.row_bytes;
         const int64_t end = start + (int64_t)rows * p.row_bytes;
         const int64_t a_start = start & ~(int64_t)15;
         int64_t a_end = (end + 15) & ~(int64_t)15;
@@ -745,8 +747,8 @@ __device__ __forceinline__ bool gemv_producer_pieces(const GemvParams &p, const 
             if (lane == 0) mbar_arrive_expect_tx(&full[s], (uint32_t)rows * bytes);
             __syncwarp();
             for (int r = lane; r < rows; r += 32)
-                bulk_g2s(dst + (size_t)r * pitch, sg.w + (int64_t)(row0 + r) * p.row_bytes + (int64_t)u0 * p.unit_bytes, bytes,
-                         &full[s]);
+                bulk_g2s(dst + (size_t)r * pitch, sg.w + (sg.row_base + row0 + r) * p.row_bytes + (int64_t)u0 * p.unit_bytes,
+                         bytes, &full[s]);
         }
     }
     return true;
@@ -760,6 +762,17 @@ __device__ __forceinline__ GemvSeg gemv_segment(const GemvParams &p, int g, int 
         const int off = p.goff[g], rows = p.goff[g + 1] - off;
         sg.w = p.gw[g];
         sg.w_bytes = (int64_t)rows * p.row_bytes;
+        sg.row_base = 0;
+        if (p.moe_ids) {
+            uint32_t e = __ldg(p.moe_ids + g);
+            if (e >= (uint32_t)p.moe_experts) {  // reported through the status word; the last expert stands in
+                e = (uint32_t)p.moe_experts - 1;
+                atomicExch(&g_device_status, LLOOM_ERR_SHAPE);
+            }
+            sg.w = p.w;
+            sg.row_base = (int64_t)e * rows;
+            sg.w_bytes = (int64_t)p.moe_experts * rows * p.row_bytes;
+        }
         sg.y = p.gy[g];
         sg.ldy = p.gldy[g];
         sg.store = p.gstore[g];
@@ -773,6 +786,7 @@ __device__ __forceinline__ GemvSeg gemv_segment(const GemvParams &p, int g, int 
         sg.store = p.store_mode;
         sg.r_begin = r_begin;
         sg.r_end = r_end;
+        sg.row_base = 0;
     }
     return sg;
 }
@@ -820,6 +834,8 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
 
     if (warp == p.n_cwarps) {
         // ---------------- producer warp ----------------
+        // routed experts: which matrices to stream is device data that the stream predecessor may have written
+        if (GROUP && p.moe_ids) asm volatile("griddepcontrol.wait;" ::: "memory");
         int it = 0;
         for (int g = 0; g < nseg; ++g) {
             const GemvSeg sg = gemv_segment<GROUP>(p, g, r_begin, r_end);
@@ -882,7 +898,7 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
                     for (int r = 0; r < RW; ++r)
                         rowp[r] = tile_base + (size_t)(local0 + r) * piece_pitch - (size_t)u0 * p.unit_bytes;
                 } else {
-                    const int64_t start = (int64_t)trow * p.row_bytes;
+                    const int64_t start = (sg.row_base + trow) * p.row_bytes;
                     const uint8_t *tile_base = stage0 + (size_t)s * p.stage_bytes + (start & 15);
 #pragma unroll
                     for (int r = 0; r < RW; ++r) rowp[r] = tile_base + (size_t)(local0 + r) * p.row_bytes;
@@ -1017,8 +1033,12 @@ static cudaError_t launch_gemv_inst(const GemvParams &p, int grid, int smem, boo
 
 template <class Fmt, int RW>
 static cudaError_t launch_gemv_m(const GemvParams &p, int grid, int smem, bool overlap, cudaStream_t stream) {
-    if (p.n_group > 1) {  // grouped launch: whole rows, eight consumer warps, one row per lane, m <= 2
-        if (RW != 1 || p.nchunks > 1 || p.n_cwarps > 8) return cudaErrorInvalidValue;
+    if (p.n_group >= 1) {  // grouped launch: eight consumer warps, one row per lane, m <= 2 (rows in pieces: m == 1)
+        if (RW != 1 || p.n_cwarps > 8) return cudaErrorInvalidValue;
+        if (p.nchunks > 1) {
+            if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 8, true, true>(p, grid, smem, overlap, stream);
+            return cudaErrorInvalidValue;
+        }
         if (p.m == 1) return launch_gemv_inst<Fmt, 1, 1, 8, false, true>(p, grid, smem, overlap, stream);
         if (p.m == 2) return launch_gemv_inst<Fmt, 2, 1, 8, false, true>(p, grid, smem, overlap, stream);
         return cudaErrorInvalidValue;

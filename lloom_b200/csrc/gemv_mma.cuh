@@ -83,11 +83,9 @@ __device__ __forceinline__ void stage_acts_mma(const GemvParams &p, uint8_t *act
 
 // One warp quantizes 256-element block (t, b) of the f32 activations into the three planes at `out` (global
 // or shared memory).  Block arithmetic: q8k_quantize_warp, shared with the canonical quantizer.
-__device__ __forceinline__ void q8k_block_to_planes(const float *__restrict__ x, uint8_t *out, int t, int b, int m, int nb,
-                                                    int act_pitch, int lane) {
+__device__ __forceinline__ void q8k_values_to_planes(const float (&v)[8], uint8_t *out, int t, int b, int m, int nb,
+                                                     int act_pitch, int lane) {
     const int blk = t * nb + b;
-    float v[8];
-    load8(x + (int64_t)blk * QK_K + lane * 8, v);
     uint32_t q_lo, q_hi;
     float d;
     int sum16;
@@ -101,6 +99,12 @@ __device__ __forceinline__ void q8k_block_to_planes(const float *__restrict__ x,
         lh[8 + (lane >> 2)] = (uint8_t)((sum32 >> 6) & 0xff);
     }
     if (lane == 0) reinterpret_cast<float *>(out + (size_t)m * act_pitch + (size_t)m * nb * 16)[blk] = d;
+}
+__device__ __forceinline__ void q8k_block_to_planes(const float *__restrict__ x, uint8_t *out, int t, int b, int m, int nb,
+                                                    int act_pitch, int lane) {
+    float v[8];
+    load8(x + (int64_t)(t * nb + b) * QK_K + lane * 8, v);
+    q8k_values_to_planes(v, out, t, b, m, nb, act_pitch, lane);
 }
 
 // f32 activations -> the plane image in global memory (the same bytes stage_acts_mma leaves in shared
@@ -185,9 +189,21 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (EPI != 0 && p.wait_flags) alive = wait_exchange(p);  // x came out of a fused gather: all peers' rows are in
     if (p.x) {  // quantizer as prologue: this CTA quantizes the activation rows into its own planes
+        // a warp's blocks are loaded four at a time before any is quantized: one L2 round trip per batch
         const int nbq = p.k >> 8, nblk = p.m * nbq;
-        for (int blk = warp; blk < nblk; blk += kMmaWarps)
-            q8k_block_to_planes(p.x, act_smem, blk / nbq, blk % nbq, p.m, nbq, p.act_pitch, lane);
+        for (int base = warp; base < nblk; base += 4 * kMmaWarps) {
+            float v[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int blk = base + j * kMmaWarps;
+                if (blk < nblk) load8(p.x + (int64_t)blk * QK_K + lane * 8, v[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int blk = base + j * kMmaWarps;
+                if (blk < nblk) q8k_values_to_planes(v[j], act_smem, blk / nbq, blk % nbq, p.m, nbq, p.act_pitch, lane);
+            }
+        }
         asm volatile("bar.sync 9, %0;" ::"r"(nthreads) : "memory");
     } else if (p.act_planes) {
         if (threadIdx.x == 0) {

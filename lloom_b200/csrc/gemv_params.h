@@ -86,13 +86,15 @@ struct GemvParams {
     int64_t gldy[kMaxGroup];
     int goff[kMaxGroup + 1];
     int gstore[kMaxGroup];
+    // Routed experts (moe_ids != nullptr, grouped launches only): matrix g is expert moe_ids[g] of the stacked
+    // tensor at `w` (every expert has as many rows as the group's matrices); the ids are device data, read after the
+    // stream predecessor is done.
+    const uint32_t *moe_ids;
+    int moe_experts;
 };
 
 // ---- tensor-core GEMV (gemv_mma.cuh) ----
 constexpr int kMmaTileRows = 16;
-// Up to this many rows the quantizer runs as the kernel's prologue (measured per forward: 10.0 us against 11.5 us
-// with the separate quantizer at M = 2; 11.6 against 11.4 at M = 4).
-constexpr int kMmaFusedMaxM = 2;
 constexpr int kMmaWarps = 16;  // consumer warps; SPLIT of them share a tile, warp j of a team takes superblocks j, j+SPLIT, ...
 constexpr int kMmaRedBytes = 2 * kMmaWarps * 32 * 16;  // double-buffered partial sums, one float4 per lane
 constexpr int kMmaBarBytes = 128;      // empty[8], one barrier for the activation image

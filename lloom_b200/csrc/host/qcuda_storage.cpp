@@ -290,7 +290,7 @@ void quantize_q5_0(const float *x, uint8_t *out, int64_t k) {
 }
 
 // ---- Q6_K: k_quants.rs:2174-2244 + utils.rs:62-224 (make_qx_quants(16, 32, ., ., 1, null)) ----
-float qx_w2(const float *x, int8_t *ls) {
+float qx_w2(const float *x, int8_t *ls, const float *qw = nullptr) {
     constexpr int n = 16, nmax = 32;
     float mx = 0.0f, amax = 0.0f;
     for (int i = 0; i < n; ++i) {
@@ -303,7 +303,7 @@ float qx_w2(const float *x, int8_t *ls) {
     for (int i = 0; i < n; ++i) {
         const int32_t l = clampi(nearest_int(iscale0 * x[i]), -nmax, nmax - 1);
         ls[i] = (int8_t)(l + nmax);
-        const float w = x[i] * x[i], lf = (float)l;
+        const float w = qw ? qw[i] : x[i] * x[i], lf = (float)l;
         sumlx += w * x[i] * lf;
         suml2 += w * lf * lf;
     }
@@ -316,7 +316,7 @@ float qx_w2(const float *x, int8_t *ls) {
         for (int i = 0; i < n; ++i) {
             const int32_t l = clampi(nearest_int(is * x[i]), -nmax, nmax - 1);
             if (l + nmax != (int32_t)ls[i]) changed = true;
-            const float w = x[i] * x[i], lf = (float)l;
+            const float w = qw ? qw[i] : x[i] * x[i], lf = (float)l;
             slx += w * x[i] * lf;
             sl2 += w * lf * lf;
         }
@@ -330,7 +330,7 @@ float qx_w2(const float *x, int8_t *ls) {
     for (int itry = 0; itry < 5; ++itry) {
         int n_changed = 0;
         for (int i = 0; i < n; ++i) {
-            const float w = x[i] * x[i];
+            const float w = qw ? qw[i] : x[i] * x[i];
             const int32_t l = (int32_t)ls[i] - nmax;
             float slx = sumlx - w * x[i] * (float)l;
             if (slx > 0.0f) {
@@ -353,7 +353,8 @@ float qx_w2(const float *x, int8_t *ls) {
     }
     return scale;
 }
-void quantize_q6k(const float *x, uint8_t *out, int64_t k) {
+// imatrix == nullptr: from_float; else from_float_imatrix (k_quants.rs:2246-2325), one importance weight per column
+void quantize_q6k(const float *x, uint8_t *out, int64_t k, const float *imatrix = nullptr) {
     int8_t L[256] = {0};
     float scales[16];
     for (int64_t b = 0; b < k / 256; ++b, x += 256, out += 210) {
@@ -361,7 +362,7 @@ void quantize_q6k(const float *x, uint8_t *out, int64_t k) {
         int8_t *sc = reinterpret_cast<int8_t *>(out + 192);
         float max_scale = 0.0f, max_abs = 0.0f;
         for (int ib = 0; ib < 16; ++ib) {
-            const float s = qx_w2(x + 16 * ib, L + 16 * ib);
+            const float s = qx_w2(x + 16 * ib, L + 16 * ib, imatrix ? imatrix + 256 * b + 16 * ib : nullptr);
             scales[ib] = s;
             if (std::fabs(s) > max_abs) { max_abs = std::fabs(s); max_scale = s; }
         }
@@ -387,6 +388,209 @@ void quantize_q6k(const float *x, uint8_t *out, int64_t k) {
     }
 }
 
+// ---- importance-matrix quantizers of the k-quants with 6-bit (scale, min) pairs: from_float_imatrix of Q4K
+// (k_quants.rs:1682-1745) and Q5K (:1959-2041); make_qkx3_quants utils.rs:372-466, make_qp_quants utils.rs:469-560 ----
+void qkx3(int nmax, const float *x, const float *weights, float &scale_out, float &min_out) {
+    constexpr int n = 32, nstep = 36;
+    constexpr float rmin = -0.9f, rdelta = 0.05f;
+    uint8_t L[n] = {0}, Laux[n];
+    float min_val = x[0], max_val = x[0];
+    float sum_w = weights[0];
+    float sum_x = sum_w * x[0];
+    for (int i = 1; i < n; ++i) {
+        if (x[i] < min_val) min_val = x[i];
+        if (x[i] > max_val) max_val = x[i];
+        sum_w += weights[i];
+        sum_x += weights[i] * x[i];
+    }
+    if (min_val > 0.0f) min_val = 0.0f;
+    if (max_val <= min_val) { scale_out = 0.0f; min_out = -min_val; return; }
+    float iscale = (float)nmax / (max_val - min_val);
+    float scale = 1.0f / iscale;
+    float best_mad = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        const uint8_t l = (uint8_t)clampi(nearest_int(iscale * (x[i] - min_val)), 0, nmax);
+        L[i] = l;
+        const float diff = scale * (float)l + min_val - x[i];
+        best_mad += weights[i] * (diff * diff);
+    }
+    for (int is = 0; is <= nstep; ++is) {
+        iscale = (rmin + rdelta * (float)is + (float)nmax) / (max_val - min_val);
+        float sum_l = 0.0f, sum_l2 = 0.0f, sum_xl = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            const uint8_t l = (uint8_t)clampi(nearest_int(iscale * (x[i] - min_val)), 0, nmax);
+            Laux[i] = l;
+            const float w = weights[i], lf = (float)l;
+            sum_l += w * lf;
+            sum_l2 += w * (lf * lf);
+            sum_xl += w * lf * x[i];
+        }
+        const float d = sum_w * sum_l2 - sum_l * sum_l;
+        if (d > 0.0f) {
+            float this_scale = (sum_w * sum_xl - sum_x * sum_l) / d;
+            float this_min = (sum_l2 * sum_x - sum_l * sum_xl) / d;
+            if (this_min > 0.0f) { this_min = 0.0f; this_scale = sum_xl / sum_l2; }
+            float mad = 0.0f;
+            for (int i = 0; i < n; ++i) {
+                const float diff = this_scale * (float)Laux[i] + this_min - x[i];
+                mad += weights[i] * (diff * diff);
+            }
+            if (mad < best_mad) {
+                std::memcpy(L, Laux, n);
+                best_mad = mad;
+                scale = this_scale;
+                min_val = this_min;
+            }
+        }
+    }
+    scale_out = scale;
+    min_out = -min_val;
+}
+float qp_quants(const float *x, uint8_t *L, const float *qw) {
+    constexpr int n = 8;
+    constexpr uint8_t nmax = 63;
+    float mx = 0.0f;
+    for (int i = 0; i < n; ++i) mx = std::isnan(x[i]) ? mx : std::max(mx, x[i]);  // f32::max skips NaN
+    if (mx == 0.0f) { std::memset(L, 0, n); return 0.0f; }
+    float iscale = (float)nmax / mx;
+    for (int i = 0; i < n; ++i) L[i] = (uint8_t)nearest_int(iscale * x[i]);  // i32 -> u8 wraps, as Rust `as`
+    const float scale = 1.0f / iscale;
+    float best_mse = 0.0f;
+    for (int i = 0; i < n; ++i) { const float diff = x[i] - scale * (float)L[i]; best_mse += qw[i] * diff * diff; }
+    for (int is = -4; is <= 4; ++is) {
+        if (is == 0) continue;
+        const float iscale_is = (0.1f * (float)is + (float)nmax) / mx;
+        const float scale_is = 1.0f / iscale_is;
+        float mse = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            const uint8_t li = std::min((uint8_t)nearest_int(iscale_is * x[i]), nmax);
+            const float diff = x[i] - scale_is * (float)li;
+            mse += qw[i] * diff * diff;
+        }
+        if (mse < best_mse) { best_mse = mse; iscale = iscale_is; }
+    }
+    float sumlx = 0.0f, suml2 = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        const uint8_t li = std::min(trunc_u8(std::round(iscale * x[i])), nmax);  // f32 -> u8 saturates
+        L[i] = li;
+        sumlx += qw[i] * x[i] * (float)li;
+        suml2 += qw[i] * ((float)li * (float)li);
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int n_changed = 0;
+        for (int i = 0; i < n; ++i) {
+            float slx = sumlx - qw[i] * x[i] * (float)L[i];
+            float sl2 = suml2 - qw[i] * ((float)L[i] * (float)L[i]);
+            if (slx > 0.0f && sl2 > 0.0f) {
+                const uint8_t nl = std::min((uint8_t)nearest_int(x[i] * sl2 / slx), nmax);
+                if (nl != L[i]) {
+                    slx += qw[i] * x[i] * (float)nl;
+                    sl2 += qw[i] * ((float)nl * (float)nl);
+                    if ((slx * slx) * suml2 > (sumlx * sumlx) * sl2) {
+                        L[i] = nl;
+                        sumlx = slx;
+                        suml2 = sl2;
+                        ++n_changed;
+                    }
+                }
+            }
+        }
+        if (n_changed == 0) break;
+    }
+    return sumlx / suml2;
+}
+// d, dmin and the twelve scale bytes of one superblock (out + 0 .. 15), imatrix form; the block is zeroed by the caller
+void kquant_imatrix_header(const float *x, const float *iw, int nmax, bool clamp63, uint8_t *out) {
+    float mins[8], scales[8], weights[32], sw[8];
+    uint8_t ls[8] = {0}, lm[8] = {0};
+    float sum_x2 = 0.0f;
+    for (int t = 0; t < 256; ++t) sum_x2 += x[t] * x[t];
+    const float sigma2 = 2.0f * sum_x2 / 256.0f;
+    for (int j = 0; j < 8; ++j) {
+        for (int l = 0; l < 32; ++l) weights[l] = iw[32 * j + l] * std::sqrt(sigma2 + x[32 * j + l] * x[32 * j + l]);
+        float sumw = 0.0f;
+        for (int l = 0; l < 32; ++l) sumw += weights[l];
+        sw[j] = sumw;
+        qkx3(nmax, x + 32 * j, weights, scales[j], mins[j]);
+    }
+    const float d_block = qp_quants(scales, ls, sw);
+    const float m_block = qp_quants(mins, lm, sw);
+    uint8_t *sc = out + 4;
+    for (int j = 0; j < 8; ++j) {
+        const uint8_t lsv = clamp63 ? std::min<uint8_t>(ls[j], 63) : ls[j], lmv = clamp63 ? std::min<uint8_t>(lm[j], 63) : lm[j];
+        if (j < 4) { sc[j] = lsv; sc[j + 4] = lmv; }
+        else {
+            sc[j + 4] = (uint8_t)((lsv & 0xF) | ((lmv & 0xF) << 4));
+            sc[j - 4] |= (uint8_t)((lsv >> 4) << 6);
+            sc[j] |= (uint8_t)((lmv >> 4) << 6);
+        }
+    }
+    const uint16_t hd = f32_to_f16(d_block), hm = f32_to_f16(m_block);
+    std::memcpy(out, &hd, 2);
+    std::memcpy(out + 2, &hm, 2);
+}
+void quantize_q4k_imatrix(const float *x, uint8_t *out, int64_t k, const float *imatrix) {
+    for (int64_t b = 0; b < k / 256; ++b, x += 256, out += 144) {
+        std::memset(out, 0, 144);
+        kquant_imatrix_header(x, imatrix + 256 * b, 15, false, out);
+        uint16_t hd, hm;
+        std::memcpy(&hd, out, 2);
+        std::memcpy(&hm, out + 2, 2);
+        const float d = f16_to_f32(hd), dmin = f16_to_f32(hm);
+        uint8_t L[256] = {0};
+        for (int j = 0; j < 8; ++j) {
+            uint8_t s, m;
+            scale_min_k4(j, out + 4, s, m);
+            const float dj = d * (float)s;
+            if (dj == 0.0f) continue;
+            const float dm = dmin * (float)m;
+            for (int t = 0; t < 32; ++t) L[32 * j + t] = (uint8_t)clampi(nearest_int((x[32 * j + t] + dm) / dj), 0, 15);
+        }
+        for (int g = 0; g < 4; ++g)
+            for (int t = 0; t < 32; ++t) out[16 + 32 * g + t] = (uint8_t)(L[64 * g + t] | (L[64 * g + 32 + t] << 4));
+    }
+}
+void quantize_q5k_imatrix(const float *x, uint8_t *out, int64_t k, const float *imatrix) {
+    for (int64_t b = 0; b < k / 256; ++b, x += 256, out += 176) {
+        std::memset(out, 0, 176);
+        kquant_imatrix_header(x, imatrix + 256 * b, 31, true, out);
+        uint16_t hd, hm;
+        std::memcpy(&hd, out, 2);
+        std::memcpy(&hm, out + 2, 2);
+        const float d = f16_to_f32(hd), dmin = f16_to_f32(hm);
+        uint8_t *qh = out + 16, *qs = out + 48;
+        uint8_t L[256] = {0};
+        for (int j = 0; j < 8; ++j) {
+            uint8_t s, m;
+            scale_min_k4(j, out + 4, s, m);
+            const float dj = d * (float)s;
+            if (dj == 0.0f) continue;
+            const float dm = dmin * (float)m;
+            for (int t = 0; t < 32; ++t) L[32 * j + t] = (uint8_t)clampi(nearest_int((x[32 * j + t] + dm) / dj), 0, 31);
+        }
+        uint8_t m1 = 1, m2 = 2;
+        for (int g = 0; g < 4; ++g) {
+            for (int t = 0; t < 32; ++t) {
+                uint8_t l1 = L[64 * g + t], l2 = L[64 * g + 32 + t];
+                if (l1 > 15) { l1 -= 16; qh[t] |= m1; }
+                if (l2 > 15) { l2 -= 16; qh[t] |= m2; }
+                qs[32 * g + t] = (uint8_t)(l1 | (l2 << 4));
+            }
+            m1 <<= 2;
+            m2 <<= 2;
+        }
+    }
+}
+
+void quantize_row_imatrix(GgmlDType t, const float *x, uint8_t *out, int64_t k, const float *imatrix) {
+    switch (t) {
+    case GgmlDType::Q4K: quantize_q4k_imatrix(x, out, k, imatrix); return;
+    case GgmlDType::Q5K: quantize_q5k_imatrix(x, out, k, imatrix); return;
+    case GgmlDType::Q6K: quantize_q6k(x, out, k, imatrix); return;
+    default: throw Error(LLOOM_ERR_DTYPE, "`from_float_imatrix` is unimplemented for this type");
+    }
+}
+
 void quantize_row(GgmlDType t, const float *x, uint8_t *out, int64_t k) {
     switch (t) {
     case GgmlDType::Q8_0: quantize_q8_0(x, out, k); return;
@@ -404,17 +608,23 @@ void quantize_row(GgmlDType t, const float *x, uint8_t *out, int64_t k) {
 int64_t block_size(GgmlDType t) { return lloom_b200_block_elems((int)t); }
 int64_t type_size(GgmlDType t) { return lloom_b200_block_bytes((int)t); }
 
-void quantize_rows(GgmlDType t, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads) {
+void quantize_rows(GgmlDType t, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads,
+                   const float *imatrix) {
     if (t != GgmlDType::Q8_0 && t != GgmlDType::Q4K && t != GgmlDType::Q6K && t != GgmlDType::Q5K &&
         t != GgmlDType::Q4_0 && t != GgmlDType::Q5_0)
         throw Error(LLOOM_ERR_DTYPE, "quantize: not a weight type of this backend");
+    if (imatrix && t != GgmlDType::Q4K && t != GgmlDType::Q5K && t != GgmlDType::Q6K)
+        throw Error(LLOOM_ERR_DTYPE, "`from_float_imatrix` is unimplemented for this type");
     if (k <= 0 || k % block_size(t) != 0) throw Error(LLOOM_ERR_SHAPE, "quantize: k is not a whole number of blocks");
     const int64_t row_bytes = k / block_size(t) * type_size(t);
     nthreads = (int)std::max<int64_t>(1, std::min<int64_t>(nthreads, rows));
     auto work = [&](int tid) {
         const int64_t per = (rows + nthreads - 1) / nthreads;
         const int64_t r1 = std::min(rows, (tid + 1) * per);
-        for (int64_t r = tid * per; r < r1; ++r) quantize_row(t, x + r * k, (uint8_t *)blocks + r * row_bytes, k);
+        for (int64_t r = tid * per; r < r1; ++r) {
+            if (imatrix) quantize_row_imatrix(t, x + r * k, (uint8_t *)blocks + r * row_bytes, k, imatrix);
+            else quantize_row(t, x + r * k, (uint8_t *)blocks + r * row_bytes, k);
+        }
     };
     std::vector<std::thread> pool;
     for (int tid = 1; tid < nthreads; ++tid) pool.emplace_back(work, tid);
@@ -456,11 +666,17 @@ std::unique_ptr<QCudaStorage> QCudaStorage::load_quantized(const CudaDevice &dev
 }
 
 void QCudaStorage::quantize_onto(const float *host_src, int64_t el_count, int64_t k, int nthreads) {
+    quantize_imatrix_onto(host_src, el_count, nullptr, k, nthreads);
+}
+
+void QCudaStorage::quantize_imatrix_onto(const float *host_src, int64_t el_count, const float *imatrix_weights,
+                                         int64_t n_per_row, int nthreads) {
+    const int64_t k = n_per_row;
     if (k <= 0 || el_count % k != 0) throw Error(LLOOM_ERR_SHAPE, "quantize_onto: shape");
     const int64_t need = el_count / block_size(dtype_) * type_size(dtype_);
     if (need != len_) throw Error(LLOOM_ERR_SHAPE, "quantize_onto: storage size does not match the source");
     std::vector<uint8_t> blocks((size_t)need);
-    quantize_rows(dtype_, host_src, blocks.data(), el_count / k, k, nthreads);
+    quantize_rows(dtype_, host_src, blocks.data(), el_count / k, k, nthreads, imatrix_weights);
     DeviceGuard g(dev_.ordinal);
     cuda_check(cudaMemcpyAsync(data_, blocks.data(), (size_t)need, cudaMemcpyHostToDevice, (cudaStream_t)dev_.stream),
                "cudaMemcpyAsync");
@@ -545,6 +761,20 @@ std::shared_ptr<QTensor> QTensor::quantize(const CudaDevice &dev, const float *s
     return std::make_shared<QTensor>(std::move(st), std::move(shape));
 }
 
+std::shared_ptr<QTensor> QTensor::quantize_imatrix(const CudaDevice &dev, const float *src, const float *imatrix_weights,
+                                                   int64_t imatrix_len, std::vector<int64_t> shape, GgmlDType dtype,
+                                                   int nthreads) {
+    if (shape.empty()) throw Error(-1, "scalar tensor cannot be quantized");
+    if (imatrix_len != shape.back()) throw Error(-1, "imatrix weights must have the same length as the last dim of src");
+    int64_t elems = 1;
+    for (int64_t d : shape) elems *= d;
+    if (shape.back() % block_size(dtype) != 0)
+        throw Error(-1, "quantized tensor must have their last dim divisible by block size");
+    auto st = QCudaStorage::zeros(dev, elems, dtype);
+    st->quantize_imatrix_onto(src, elems, imatrix_weights, shape.back(), nthreads);
+    return std::make_shared<QTensor>(std::move(st), std::move(shape));
+}
+
 std::shared_ptr<QTensor> QTensor::from_data(const CudaDevice &dev, const void *bytes, int64_t nbytes, GgmlDType dtype,
                                             std::vector<int64_t> shape) {
     int64_t elems = 1;
@@ -615,6 +845,22 @@ const char *lloom_b200_host_last_error(void) { return t_host_error.c_str(); }
 
 int lloom_b200_host_quantize_rows(int dtype, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads) {
     return guarded([&] { quantize_rows((GgmlDType)dtype, x, blocks, rows, k, nthreads); });
+}
+
+int lloom_b200_host_quantize_rows_imatrix(int dtype, const float *x, const float *imatrix, void *blocks, int64_t rows,
+                                          int64_t k, int nthreads) {
+    return guarded([&] {
+        if (!imatrix) throw Error(LLOOM_ERR_NULL, "quantize_imatrix: no importance weights");
+        quantize_rows((GgmlDType)dtype, x, blocks, rows, k, nthreads, imatrix);
+    });
+}
+
+int lloom_b200_host_qtensor_quantize_imatrix(int device, void *stream, const float *src, const float *imatrix, int64_t n,
+                                             int64_t k, int dtype, int nthreads, void **out) {
+    return guarded([&] {
+        CudaDevice dev{device, stream};
+        *out = new Handle{QTensor::quantize_imatrix(dev, src, imatrix, k, {n, k}, (GgmlDType)dtype, nthreads)};
+    });
 }
 
 int lloom_b200_host_qtensor_quantize(int device, void *stream, const float *src, int64_t n, int64_t k, int dtype,

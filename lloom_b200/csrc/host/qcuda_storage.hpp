@@ -35,7 +35,10 @@ struct CudaDevice {
 // CPU weight quantizers, T::from_float (k_quants.rs:738-767, 1622-1680, 2174-2244 with
 // utils.rs:62-224, 227-284).  The reference's CUDA slot quantizes weights on the CPU and uploads
 // (cuda.rs:720-741); so does this one.  rows x k floats -> rows x (k/block) blocks, rows in parallel.
-void quantize_rows(GgmlDType t, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads);
+// imatrix != nullptr: T::from_float_imatrix with one importance weight per column (k_quants.rs:1682, 1959, 2246;
+// Q4K, Q5K and Q6K only, like the reference).
+void quantize_rows(GgmlDType t, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads,
+                   const float *imatrix = nullptr);
 
 class QCudaStorage {
   public:
@@ -50,6 +53,9 @@ class QCudaStorage {
                                                         GgmlDType dtype);
     // cuda.rs:720-741 quantize_onto: CPU quantizer over host f32, then upload.
     void quantize_onto(const float *host_src, int64_t el_count, int64_t k, int nthreads);
+    // cuda.rs:743-790 quantize_imatrix / quantize_imatrix_onto: the same with importance weights, one per column
+    void quantize_imatrix_onto(const float *host_src, int64_t el_count, const float *imatrix_weights, int64_t n_per_row,
+                               int nthreads);
 
     GgmlDType dtype() const { return dtype_; }
     const CudaDevice &device() const { return dev_; }
@@ -80,6 +86,10 @@ class QTensor {
     // mod.rs:919-938: quantize host f32 [.., k] with the CPU quantizer and move it to the device
     static std::shared_ptr<QTensor> quantize(const CudaDevice &dev, const float *src, std::vector<int64_t> shape,
                                              GgmlDType dtype, int nthreads);
+    // mod.rs:940-1020 quantize_imatrix / quantize_imatrix_onto: imatrix_len must equal the last dim
+    static std::shared_ptr<QTensor> quantize_imatrix(const CudaDevice &dev, const float *src, const float *imatrix_weights,
+                                                     int64_t imatrix_len, std::vector<int64_t> shape, GgmlDType dtype,
+                                                     int nthreads);
     static std::shared_ptr<QTensor> from_data(const CudaDevice &dev, const void *bytes, int64_t nbytes,
                                               GgmlDType dtype, std::vector<int64_t> shape);
     GgmlDType dtype() const { return storage_->dtype(); }

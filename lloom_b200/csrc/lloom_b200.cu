@@ -106,9 +106,10 @@ static cudaError_t launch_gemv_dp4a(const GemvParams &p, int grid, int smem, boo
     return cudaErrorInvalidValue;
 }
 
-// Whether the tensor-core GEMV quantizes the activations itself (as its prologue): up to two rows, and few enough
-// 256-element blocks that a CTA's sixteen warps get through them in two rounds.
-static bool gemv_mma_fused(int64_t m, int64_t k) { return m <= kMmaFusedMaxM && m * (k / QK_K) <= 32; }
+// Whether the tensor-core GEMV quantizes the activations itself (as its prologue, every CTA all rows): up to 48
+// 256-element blocks, three per warp.  Measured per forward on [14336, 4096], prologue against separate quantizer
+// kernel: 3 rows 10.5 / 11.1 us, 4 rows 11.4 / 11.1 us, 8 rows 14.7 / 11.2 us; [4096, 14336], 2 rows: 13.1 / 11.8 us.
+static bool gemv_mma_fused(int64_t m, int64_t k) { return m * (k / QK_K) <= 48; }
 
 // Shared-memory plan of the tensor-core GEMV: a stage holds `chunk_sb` superblocks of 16 rows -- whole rows when two
 // such stages fit beside the activation planes, else the rows are cut into `nchunks` pieces of equal length
@@ -180,6 +181,8 @@ struct GemvGroup {
     int64_t n[kMaxGroup] = {};
     int64_t ldy[kMaxGroup] = {};
     int store[kMaxGroup] = {};
+    const uint32_t *moe_ids = nullptr;  // routed experts: matrix g = expert moe_ids[g] of the stack at `w` of the launch
+    int moe_experts = 0;
 };
 
 // Launches the GEMV.  Exactly one of `act` (canonical activation blocks) and `x` (f32 activations,
@@ -233,6 +236,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
         p.goff[group->count] = (int)off;
         p.n = (int)off;
         n = off;
+        p.moe_ids = group->moe_ids;
+        p.moe_experts = group->moe_experts;
     }
     // lanes per row: one lane per unit (superblock, or pair of 32-element blocks), rounded up to a power of two
     const int64_t units = k / (act_is_q8_0(w_dtype) ? 64 : 256);
@@ -318,7 +323,7 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
             // Long rows in a side-by-side shape: cut the rows into pieces of 16 units (32 for 64-element units), so
             // that a stage is 16 (8) rows x one piece -- the tile the kernel streams at K = 4096 -- instead of giving
             // up the overlap between consecutive launches for a one-CTA-per-SM shape.
-            if (group || !shapes[si].half || cw > 8 || p.row_bytes % 16 != 0) continue;
+            if ((group && m != 1) || !shapes[si].half || cw > 8 || p.row_bytes % 16 != 0) continue;
             const int cu = act_is_q8_0(w_dtype) ? 32 : 16;
             if (units <= cu || ((int64_t)cu * p.unit_bytes) % 16 != 0) continue;
             const int cl = act_is_q8_0(w_dtype) ? 5 : 4;
@@ -689,6 +694,41 @@ int lloom_b200_qmatmul_fwd_group(int w_dtype, int n_mats, const void *const *w_b
         rc = gemv_launch(w_dtype, group.w[g], workspace, nullptr, group.y[g], m, group.n[g], k, group.ldy[g],
                          (cudaStream_t)stream, all_mma, &out);
         if (rc != LLOOM_OK) return rc;
+    }
+    return LLOOM_OK;
+}
+
+int lloom_b200_indexed_moe_forward(int w_dtype, const void *w_experts, int64_t n_experts, int64_t n, int64_t k,
+                                   const float *x, int64_t batch, int64_t in_dim1, const uint32_t *ids, int64_t topk,
+                                   float *out, void *workspace, int64_t workspace_bytes, void *stream) {
+    int rc = check_common(w_dtype, 1, n, k);
+    if (rc != LLOOM_OK) return rc;
+    if (n_experts <= 0 || n_experts > (1 << 20) || batch <= 0 || topk <= 0 || (in_dim1 != 1 && in_dim1 != topk))
+        return LLOOM_ERR_SHAPE;
+    if (!w_experts || !x || !ids || !out) return LLOOM_ERR_NULL;
+    if (n_experts * n > (1ll << 30)) return LLOOM_ERR_SHAPE;
+    if (!aligned(w_experts, 16) || !aligned(x, 16) || !aligned(ids, 4) || !aligned(out, 4)) return LLOOM_ERR_ALIGN;
+    const int64_t need = lloom_b200_workspace_bytes(w_dtype, 1, n, k);
+    if (!workspace || workspace_bytes < need) return LLOOM_ERR_WORKSPACE;
+    if (!aligned(workspace, 256)) return LLOOM_ERR_ALIGN;
+    const bool share_x = in_dim1 == 1 && topk <= kMaxGroup;
+    for (int64_t b = 0; b < batch; ++b) {
+        for (int64_t t0 = 0; t0 < topk; t0 += share_x ? topk : 1) {
+            GemvGroup group;
+            group.count = share_x ? (int)topk : 1;
+            for (int g = 0; g < group.count; ++g) {
+                group.w[g] = (const uint8_t *)w_experts;  // replaced on the device by the routed expert
+                group.y[g] = out + ((b * topk + t0 + g) * n);
+                group.n[g] = n;
+                group.ldy[g] = n;
+                group.store[g] = LLOOM_STORE_PLAIN;
+            }
+            group.moe_ids = ids + b * topk + t0;
+            group.moe_experts = (int)n_experts;
+            const float *xrow = x + (b * in_dim1 + (in_dim1 == 1 ? 0 : t0)) * k;
+            rc = gemv_launch(w_dtype, w_experts, nullptr, xrow, nullptr, 1, 0, k, 0, (cudaStream_t)stream, false, nullptr, &group);
+            if (rc != LLOOM_OK) return rc;
+        }
     }
     return LLOOM_OK;
 }

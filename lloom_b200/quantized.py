@@ -269,6 +269,18 @@ class QTensor:
         return cls.from_data(quantize_weights_host(src, dtype, nthreads), dtype,
                              tuple(src.shape), device)
 
+    @classmethod
+    def quantize_imatrix(cls, src, imatrix_weights, dtype: GgmlDType, device="cuda", nthreads: int = 0) -> "QTensor":
+        """``QTensor::quantize_imatrix`` / ``quantize_imatrix_onto`` (mod.rs:940-1020): importance-weighted CPU
+        quantization (one weight per column of ``src``), then upload.  Q4K, Q5K and Q6K, like the reference."""
+        imatrix_weights = np.ascontiguousarray(imatrix_weights, dtype=np.float32)
+        if imatrix_weights.ndim != 1 or imatrix_weights.shape[0] != src.shape[-1]:
+            raise LloomError(_lib.ERR_SHAPE, "quantize_imatrix",
+                             f"imatrix weights must have the same length {imatrix_weights.shape} as the last dim of src "
+                             f"{src.shape[-1]}")
+        return cls.from_data(quantize_weights_host(src, dtype, nthreads, imatrix=imatrix_weights), dtype,
+                             tuple(src.shape), device)
+
     def dtype(self) -> GgmlDType:
         return self.storage.dtype()
 
@@ -303,6 +315,35 @@ class QTensor:
     def fwd(self, x: torch.Tensor) -> torch.Tensor:
         """``CustomOp1::cuda_fwd`` (mod.rs:2009-2019)."""
         return self.storage.fwd(self.shape, x)
+
+    def indexed_moe_forward(self, x: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Routed matmul over stacked experts (mod.rs:1539-1650, cuda.rs:505-622): weight ``[n_experts, n, k]``,
+        ``x [batch, 1 or topk, k]`` f32, ``ids [batch, topk]`` on the device -> ``[batch, topk, n]`` with
+        ``out[b, t] = W[ids[b, t]] @ x[b, 0 or t]``.  Shape errors follow the reference's CPU arm."""
+        if len(self.shape) != 3:
+            raise LloomError(_lib.ERR_SHAPE, "indexed_moe_forward", f"weight shape {self.shape} is not [experts, n, k]")
+        n_experts, n, k = self.shape
+        if x.dim() != 3 or ids.dim() != 2:
+            raise LloomError(_lib.ERR_SHAPE, "indexed_moe_forward", "x is [batch, in_dim1, k], ids [batch, topk]")
+        batch, in_dim1, k_in = x.shape
+        batch_ids, topk = ids.shape
+        if k_in != k or batch != batch_ids or (in_dim1 != 1 and in_dim1 != topk):
+            raise LloomError(_lib.ERR_SHAPE, "indexed_moe_forward",
+                             f"x {tuple(x.shape)} / ids {tuple(ids.shape)} do not fit weight {self.shape}")
+        dev = self.device()
+        if x.device != dev or ids.device != dev:
+            raise LloomError(_lib.ERR_DEVICE, "indexed_moe_forward", "x and ids must be on the weight's device")
+        x = x.float().contiguous()
+        ids32 = ids.to(torch.int64).to(torch.int32).contiguous()  # u32 bit pattern
+        out = torch.empty(batch, topk, n, dtype=torch.float32, device=dev)
+        L = _lib.lib()
+        with torch.cuda.device(dev):
+            ws_bytes = int(L.lloom_b200_workspace_bytes(int(self.dtype()), 1, n, k))
+            ws = _Workspace.get(dev, ws_bytes)
+            check(L.lloom_b200_indexed_moe_forward(int(self.dtype()), self.device_ptr(), n_experts, n, k, x.data_ptr(), batch,
+                                                   in_dim1, ids32.data_ptr(), topk, out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                   _stream_ptr(dev)), "indexed_moe_forward")
+        return out
 
 
 class QMatMul:
@@ -357,8 +398,8 @@ def forward_group(mats: Sequence["QMatMul"], xs: torch.Tensor, stores: Sequence[
     (0 plain, 1 SiLU, 2 multiply into ``outs[g]``).  Each result equals that matrix's own ``forward`` bit for bit."""
     import ctypes as C
 
-    if not 1 <= len(mats) <= 4:
-        raise LloomError(_lib.ERR_SHAPE, "forward_group", "1 to 4 matrices")
+    if not 1 <= len(mats) <= 8:
+        raise LloomError(_lib.ERR_SHAPE, "forward_group", "1 to 8 matrices")
     st0 = mats[0].qtensor.storage
     dt, dev = st0.dtype(), st0.device()
     k = mats[0].qtensor.shape[1]
@@ -385,8 +426,9 @@ def forward_group(mats: Sequence["QMatMul"], xs: torch.Tensor, stores: Sequence[
     return list(outs)
 
 
-def quantize_weights_host(src, dtype: GgmlDType, nthreads: int = 0) -> np.ndarray:
-    """CPU ``T::from_float`` over the rows of ``src`` through the library's host layer; uint8 [rows, row_bytes]."""
+def quantize_weights_host(src, dtype: GgmlDType, nthreads: int = 0, imatrix=None) -> np.ndarray:
+    """CPU ``T::from_float`` (``from_float_imatrix`` when ``imatrix`` is given) over the rows of ``src`` through the
+    library's host layer; uint8 [rows, row_bytes]."""
     import os
 
     dtype = GgmlDType(dtype)
@@ -399,8 +441,13 @@ def quantize_weights_host(src, dtype: GgmlDType, nthreads: int = 0) -> np.ndarra
     rows = src.size // k
     out = np.zeros((rows, k // dtype.block_size() * dtype.type_size()), dtype=np.uint8)
     L = _lib.lib()
-    rc = L.lloom_b200_host_quantize_rows(int(dtype), src.ctypes.data, out.ctypes.data, rows, k,
-                                         nthreads or (os.cpu_count() or 1))
+    if imatrix is not None:
+        imatrix = np.ascontiguousarray(imatrix, dtype=np.float32)
+        rc = L.lloom_b200_host_quantize_rows_imatrix(int(dtype), src.ctypes.data, imatrix.ctypes.data, out.ctypes.data, rows,
+                                                     k, nthreads or (os.cpu_count() or 1))
+    else:
+        rc = L.lloom_b200_host_quantize_rows(int(dtype), src.ctypes.data, out.ctypes.data, rows, k,
+                                             nthreads or (os.cpu_count() or 1))
     if rc != 0:
         raise LloomError(rc, "quantize", L.lloom_b200_host_last_error().decode())
     return out

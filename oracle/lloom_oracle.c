@@ -323,7 +323,7 @@ static void dequantize_row_q4k(const blk_q4k *x, float *y, int64_t k) {
 
 /* utils.rs:62-224 make_qx_quants(n, nmax, x, ls, rmse_type = 1, qw = null):
  * weights are x*x; the rmse_type >= 3 tail of the reference is unreachable here. */
-static float make_qx_quants_w2(int n, int nmax, const float *x, int8_t *ls) {
+static float make_qx_quants_w(int n, int nmax, const float *x, int8_t *ls, const float *qw) {
     float max = 0.0f, amax = 0.0f;
     for (int i = 0; i < n; ++i) {
         float ax = fabsf(x[i]);
@@ -338,7 +338,7 @@ static float make_qx_quants_w2(int n, int nmax, const float *x, int8_t *ls) {
     for (int i = 0; i < n; ++i) {
         int32_t l = clampi(nearest_int(iscale * x[i]), -nmax, nmax - 1);
         ls[i] = (int8_t)(l + nmax);
-        float w = x[i] * x[i];
+        float w = qw ? qw[i] : x[i] * x[i];
         float lf = (float)l;
         sumlx += w * x[i] * lf;
         suml2 += w * lf * lf;
@@ -352,7 +352,7 @@ static float make_qx_quants_w2(int n, int nmax, const float *x, int8_t *ls) {
         for (int i = 0; i < n; ++i) {
             int32_t l = clampi(nearest_int(is * x[i]), -nmax, nmax - 1);
             if (l + nmax != (int32_t)ls[i]) changed = 1;
-            float w = x[i] * x[i];
+            float w = qw ? qw[i] : x[i] * x[i];
             float lf = (float)l;
             slx += w * x[i] * lf;
             sl2 += w * lf * lf;
@@ -370,7 +370,7 @@ static float make_qx_quants_w2(int n, int nmax, const float *x, int8_t *ls) {
     for (int itry = 0; itry < 5; ++itry) {
         int n_changed = 0;
         for (int i = 0; i < n; ++i) {
-            float w = x[i] * x[i];
+            float w = qw ? qw[i] : x[i] * x[i];
             int32_t l = (int32_t)ls[i] - nmax;
             float slx = sumlx - w * x[i] * (float)l;
             if (slx > 0.0f) {
@@ -398,7 +398,9 @@ static float make_qx_quants_w2(int n, int nmax, const float *x, int8_t *ls) {
 
 /* BlockQ6K::from_float, k_quants.rs:2174-2244.  An all-zero superblock follows
  * the same float path as the reference (iscale = -inf, d = f16(-0), NaN -> 0). */
-static void quantize_row_q6k(const float *x, blk_q6k *y, int64_t k) {
+/* imatrix == NULL: BlockQ6K::from_float (k_quants.rs:2174-2244); else from_float_imatrix (k_quants.rs:2246-2325) on
+ * one row: the importance weights of superblock i of the row are imatrix[256 i ..]. */
+static void quantize_row_q6k_w(const float *x, blk_q6k *y, int64_t k, const float *imatrix) {
     int8_t L[QK_K];
     float scales[QK_K / 16];
     memset(L, 0, sizeof(L));
@@ -407,7 +409,7 @@ static void quantize_row_q6k(const float *x, blk_q6k *y, int64_t k) {
         blk_q6k *b = &y[i];
         float max_scale = 0.0f, max_abs_scale = 0.0f;
         for (int ib = 0; ib < 16; ++ib) {
-            float s = make_qx_quants_w2(16, 32, xb + 16 * ib, L + 16 * ib);
+            float s = make_qx_quants_w(16, 32, xb + 16 * ib, L + 16 * ib, imatrix ? imatrix + QK_K * i + 16 * ib : 0);
             scales[ib] = s;
             float as = fabsf(s);
             if (as > max_abs_scale) { max_abs_scale = as; max_scale = s; }
@@ -659,6 +661,221 @@ static inline void q5k_codes(const blk_q5k *b, int8_t *a) {
 }
 static inline void q5k_scales_mins(const blk_q5k *b, uint8_t *sc, uint8_t *mn) {
     for (int j = 0; j < 8; ++j) scale_min_k4(j, b->scales, &sc[j], &mn[j]);
+}
+
+static void quantize_row_q6k(const float *x, blk_q6k *y, int64_t k) { quantize_row_q6k_w(x, y, k, 0); }
+
+/* ---- importance-matrix quantizers: from_float_imatrix of Q4K (k_quants.rs:1682-1745) and Q5K (:1959-2041), with
+ * make_qkx3_quants (utils.rs:372-466) and make_qp_quants (utils.rs:469-560) ---- */
+
+static void make_qkx3_quants(int n, int nmax, const float *x, const float *weights, float rmin, float rdelta, int nstep,
+                             int use_mad, float *out_scale, float *out_min) {
+    uint8_t L[32], Laux[32];
+    memset(L, 0, sizeof(L));
+    float min_val = x[0], max_val = x[0];
+    float sum_w = weights ? weights[0] : x[0] * x[0];
+    float sum_x = sum_w * x[0];
+    for (int i = 1; i < n; ++i) {
+        if (x[i] < min_val) min_val = x[i];
+        if (x[i] > max_val) max_val = x[i];
+        float w = weights ? weights[i] : x[i] * x[i];
+        sum_w += w;
+        sum_x += w * x[i];
+    }
+    if (min_val > 0.0f) min_val = 0.0f;
+    if (max_val <= min_val) { *out_scale = 0.0f; *out_min = -min_val; return; }
+    float iscale = (float)nmax / (max_val - min_val);
+    float scale = 1.0f / iscale;
+    float best_mad = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        uint8_t l = (uint8_t)clampi(nearest_int(iscale * (x[i] - min_val)), 0, nmax);
+        L[i] = l;
+        float diff = scale * (float)l + min_val - x[i];
+        diff = use_mad ? fabsf(diff) : diff * diff;
+        float w = weights ? weights[i] : x[i] * x[i];
+        best_mad += w * diff;
+    }
+    if (nstep < 1) { *out_scale = scale; *out_min = -min_val; return; }
+    for (int is = 0; is <= nstep; ++is) {
+        iscale = (rmin + rdelta * (float)is + (float)nmax) / (max_val - min_val);
+        float sum_l = 0.0f, sum_l2 = 0.0f, sum_xl = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            uint8_t l = (uint8_t)clampi(nearest_int(iscale * (x[i] - min_val)), 0, nmax);
+            Laux[i] = l;
+            float w = weights ? weights[i] : x[i] * x[i];
+            float lf = (float)l;
+            sum_l += w * lf;
+            sum_l2 += w * (lf * lf);
+            sum_xl += w * lf * x[i];
+        }
+        float d = sum_w * sum_l2 - sum_l * sum_l;
+        if (d > 0.0f) {
+            float this_scale = (sum_w * sum_xl - sum_x * sum_l) / d;
+            float this_min = (sum_l2 * sum_x - sum_l * sum_xl) / d;
+            if (this_min > 0.0f) { this_min = 0.0f; this_scale = sum_xl / sum_l2; }
+            float mad = 0.0f;
+            for (int i = 0; i < n; ++i) {
+                float diff = this_scale * (float)Laux[i] + this_min - x[i];
+                diff = use_mad ? fabsf(diff) : diff * diff;
+                float w = weights ? weights[i] : x[i] * x[i];
+                mad += w * diff;
+            }
+            if (mad < best_mad) {
+                memcpy(L, Laux, sizeof(L));
+                best_mad = mad;
+                scale = this_scale;
+                min_val = this_min;
+            }
+        }
+    }
+    *out_scale = scale;
+    *out_min = -min_val;
+}
+
+static float make_qp_quants(int n, uint8_t nmax, const float *x, uint8_t *L, const float *qw) {
+    float max = 0.0f;
+    for (int i = 0; i < n; ++i) max = rmaxf(max, x[i]);
+    if (max == 0.0f) { for (int i = 0; i < n; ++i) L[i] = 0; return 0.0f; }
+    float iscale = (float)nmax / max;
+    for (int i = 0; i < n; ++i) L[i] = (uint8_t)nearest_int(iscale * x[i]);  /* i32 -> u8: wrapping, as Rust `as` */
+    float scale = 1.0f / iscale;
+    float best_mse = 0.0f;
+    for (int i = 0; i < n; ++i) { float diff = x[i] - scale * (float)L[i]; best_mse += qw[i] * diff * diff; }
+    for (int is = -4; is <= 4; ++is) {
+        if (is == 0) continue;
+        float iscale_is = (0.1f * (float)is + (float)nmax) / max;
+        float scale_is = 1.0f / iscale_is;
+        float mse = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            uint8_t li = (uint8_t)nearest_int(iscale_is * x[i]);
+            if (li > nmax) li = nmax;
+            float diff = x[i] - scale_is * (float)li;
+            mse += qw[i] * diff * diff;
+        }
+        if (mse < best_mse) { best_mse = mse; iscale = iscale_is; }
+    }
+    float sumlx = 0.0f, suml2 = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        uint8_t li = sat_u8_trunc(roundf(iscale * x[i]));  /* f32 -> u8: saturating */
+        if (li > nmax) li = nmax;
+        L[i] = li;
+        sumlx += qw[i] * x[i] * (float)li;
+        suml2 += qw[i] * ((float)li * (float)li);
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int n_changed = 0;
+        for (int i = 0; i < n; ++i) {
+            float slx = sumlx - qw[i] * x[i] * (float)L[i];
+            float sl2 = suml2 - qw[i] * ((float)L[i] * (float)L[i]);
+            if (slx > 0.0f && sl2 > 0.0f) {
+                uint8_t new_li = (uint8_t)nearest_int(x[i] * sl2 / slx);
+                if (new_li > nmax) new_li = nmax;
+                if (new_li != L[i]) {
+                    slx += qw[i] * x[i] * (float)new_li;
+                    sl2 += qw[i] * ((float)new_li * (float)new_li);
+                    if ((slx * slx) * suml2 > (sumlx * sumlx) * sl2) {
+                        L[i] = new_li;
+                        sumlx = slx;
+                        suml2 = sl2;
+                        ++n_changed;
+                    }
+                }
+            }
+        }
+        if (n_changed == 0) break;
+    }
+    return sumlx / suml2;
+}
+
+/* the (d, dmin, scales[12]) header both k-quants with 6-bit (scale, min) pairs share, imatrix form: returns through b */
+static void kquant_imatrix_header(const float *xb, const float *iw, int nmax, int clamp63, uint16_t *d_out, uint16_t *dmin_out,
+                                  uint8_t *scales12) {
+    float mins[8], scales[8], weights[32], sw[8];
+    uint8_t ls[8], lm[8];
+    memset(ls, 0, sizeof(ls));
+    memset(lm, 0, sizeof(lm));
+    float sum_x2 = 0.0f;
+    for (int t = 0; t < QK_K; ++t) sum_x2 += xb[t] * xb[t];
+    float sigma2 = 2.0f * sum_x2 / (float)QK_K;
+    for (int j = 0; j < 8; ++j) {
+        for (int l = 0; l < 32; ++l) weights[l] = iw[32 * j + l] * sqrtf(sigma2 + xb[32 * j + l] * xb[32 * j + l]);
+        float sumw = 0.0f;
+        for (int l = 0; l < 32; ++l) sumw += weights[l];
+        sw[j] = sumw;
+        make_qkx3_quants(32, nmax, xb + 32 * j, weights, -0.9f, 0.05f, 36, 0, &scales[j], &mins[j]);
+    }
+    float d_block = make_qp_quants(8, 63, scales, ls, sw);
+    float m_block = make_qp_quants(8, 63, mins, lm, sw);
+    for (int j = 0; j < 8; ++j) {
+        uint8_t lsv = ls[j], lmv = lm[j];
+        if (clamp63) { if (lsv > 63) lsv = 63; if (lmv > 63) lmv = 63; }
+        if (j < 4) {
+            scales12[j] = lsv;
+            scales12[j + 4] = lmv;
+        } else {
+            scales12[j + 4] = (uint8_t)((lsv & 0xF) | ((lmv & 0xF) << 4));
+            scales12[j - 4] |= (uint8_t)((lsv >> 4) << 6);
+            scales12[j] |= (uint8_t)((lmv >> 4) << 6);
+        }
+    }
+    *d_out = lo_f32_to_f16(d_block);
+    *dmin_out = lo_f32_to_f16(m_block);
+}
+
+static void quantize_row_q4k_imatrix(const float *x, blk_q4k *y, int64_t k, const float *imatrix) {
+    for (int64_t i = 0; i < k / QK_K; ++i) {
+        const float *xb = x + i * QK_K;
+        blk_q4k *b = &y[i];
+        memset(b, 0, sizeof(*b));
+        kquant_imatrix_header(xb, imatrix + QK_K * i, 15, 0, &b->d, &b->dmin, b->scales);
+        uint8_t L[QK_K];
+        memset(L, 0, sizeof(L));
+        float bd = lo_f16_to_f32(b->d), bdmin = lo_f16_to_f32(b->dmin);
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, m;
+            scale_min_k4(j, b->scales, &sc, &m);
+            float d = bd * (float)sc;
+            if (d != 0.0f) {
+                float dm = bdmin * (float)m;
+                for (int t = 0; t < 32; ++t) L[32 * j + t] = (uint8_t)clampi(nearest_int((xb[32 * j + t] + dm) / d), 0, 15);
+            }
+        }
+        for (int g = 0; g < 4; ++g)
+            for (int t = 0; t < 32; ++t) b->qs[32 * g + t] = (uint8_t)(L[64 * g + t] | (L[64 * g + 32 + t] << 4));
+    }
+}
+
+static void quantize_row_q5k_imatrix(const float *x, blk_q5k *y, int64_t k, const float *imatrix) {
+    for (int64_t i = 0; i < k / QK_K; ++i) {
+        const float *xb = x + i * QK_K;
+        blk_q5k *b = &y[i];
+        memset(b, 0, sizeof(*b));
+        kquant_imatrix_header(xb, imatrix + QK_K * i, 31, 1, &b->d, &b->dmin, b->scales);
+        uint8_t L[QK_K];
+        memset(L, 0, sizeof(L));
+        float bd = lo_f16_to_f32(b->d), bdmin = lo_f16_to_f32(b->dmin);
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, m;
+            scale_min_k4(j, b->scales, &sc, &m);
+            float d = bd * (float)sc;
+            if (d != 0.0f) {
+                float dm = bdmin * (float)m;
+                for (int t = 0; t < 32; ++t) L[32 * j + t] = (uint8_t)clampi(nearest_int((xb[32 * j + t] + dm) / d), 0, 31);
+            }
+        }
+        uint8_t m1 = 1, m2 = 2;
+        for (int n = 0; n < QK_K; n += 64) {
+            int off = (n / 64) * 32;
+            for (int j = 0; j < 32; ++j) {
+                uint8_t l1 = L[n + j], l2 = L[n + j + 32];
+                if (l1 > 15) { l1 -= 16; b->qh[j] |= m1; }
+                if (l2 > 15) { l2 -= 16; b->qh[j] |= m2; }
+                b->qs[off + j] = (uint8_t)(l1 | (l2 << 4));
+            }
+            m1 <<= 2;
+            m2 <<= 2;
+        }
+    }
 }
 
 /* ---- vec_dot, scalar generic order (vec_dot_unopt) ---- */
@@ -1215,6 +1432,18 @@ int lo_quantize_row(int dtype, const float *x, void *blocks, int64_t k) {
     case LO_Q4_0: quantize_row_q4_0(x, blocks, k); return 0;
     case LO_Q5_0: quantize_row_q5_0(x, blocks, k); return 0;
     case LO_Q5_K: quantize_row_q5k(x, blocks, k); return 0;
+    }
+    return -2;
+}
+
+/* T::from_float_imatrix over one row of k = n_per_row elements: the importance weights are one per column
+ * (QTensor::quantize_imatrix, mod.rs:940-975); only Q4K, Q5K and Q6K of this oracle's formats implement it. */
+int lo_quantize_row_imatrix(int dtype, const float *x, void *blocks, int64_t k, const float *imatrix) {
+    if (k % QK_K != 0) return -2;
+    switch (dtype) {
+    case LO_Q4_K: quantize_row_q4k_imatrix(x, blocks, k, imatrix); return 0;
+    case LO_Q5_K: quantize_row_q5k_imatrix(x, blocks, k, imatrix); return 0;
+    case LO_Q6_K: quantize_row_q6k_w(x, blocks, k, imatrix); return 0;
     }
     return -2;
 }

@@ -48,6 +48,8 @@ float lo_f16_to_f32(uint16_t h);
 int lo_quantize_row(int dtype, const float *x, void *blocks, int64_t k);
 /* Same over `rows` rows of k elements, rows split over nthreads (setup helper). */
 int lo_quantize_rows(int dtype, const float *x, void *blocks, int64_t rows, int64_t k, int nthreads);
+/* T::from_float_imatrix for one row (k = n_per_row; imatrix: k importance weights); -2 for types without one. */
+int lo_quantize_row_imatrix(int dtype, const float *x, void *blocks, int64_t k, const float *imatrix);
 /* T::to_float */
 int lo_dequantize_row(int dtype, const void *blocks, float *y, int64_t k);
 

@@ -53,6 +53,8 @@ def lib() -> C.CDLL:
         L.lo_f16_to_f32.argtypes = [C.c_uint16]
         L.lo_quantize_rows.restype = C.c_int
         L.lo_quantize_rows.argtypes = [C.c_int, vp, vp, i64, i64, C.c_int]
+        L.lo_quantize_row_imatrix.restype = C.c_int
+        L.lo_quantize_row_imatrix.argtypes = [C.c_int, vp, vp, i64, vp]
         L.lo_dequantize_row.restype = C.c_int
         L.lo_dequantize_row.argtypes = [C.c_int, vp, vp, i64]
         L.lo_vec_dot.restype = C.c_float
@@ -109,6 +111,22 @@ def quantize(dtype: int, x, nthreads: int = 1) -> np.ndarray:
     rc = lib().lo_quantize_rows(dtype, _ptr(x), _ptr(out), rows, k, nthreads)
     if rc != 0:
         raise ValueError(f"oracle quantize failed rc={rc} dtype={dtype} k={k}")
+    return out
+
+
+def quantize_imatrix(dtype: int, x, imatrix) -> np.ndarray:
+    """``T::from_float_imatrix`` over each row of ``x`` with one importance weight per column (``QTensor::quantize_imatrix``)."""
+    x = _f32(x)
+    if x.ndim == 1:
+        x = x[None, :]
+    imatrix = _f32(imatrix)
+    rows, k = x.shape
+    assert imatrix.shape == (k,)
+    out = np.zeros((rows, row_bytes(dtype, k)), dtype=np.uint8)
+    for r in range(rows):
+        rc = lib().lo_quantize_row_imatrix(dtype, _ptr(x[r]), _ptr(out[r]), k, _ptr(imatrix))
+        if rc != 0:
+            raise ValueError(f"oracle quantize_imatrix failed rc={rc} dtype={dtype} k={k}")
     return out
 
 

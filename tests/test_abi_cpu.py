@@ -141,3 +141,33 @@ def test_host_weight_quantizer_matches_oracle(cuda_lib, oracle, dt):
     i = np.arange(4096, dtype=np.float32)
     cosv = (np.float32(0.1) + np.float32(2.0) * np.cos(i)).astype(np.float32)[None, :]
     np.testing.assert_array_equal(quantize_weights_host(cosv, dt), oracle.quantize(dt, cosv))
+
+
+@pytest.mark.parametrize("dt", [12, 13, 14])
+def test_imatrix_quantizer(cuda_lib, oracle, dt):
+    """from_float_imatrix (k_quants.rs:1682, 1959, 2246): the host layer's blocks equal the oracle's byte for byte, and
+    the reference's own property holds (imatrix_quantize_q4k/q5k/q6k, quantized_tests.rs:571-690): with importance
+    weights accumulated from activations the mean absolute dequantization error does not exceed the plain quantizer's."""
+    import numpy as np
+
+    from lloom_b200.quantized import LloomError, quantize_weights_host
+
+    rng = np.random.default_rng(dt)
+    values, rows, ncall = np.zeros(768, np.float64), 0, 0
+    for _ in range(10):
+        res = rng.standard_normal((256, 512)).astype(np.float32) @ rng.standard_normal((512, 768)).astype(np.float32)
+        values += (res.astype(np.float64) ** 2).sum(0)
+        rows += res.shape[0]
+        ncall += 1
+    imatrix = (values / rows * ncall).astype(np.float32)
+    xs = rng.standard_normal((96, 768)).astype(np.float32)
+    xs[5] = 0.0
+    xs[7, :256] = 0.0
+    q_imat = quantize_weights_host(xs, dt, nthreads=3, imatrix=imatrix)
+    np.testing.assert_array_equal(q_imat, oracle.quantize_imatrix(dt, xs, imatrix))
+    q_plain = quantize_weights_host(xs, dt)
+    err_plain = np.abs(oracle.dequantize(dt, q_plain, 768) - xs).mean()
+    err_imat = np.abs(oracle.dequantize(dt, q_imat, 768) - xs).mean()
+    assert err_imat < err_plain, (err_imat, err_plain)
+    with pytest.raises(LloomError):  # Q8_0 has no from_float_imatrix in the reference either
+        quantize_weights_host(xs, 8, imatrix=imatrix)

@@ -569,3 +569,56 @@ def test_second_device_in_one_process(oracle):
         xt = torch.from_numpy(x).to(dv)
         outs.append((mm.forward(xt).cpu(), mm.forward(xt[:1]).cpu()))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("dt,n,k", [(12, 300, 1024), (14, 130, 512), (8, 257, 512), (13, 96, 2048), (12, 64, 14336)])
+def test_indexed_moe_forward(dev, oracle, dt, n, k):
+    """QTensor::indexed_moe_forward (mod.rs:1539-1650, cuda.rs:505-622): every (token, expert) product equals the plain
+    forward of that expert's matrix on that row bit for bit, matches the oracle within tolerance, and stays close to
+    the reference CPU arm's dequantize-and-dot (which does not quantize the activations)."""
+    import lloom_b200 as lb
+    from lloom_b200 import _lib
+    from lloom_b200 import quantized as Q
+
+    n_experts, batch, topk = 6, 3, 4
+    rng = np.random.default_rng(dt + n)
+    w = rng.standard_normal((n_experts, n, k)).astype(np.float32) * np.float32(0.02)
+    wq = oracle.quantize(dt, w.reshape(n_experts * n, k), nthreads=8)
+    rb = wq.shape[1]
+    stacked = lb.QTensor.from_data(wq.tobytes(), dt, (n_experts, n, k), dev)
+    experts = [lb.QMatMul.from_qtensor(lb.QTensor.from_data(wq[e * n:(e + 1) * n].tobytes(), dt, (n, k), dev)) for e in range(n_experts)]
+    ids_np = np.stack([rng.permutation(n_experts)[:topk] for _ in range(batch)]).astype(np.int64)
+    ids = torch.from_numpy(ids_np).to(dev)
+    for overlap in (0, 1):
+        prev = _lib.lib().lloom_b200_set_launch_overlap(overlap)
+        try:
+            for in_dim1 in (1, topk):
+                x_np = rng.standard_normal((batch, in_dim1, k)).astype(np.float32)
+                x = torch.from_numpy(x_np).to(dev)
+                got = stacked.indexed_moe_forward(x, ids)
+                assert tuple(got.shape) == (batch, topk, n)
+                got_np = got.cpu().numpy()
+                dense = oracle.dequantize(dt, wq, k).reshape(n_experts, n, k).astype(np.float64)
+                for b in range(batch):
+                    for t in range(topk):
+                        e = int(ids_np[b, t])
+                        xi = 0 if in_dim1 == 1 else t
+                        want = experts[e].forward(x[b, xi:xi + 1])
+                        assert torch.equal(got[b, t:t + 1], want), (dt, b, t, in_dim1)
+                        ref = oracle.matmul(dt, x_np[b, xi:xi + 1], wq[e * n:(e + 1) * n], n)
+                        absum = oracle.matmul_absum(dt, x_np[b, xi:xi + 1], wq[e * n:(e + 1) * n], n)
+                        assert_matmul_close(got_np[b, t:t + 1], ref, absum, f"moe {DT_NAMES[dt]} b={b} t={t}")
+                        cpu_arm = dense[e] @ x_np[b, xi].astype(np.float64)
+                        scale = np.abs(dense[e]) @ np.abs(x_np[b, xi].astype(np.float64))
+                        assert (np.abs(got_np[b, t] - cpu_arm) <= 2e-2 * scale).all()
+        finally:
+            _lib.lib().lloom_b200_set_launch_overlap(prev)
+    assert Q.device_status() == 0
+    # an expert id past the stack is clamped and reported through the status word
+    bad = ids.clone()
+    bad[0, 0] = n_experts + 3
+    stacked.indexed_moe_forward(torch.from_numpy(rng.standard_normal((batch, 1, k)).astype(np.float32)).to(dev), bad)
+    torch.cuda.synchronize()
+    assert Q.device_status() == _lib.ERR_SHAPE
+    with pytest.raises(lb.LloomError):
+        stacked.indexed_moe_forward(torch.zeros(batch, 2, k, device=dev), ids)
