@@ -19,7 +19,10 @@ from oracle import oracle as O  # noqa: E402
 CASES = [  # (dtype, n, k, m, seed)
     (O.Q8_0, 9, 256, 1, 11), (O.Q8_0, 65, 768, 3, 12), (O.Q8_0, 33, 2048, 8, 13),
     (O.Q4_K, 9, 256, 1, 21), (O.Q4_K, 65, 768, 3, 22), (O.Q4_K, 33, 2048, 8, 23), (O.Q4_K, 130, 512, 70, 24),
-    (O.Q6_K, 9, 256, 1, 31), (O.Q6_K, 65, 768, 3, 32), (O.Q6_K, 33, 2048, 8, 33),
+    (O.Q6_K, 9, 256, 1, 31), (O.Q6_K, 65, 768, 3, 32), (O.Q6_K, 33, 2048, 8, 33), (O.Q6_K, 130, 512, 70, 34),
+    (O.Q8_0, 130, 512, 70, 14),
+    (O.Q4_0, 9, 256, 1, 41), (O.Q4_0, 33, 2048, 8, 42), (O.Q5_0, 9, 256, 1, 51), (O.Q5_0, 33, 2048, 8, 52),
+    (O.Q5_K, 9, 256, 1, 61), (O.Q5_K, 65, 768, 3, 62), (O.Q5_K, 33, 2048, 8, 63),
 ]
 
 
