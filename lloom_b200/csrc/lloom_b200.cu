@@ -122,7 +122,12 @@ struct MmaPlan {
 
 static MmaPlan gemv_mma_plan(const DeviceInfo &di, int w_dtype, int64_t m, int64_t n, int64_t k) {
     MmaPlan pl;
-    if (w_dtype != LLOOM_Q4_K || m < 2 || m > 8) return pl;
+    if (w_dtype != LLOOM_Q4_K || m > 8) return pl;
+    // One row always runs on the dp4a kernel.  Back to back with itself this kernel (quantizer as prologue) is the
+    // faster one on long rows -- [4096, 14336] 10.9 against 12.5 us, [4096, 11008] 8.9 / 10.0 us, [14336, 5120] 10.9 /
+    // 12.7 us ([8192, 8192]: 12.0 / 10.5 us) -- but it fills an SM alone, so its neighbours in a decode step's chain of
+    // launches cannot start beside it: a 225-matmul step took 1.55 ms with it against 1.43 ms without.
+    if (m < 2) return pl;
     const int64_t nb = k / QK_K;
     const int64_t total = (n + kMmaTileRows - 1) / kMmaTileRows;
     const int64_t grid = total < di.sm_count ? total : di.sm_count;
@@ -134,10 +139,7 @@ static MmaPlan gemv_mma_plan(const DeviceInfo &di, int w_dtype, int64_t m, int64
         const int64_t pitch = bank_pitch(chunk * Q4K_BYTES, 8);
         const int64_t stage = (int64_t)kMmaTileRows * pitch;
         const int64_t room = (int64_t)di.max_smem_optin - kMmaBarBytes - kMmaRedBytes - bars - mma_act_bytes(m, k);
-        if (room >= 2 * stage) {
-            // (a single row stays on the dp4a kernel even at K = 14336, where this kernel alone would be faster --
-            // 11.8 us against 14.9 us: the quantizer launch in front of it breaks the chain of overlapping
-            // launches, and a 225-matmul decode step got 8 % slower with it)
+        if (room >= 2 * stage) {  // (asking for three or more stages of shorter pieces measured equal or slower)
             pl.ok = true;
             pl.chunk_sb = (int)chunk;
             pl.nchunks = (int)((nb + chunk - 1) / chunk);
@@ -324,9 +326,8 @@ static int gemv_launch(int w_dtype, const void *w, const void *act, const float 
             // that a stage is 16 (8) rows x one piece -- the tile the kernel streams at K = 4096 -- instead of giving
             // up the overlap between consecutive launches for a one-CTA-per-SM shape.
             if ((group && m != 1) || !shapes[si].half || cw > 8 || p.row_bytes % 16 != 0) continue;
-            const int cu = act_is_q8_0(w_dtype) ? 32 : 16;
+            const int cu = act_is_q8_0(w_dtype) ? 32 : 16, cl = act_is_q8_0(w_dtype) ? 5 : 4;
             if (units <= cu || ((int64_t)cu * p.unit_bytes) % 16 != 0) continue;
-            const int cl = act_is_q8_0(w_dtype) ? 5 : 4;
             const int64_t pstage = round16((int64_t)cw * (32 >> cl) * rw * cu * p.unit_bytes + pad);
             if (budget < 2 * pstage) continue;
             stage = pstage;
@@ -398,7 +399,9 @@ static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *
         DeviceInfo di;
         rc = device_info(di);
         if (rc != LLOOM_OK) return rc;
-        const bool mma = gemv_mma_fits(di, w_dtype, m, n, k);
+        // activations that an earlier fused gather delivers may only be read by the kernel that waits for that gather
+        const bool must_fuse = out && out->wait_flags;
+        const bool mma = gemv_mma_fits(di, w_dtype, m, n, k) && (!must_fuse || gemv_mma_fused(m, k));
         // up to two rows: one launch, the activation quantizer is the GEMV's prologue (the workspace stays
         // unused).  From three rows on, every CTA re-quantizing all rows costs more than one small kernel does.
         if ((m <= 2 && !mma) || (mma && gemv_mma_fused(m, k)))
@@ -671,7 +674,8 @@ int lloom_b200_qmatmul_fwd_group(int w_dtype, int n_mats, const void *const *w_b
     if (rc != LLOOM_OK) return rc;
     // One launch for the whole group where the dp4a kernel with its quantizer prologue is the decode path anyway
     // (one row; two rows of the formats without a tensor-core GEMV) and whole rows fit its stages.
-    const bool one_launch = n_mats > 1 && (m == 1 || (m == 2 && !gemv_mma_fits(di, w_dtype, m, n_max, k)));
+    // (where a forward of its own would take the tensor-core kernel, so does every matrix here: same bits either way)
+    const bool one_launch = n_mats > 1 && m <= 2 && !gemv_mma_fits(di, w_dtype, m, n_max, k);
     if (one_launch) {
         rc = gemv_launch(w_dtype, nullptr, nullptr, x, nullptr, m, 0, k, 0, (cudaStream_t)stream, false, nullptr, &group);
         if (rc != LLOOM_ERR_SHAPE) return rc;  // rows too long for whole-row stages: matrix by matrix below

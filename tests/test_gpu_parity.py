@@ -339,6 +339,28 @@ def test_q4k_long_rows(dev, oracle, n, m):
     assert run_fwd(dev, 12, np.ascontiguousarray(wq[half:]), n - half, k, x).tobytes() == np.ascontiguousarray(got[:, half:]).tobytes()
 
 
+@pytest.mark.parametrize("n,k", [(130, 11008), (257, 16384), (64, 5120), (100, 12288), (96, 20480), (48, 8192)])
+def test_q4k_single_row_long_k(dev, oracle, n, k):
+    """One activation row, K beyond 4096: the dp4a kernel cuts the rows into pieces of 16 superblocks (the last one
+    shorter where K is no multiple of 4096).  Oracle parity, the same bits from run to run, for a row shard, and
+    from a grouped launch."""
+    _, x, wq = make_case(oracle, 12, n, k, 1, seed=n + k)
+    ref = oracle.matmul(12, x, wq, n, nthreads=8)
+    absum = oracle.matmul_absum(12, x, wq, n, nthreads=8)
+    got = run_fwd(dev, 12, wq, n, k, x)
+    assert_matmul_close(got, ref, absum, f"Q4K single row n={n} k={k}")
+    assert run_fwd(dev, 12, wq, n, k, x).tobytes() == got.tobytes()
+    half = n // 2
+    assert run_fwd(dev, 12, np.ascontiguousarray(wq[half:]), n - half, k, x).tobytes() == np.ascontiguousarray(got[:, half:]).tobytes()
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+    mats = [lb.QMatMul.from_qtensor(lb.QTensor.from_data(w.tobytes(), 12, (w.shape[0], k), dev))
+            for w in (wq, np.ascontiguousarray(wq[half:]))]
+    outs = Q.forward_group(mats, torch.from_numpy(x).to(dev))
+    assert outs[0].cpu().numpy().tobytes() == got.tobytes()
+    assert outs[1].cpu().numpy().tobytes() == np.ascontiguousarray(got[:, half:]).tobytes()
+
+
 def test_gemm_q4k_prefill_config_m2048(dev, oracle):
     """C4 at M = 2048 (the size the prefill throughput is quoted on): oracle parity on a sample of rows and
     columns, every output finite, and the prebuilt weight image gives the same bits as the per-call expansion."""
