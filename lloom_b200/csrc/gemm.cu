@@ -12,8 +12,12 @@ LLOOM_TU_REGISTER()
 
 namespace {
 
-using CfgQ8_0 = PlanesCfg<32, 1>;
-using CfgQ6K = PlanesCfg<256, 2>;
+using CfgQ8_0 = PlanesCfg<32, 1, 128>;
+using CfgQ6K = PlanesCfg<256, 2, 256>;      // more than 128 activation rows
+using CfgQ6KSmall = PlanesCfg<256, 2, 128>;  // up to 128: a 256-row tile would fetch and multiply empty rows
+
+// activation rows per tile of the Q6_K GEMM for a call of m rows
+int q6k_bm(int64_t m) { return m <= 128 ? CfgQ6KSmall::kBM : CfgQ6K::kBM; }
 
 // Weight images of more than this are built and consumed slab by slab (whole 128-row tiles), so that the
 // caller's workspace stays bounded whatever the matrix (a Q6_K lm_head image is 2.1 GB).
@@ -49,8 +53,8 @@ int64_t image_bytes_for_rows(int w_dtype, int64_t rows, int64_t k) {
 int64_t act_image_bytes(int w_dtype, int64_t m, int64_t k) {
     switch (w_dtype) {
     case LLOOM_Q4_K: return gemm_act_layout(m, k).total;
-    case LLOOM_Q8_0: return planes_act_layout(m, k, 32).total;
-    case LLOOM_Q6_K: return planes_act_layout(m, k, 256).total;
+    case LLOOM_Q8_0: return planes_act_layout(m, k, 32, CfgQ8_0::kBM).total;
+    case LLOOM_Q6_K: return planes_act_layout(m, k, 256, q6k_bm(m)).total;
     }
     return 0;
 }
@@ -79,7 +83,7 @@ cudaError_t launch_planes(const PlanesParams &p, cudaStream_t stream) {
     static OnceSmem once;
     cudaError_t e = opt_in_smem(gemm_planes_kernel<Cfg>, once, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    gemm_planes_kernel<Cfg><<<(unsigned)(p.n_tiles * p.m_tiles), kPlanesThreads, Cfg::kSmemBytes, stream>>>(p);
+    gemm_planes_kernel<Cfg><<<(unsigned)(p.n_tiles * p.m_tiles), Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -89,7 +93,7 @@ bool gemm_supported(int w_dtype, int64_t m, int64_t k, int max_smem) {
     if (m <= 8) return false;
     switch (w_dtype) {
     case LLOOM_Q4_K: return k % 256 == 0 && kGemmSmemBytes <= max_smem;
-    case LLOOM_Q6_K: return k % 256 == 0 && CfgQ6K::kSmemBytes <= max_smem;
+    case LLOOM_Q6_K: return k % 256 == 0 && CfgQ6K::kSmemBytes <= max_smem && CfgQ6KSmall::kSmemBytes <= max_smem;
     case LLOOM_Q8_0: return k % 128 == 0 && CfgQ8_0::kSmemBytes <= max_smem;  // a pipeline stage is 128 of K
     }
     return false;
@@ -123,14 +127,17 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
                          int64_t n, int64_t k, int64_t ldy, void *scratch, cudaStream_t stream) {
     const uint8_t *w = (const uint8_t *)w_blocks;
     uint8_t *act_img = (uint8_t *)scratch;
-    const int64_t mt = gemm_m_tiles(m);
+    const int64_t mt = w_dtype == LLOOM_Q6_K ? (m + q6k_bm(m) - 1) / q6k_bm(m) : gemm_m_tiles(m);
     // activation side, once per call
     if (w_dtype == LLOOM_Q4_K) {
         gemm_prep_kernel<<<(unsigned)(mt * (k / 256) * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
     } else if (w_dtype == LLOOM_Q8_0) {
-        planes_prep_kernel<true><<<(unsigned)(mt * (k / 64)), 128, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
+        planes_prep_kernel<true, CfgQ8_0::kBM><<<(unsigned)(mt * (k / 64)), CfgQ8_0::kBM, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
     } else if (w_dtype == LLOOM_Q6_K) {
-        planes_prep_kernel<false><<<(unsigned)(mt * (k / 64)), 128, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
+        if (q6k_bm(m) == CfgQ6K::kBM)
+            planes_prep_kernel<false, CfgQ6K::kBM><<<(unsigned)(mt * (k / 64)), CfgQ6K::kBM, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
+        else
+            planes_prep_kernel<false, CfgQ6KSmall::kBM><<<(unsigned)(mt * (k / 64)), CfgQ6KSmall::kBM, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
     } else {
         return cudaErrorInvalidValue;
     }
@@ -188,7 +195,7 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
             } else {
                 p.scale_stride = Q6K_BYTES;
                 p.scale_off = 208;
-                e = launch_planes<CfgQ6K>(p, stream);
+                e = q6k_bm(m) == CfgQ6K::kBM ? launch_planes<CfgQ6K>(p, stream) : launch_planes<CfgQ6KSmall>(p, stream);
             }
         }
         if (e != cudaSuccess) return e;

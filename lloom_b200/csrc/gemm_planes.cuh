@@ -11,9 +11,12 @@
 //   Q6_K: v = sc_j * (q6 - 32) has up to 13 significant bits, so it is split v = hi + lo with lo = v mod 64 in
 //         [0, 63] and hi a multiple of 64 in [-4096, 4032]: both exact in f16.  The two planes multiply the same
 //         B = q8 codes and add into the same accumulator, which then holds S itself; one drain per 256 of K.
-// The kernel is the Q4_K GEMM's frame (gemm_q4k.cuh) with the drain group and the plane count as parameters:
-// 128 x 128 output tile per CTA; operands arrive as ready-made 128-byte-swizzled K-major images by bulk copies;
-// four 128-column accumulators in tensor memory, so the drain of group g overlaps the MMAs of g+1..g+3.
+// The kernel is the Q4_K GEMM's frame (gemm_q4k.cuh) with the drain group, the plane count and the activation rows
+// per tile (BM, the UMMA N) as parameters: 128 x BM output tile per CTA; operands arrive as ready-made
+// 128-byte-swizzled K-major images by bulk copies; 512 / BM accumulators in tensor memory, so the drain of group g
+// overlaps the MMAs of the following groups.  A tcgen05.mma of M = 128, K = 16 takes the same time for N = 128 and
+// N = 256, so BM = 256 doubles the tensor rate where the epilogue keeps up: Q6_K (one drain per 256 of K) runs at
+// BM = 256, Q8_0 (one drain per 32 of K, epilogue-bound) stays at 128.
 // Warp roles: 0-7 epilogue, 8 operand copies, 9 MMA issuer (one elected lane), 10 activation-scale copies.
 // All waits are bounded and abortable; tensor memory is released on every path.
 #pragma once
@@ -22,39 +25,43 @@
 
 namespace lloom {
 
-template <int GROUP_K, int PLANES>
+template <int GROUP_K, int PLANES, int BM>
 struct PlanesCfg {
     static constexpr int kGroupK = GROUP_K;            // K elements per accumulator drain
     static constexpr int kPlanes = PLANES;             // f16 images per weight element
+    static constexpr int kBM = BM;                     // activation rows per tile (UMMA N): 128 or 256
     static constexpr int kStageK = PLANES == 1 ? 128 : 64;  // K elements per pipeline stage
-    static constexpr int kStages = PLANES == 1 ? 3 : 4;
+    static constexpr int kStages = (PLANES == 1 || BM == 256) ? 3 : 4;
     static constexpr int kAtomsPerStage = kStageK / 64;
+    static constexpr int kBAtomBytes = BM * 64 * 2;    // B atom: BM rows x 64 of K
     static constexpr int kStageABytes = kAtomsPerStage * PLANES * kGemmAtomBytes;
-    static constexpr int kStageBBytes = kAtomsPerStage * kGemmAtomBytes;
-    static constexpr int kAccBufs = 4;
+    static constexpr int kStageBBytes = kAtomsPerStage * kBAtomBytes;
+    static constexpr int kAccBufs = 512 / BM;
+    static constexpr int kDaBytes = BM * 4;
+    // BM = 256: 128 running sums per epilogue thread; three whole warpgroups, so that the two epilogue warpgroups can
+    // take registers from the third (setmaxnreg)
+    static constexpr int kThreads = BM == 256 ? 384 : 352;  // 8 epilogue warps + operand copies + MMA issuer + scale copies
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int kOffA = 0;
     static constexpr int kOffB = kOffA + kStages * kStageABytes;
     static constexpr int kOffDa = kOffB + kStages * kStageBBytes;
-    static constexpr int kOffBars = kOffDa + kAccBufs * kGemmDaBytes;
+    static constexpr int kOffBars = kOffDa + kAccBufs * kDaBytes;
     static constexpr int kNumBars = 2 * kStages + 3 * kAccBufs;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 };
 
-constexpr int kPlanesThreads = 352;  // 8 epilogue warps + operand copies + MMA issuer + scale copies
-
-// Operand images: activation side [m-tile][k/64 atoms][16 KB] + scales [m-tile][k/GROUP_K][128] f32;
+// Operand images: activation side [m-tile][k/64 atoms][BM x 128 B] + scales [m-tile][k/GROUP_K][BM] f32;
 // weight side [n-tile][k/64 atoms][PLANES][16 KB].
 struct PlanesActLayout {
     int64_t bimg, dat, total;
 };
-__host__ __device__ inline PlanesActLayout planes_act_layout(int64_t m, int64_t k, int group_k) {
+__host__ __device__ inline PlanesActLayout planes_act_layout(int64_t m, int64_t k, int group_k, int bm) {
     PlanesActLayout s;
-    const int64_t mt = gemm_m_tiles(m);
+    const int64_t mt = (m + bm - 1) / bm;
     s.bimg = 0;
-    s.dat = mt * (k / 64) * kGemmAtomBytes;
-    s.total = (s.dat + mt * (k / group_k) * kGemmDaBytes + 1023) / 1024 * 1024;
+    s.dat = mt * (k / 64) * bm * 128;
+    s.total = (s.dat + mt * (k / group_k) * bm * 4 + 1023) / 1024 * 1024;
     return s;
 }
 __host__ __device__ inline int64_t planes_weight_bytes(int64_t n, int64_t k, int planes) {
@@ -67,17 +74,18 @@ __device__ __forceinline__ uint32_t f16x2_from_ints(int a, int b) {
 }
 
 // Canonical activation blocks -> B image + scale plane.  One CTA per (m-tile, 64-element atom of K), one thread
-// per token of the tile.  ACT_Q8_0: 34-byte Q8_0 blocks (f16 d, 32 codes); else 292-byte Q8_K blocks (f32 d, 256 codes).
-template <bool ACT_Q8_0>
-__global__ void __launch_bounds__(128) planes_prep_kernel(const uint8_t *__restrict__ act, int m, int k,
-                                                          uint8_t *__restrict__ scratch) {
+// per activation row of the tile (BM threads).  ACT_Q8_0: 34-byte Q8_0 blocks (f16 d, 32 codes); else 292-byte Q8_K
+// blocks (f32 d, 256 codes).
+template <bool ACT_Q8_0, int BM>
+__global__ void __launch_bounds__(BM) planes_prep_kernel(const uint8_t *__restrict__ act, int m, int k,
+                                                         uint8_t *__restrict__ scratch) {
     const int atoms = k / 64;
     const int mt = blockIdx.x / atoms, atom = blockIdx.x % atoms;
-    const int t = threadIdx.x, row = mt * kGemmBM + t;
+    const int t = threadIdx.x, row = mt * BM + t;
     const int group_k = ACT_Q8_0 ? 32 : 256;
-    const PlanesActLayout lay = planes_act_layout(m, k, group_k);
-    uint8_t *img = scratch + lay.bimg + ((int64_t)mt * atoms + atom) * kGemmAtomBytes;
-    float *dat = reinterpret_cast<float *>(scratch + lay.dat) + (int64_t)mt * (k / group_k) * 128;
+    const PlanesActLayout lay = planes_act_layout(m, k, group_k, BM);
+    uint8_t *img = scratch + lay.bimg + ((int64_t)mt * atoms + atom) * (BM * 128);
+    float *dat = reinterpret_cast<float *>(scratch + lay.dat) + (int64_t)mt * (k / group_k) * BM;
     int q[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) q[i] = 0;
@@ -87,7 +95,7 @@ __global__ void __launch_bounds__(128) planes_prep_kernel(const uint8_t *__restr
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const unsigned short *p16 = reinterpret_cast<const unsigned short *>(blk + h * Q8_0_BYTES);
-                dat[(atom * 2 + h) * 128 + t] = f16_bits_to_f32(p16[0]);
+                dat[(atom * 2 + h) * BM + t] = f16_bits_to_f32(p16[0]);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const unsigned short w = p16[1 + i];
@@ -97,7 +105,7 @@ __global__ void __launch_bounds__(128) planes_prep_kernel(const uint8_t *__restr
             }
         } else {
             const uint8_t *blk = act + ((int64_t)row * (k / 256) + (atom >> 2)) * Q8K_BYTES;  // 4-byte aligned
-            if ((atom & 3) == 0) dat[(atom >> 2) * 128 + t] = *reinterpret_cast<const float *>(blk);
+            if ((atom & 3) == 0) dat[(atom >> 2) * BM + t] = *reinterpret_cast<const float *>(blk);
             const uint32_t *p32 = reinterpret_cast<const uint32_t *>(blk + 4 + (atom & 3) * 64);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -108,10 +116,10 @@ __global__ void __launch_bounds__(128) planes_prep_kernel(const uint8_t *__restr
         }
     } else {
         if (ACT_Q8_0) {
-            dat[(atom * 2) * 128 + t] = 0.0f;
-            dat[(atom * 2 + 1) * 128 + t] = 0.0f;
+            dat[(atom * 2) * BM + t] = 0.0f;
+            dat[(atom * 2 + 1) * BM + t] = 0.0f;
         } else if ((atom & 3) == 0) {
-            dat[(atom >> 2) * 128 + t] = 0.0f;
+            dat[(atom >> 2) * BM + t] = 0.0f;
         }
     }
 #pragma unroll
@@ -231,7 +239,7 @@ struct PlanesParams {
 };
 
 template <class Cfg>
-__global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const PlanesParams p) {
+__global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const PlanesParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::kOffBars);
@@ -243,7 +251,7 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // m-tiles of one n-tile are neighbours in launch order, so the n-tile's A images are shared through L2
     const int mt = blockIdx.x % p.m_tiles, nt = blockIdx.x / p.m_tiles;
-    const int m0 = mt * kGemmBM;
+    const int m0 = mt * Cfg::kBM;
     const int64_t n0 = p.row0 + (int64_t)nt * kGemmBN;
     const int atoms = p.k / 64;
     const int ngroups = p.k / Cfg::kGroupK;
@@ -262,7 +270,7 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == kGemmEpiWarps + 1) {  // tensor memory: all 512 columns, four 128-column accumulators
+    if (warp == kGemmEpiWarps + 1) {  // tensor memory: all 512 columns, 512 / BM accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -272,17 +280,21 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // BM = 256, per scheduler: two epilogue warps of 216 registers and one other warp of 72.  One setmaxnreg per
+    // warpgroup, executed by all of its warps at the top of the branch that holds all of the warpgroup's code.
     if (warp < kGemmEpiWarps) {
         // ------------------------------ epilogue ------------------------------
-        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 64*(w/4)..
+        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns (BM/2)*(w/4)..
+        if (Cfg::kBM == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
+        constexpr int kCW = Cfg::kBM / 2;  // columns per warp
         const int q = warp & 3, half = warp >> 2;
         const int r = q * 32 + lane;  // row of the tile == TMEM lane
         const int64_t n = n0 + r;
         const bool row_ok = n < p.n_end;
         const uint8_t *wrow = p.w + (row_ok ? n : 0) * p.row_bytes + p.scale_off;
-        uint64_t out2[32];
+        uint64_t out2[kCW / 2];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) out2[j] = 0ull;
+        for (int j = 0; j < kCW / 2; ++j) out2[j] = 0ull;
         unsigned short hdr_next = row_ok ? __ldg(reinterpret_cast<const unsigned short *>(wrow)) : (unsigned short)0;
         bool ok = true;
         for (int g = 0; g < ngroups && ok; ++g) {
@@ -296,50 +308,57 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
             ok = mbar_wait_abortable<64>(&da_full[buf], par, abort_flag) && mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + half * 64);
-            uint32_t va[32], vb[32];
-            tmem_ld32(t_main, va);
-            tmem_ld32(t_main + 32, vb);
-            // the 64 activation scales of this warp's columns, as f32 pairs, times the weight scale: (d_a * d_w)
-            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + Cfg::kOffDa + buf * kGemmDaBytes + half * 256);
-            uint64_t d2[16];
+            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kBM + half * kCW);
+            // the activation scales of this warp's columns, as f32 pairs, times the weight scale: (d_a * d_w)
+            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + Cfg::kOffDa + buf * Cfg::kDaBytes + half * kCW * 4);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const ulonglong2 t = dap[j];
-                d2[2 * j] = mul_f32x2(t.x, dw2);
-                d2[2 * j + 1] = mul_f32x2(t.y, dw2);
+            for (int c = 0; c < kCW / 64; ++c) {  // 64 columns at a time: two loads in flight
+                uint32_t va[32], vb[32];
+                tmem_ld32(t_main + 64 * c, va);
+                tmem_ld32(t_main + 64 * c + 32, vb);
+                uint64_t d2[16];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const ulonglong2 t = dap[16 * c + j];
+                    d2[2 * j] = mul_f32x2(t.x, dw2);
+                    d2[2 * j + 1] = mul_f32x2(t.y, dw2);
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    out2[32 * c + j] = fma_f32x2(d2[j], (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[32 * c + j]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const ulonglong2 t = dap[16 * c + 8 + j];
+                    d2[2 * j] = mul_f32x2(t.x, dw2);
+                    d2[2 * j + 1] = mul_f32x2(t.y, dw2);
+                }
+                if (c == kCW / 64 - 1) {
+                    // everything this warp needs from tensor memory and from the scale tile is in registers now
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    out2[32 * c + 16 + j] = fma_f32x2(d2[j], (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[32 * c + 16 + j]);
             }
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                out2[j] = fma_f32x2(d2[j], (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[j]);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const ulonglong2 t = dap[8 + j];
-                d2[2 * j] = mul_f32x2(t.x, dw2);
-                d2[2 * j + 1] = mul_f32x2(t.y, dw2);
-            }
-            // everything this warp needs from tensor memory and from the scale tile is in registers now
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                out2[16 + j] = fma_f32x2(d2[j], (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[16 + j]);
         }
         if (ok && row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int mrow = m0 + half * 64 + 2 * j;
+            for (int j = 0; j < kCW / 2; ++j) {
+                const int mrow = m0 + half * kCW + 2 * j;
                 if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] & 0xffffffffu));
                 if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
             }
         }
-    } else if (warp == kGemmEpiWarps) {
+    } else {
+    if (Cfg::kBM == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
+    if (warp == kGemmEpiWarps) {
         // ------------------------------ operand tiles: bulk copies ------------------------------
         // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
         const uint8_t *aimg = p.w_img + (int64_t)nt * atoms * Cfg::kPlanes * kGemmAtomBytes;
-        const uint8_t *bimg = p.act_img + (int64_t)mt * atoms * kGemmAtomBytes;
+        const uint8_t *bimg = p.act_img + (int64_t)mt * atoms * Cfg::kBAtomBytes;
         bool ok = true;
         for (int it = 0; it < nstages && ok; ++it) {
             const int s = it % Cfg::kStages;
@@ -354,24 +373,24 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
         }
     } else if (warp == kGemmEpiWarps + 2) {
         // ------------------------------ activation scales of each drain group ------------------------------
-        const PlanesActLayout lay = planes_act_layout(p.m, p.k, Cfg::kGroupK);
-        const uint8_t *dat = p.act_img + lay.dat + (int64_t)mt * ngroups * kGemmDaBytes;
+        const PlanesActLayout lay = planes_act_layout(p.m, p.k, Cfg::kGroupK, Cfg::kBM);
+        const uint8_t *dat = p.act_img + lay.dat + (int64_t)mt * ngroups * Cfg::kDaBytes;
         bool ok = true;
         for (int g = 0; g < ngroups && ok; ++g) {
             const int buf = g % Cfg::kAccBufs;
             if (g >= Cfg::kAccBufs) ok = mbar_wait_abortable<32>(&acc_empty[buf], ((g / Cfg::kAccBufs) - 1) & 1, abort_flag);
             if (!ok) break;
             if (lane == 0) {
-                mbar_arrive_expect_tx(&da_full[buf], kGemmDaBytes);
-                bulk_g2s(smem + Cfg::kOffDa + buf * kGemmDaBytes, dat + (int64_t)g * kGemmDaBytes, kGemmDaBytes, &da_full[buf]);
+                mbar_arrive_expect_tx(&da_full[buf], Cfg::kDaBytes);
+                bulk_g2s(smem + Cfg::kOffDa + buf * Cfg::kDaBytes, dat + (int64_t)g * Cfg::kDaBytes, Cfg::kDaBytes, &da_full[buf]);
             }
             __syncwarp();
         }
     } else if (warp == kGemmEpiWarps + 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp walks the loop; lane 0 issues the MMAs and commits.
-        // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
-        const uint32_t idesc = (1u << 4) | ((uint32_t)(kGemmBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
+        // instruction descriptor: D = f32, A = B = f16, both K-major, N = BM, M = 128
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(Cfg::kBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
         constexpr int kStepsPerStage = Cfg::kStageK / 16;
         constexpr int kStepsPerGroup = Cfg::kGroupK / 16;
         bool ok = true;
@@ -393,8 +412,8 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
                     tc_fence_after();
                 }
                 if (lane == 0) {
-                    const uint32_t d_acc = tmem_base + (uint32_t)(buf * 128);
-                    const uint32_t boff = (uint32_t)((kk >> 2) * kGemmAtomBytes + (kk & 3) * 32);
+                    const uint32_t d_acc = tmem_base + (uint32_t)(buf * Cfg::kBM);
+                    const uint32_t boff = (uint32_t)((kk >> 2) * Cfg::kBAtomBytes + (kk & 3) * 32);
 #pragma unroll
                     for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
                         const uint32_t aoff = (uint32_t)(((kk >> 2) * Cfg::kPlanes + pl) * kGemmAtomBytes + (kk & 3) * 32);
@@ -409,6 +428,7 @@ __global__ void __launch_bounds__(kPlanesThreads, 1) gemm_planes_kernel(const Pl
             if (lane == 0) umma_commit(&empty[s]);
             __syncwarp();
         }
+    }
     }
     // ------------------------------ teardown ------------------------------
     tc_fence_before();

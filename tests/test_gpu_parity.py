@@ -434,10 +434,12 @@ def test_decode_stack_shapes_q4k(dev, oracle, n, k, m):
 
 @pytest.mark.parametrize("dt,n,k,m", [(8, 128, 128, 128), (8, 130, 256, 9), (8, 300, 1024, 64), (8, 8192, 2048, 512),
                                       (8, 77, 2048, 200), (14, 128, 256, 128), (14, 130, 512, 9), (14, 300, 1024, 64),
-                                      (14, 2004, 4096, 512), (14, 77, 2048, 200), (8, 64, 192, 40)])
+                                      (14, 2004, 4096, 512), (14, 77, 2048, 200), (8, 64, 192, 40),
+                                      (14, 2004, 4096, 100), (14, 300, 4096, 700), (14, 1100, 2048, 129)])
 def test_gemm_q8_0_q6k_tensor_core_path(dev, oracle, dt, n, k, m):
     """Prefill GEMM (m > 8) for Q8_0 and Q6_K on the tcgen05 kernel: ragged tiles in both directions, one to many
-    drain groups; (Q8_0 with k not a multiple of 128 runs as slabs of the GEMV)."""
+    drain groups, several CTAs at once; Q6_K with 128-row (m <= 128) and 256-row activation tiles; (Q8_0 with k not a
+    multiple of 128 runs as slabs of the GEMV)."""
     from lloom_b200 import quantized as Q
 
     _, x, wq = make_case(oracle, dt, n, k, m, seed=dt + n + k + m)
