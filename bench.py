@@ -541,6 +541,14 @@ def run_gpu(args):
         q.data_host = w3[i * N:(i + 1) * N]
     configs["J1_q6k_gemm_14336x4096"] = gemm_leg(q6_pool, Q6_K, N, K, (64, 512, 2048), 7, "J1 Q6_K GEMM", check_m=(64, 512))
     del q6_pool
+    # the three added formats on the same two frames (Q5_K: Q4_K's kernel; Q4_0 / Q5_0: Q8_0's), M = 512 and 2048
+    for dt, name, n_, k_ in ((13, "q5k", N, K), (2, "q4_0", n1, k1), (6, "q5_0", n1, k1)):
+        wx = S.quantized_matrix(20 + dt, n_, k_, dt)
+        qx = [lb.QTensor.from_data(wx, dt, (n_, k_), dev) for _ in range(2)]
+        for q in qx:
+            q.data_host = wx
+        configs[f"J1_{name}_gemm_{n_}x{k_}"] = gemm_leg(qx, dt, n_, k_, (512, 2048), 7, f"J1 {name} GEMM", check_m=(512,))
+        del qx, wx
 
     # ---- C5: decode matmul stack (32 layers + lm_head), M = 1 and 8, one CUDA graph per step ----
     configs["C5_decode_stack"] = stack_leg(args, torch, lb, Q, S, T, O, dev, hbm_peak, parity, rng, lm_head=(q3, w3))

@@ -120,8 +120,8 @@ int lloom_b200_gemv(int w_dtype, const void *w_blocks, const void *act_blocks, f
                     int64_t k, int64_t ldy, void *stream);
 
 /* Prefill GEMM, any m >= 1 (meant for m > 8): same result definition as the GEMV
- * (matmul m > 1 arm, k_quants.rs:2518-2585).  Q4_K, Q6_K and Q8_0 (k a multiple of 128) run on tcgen05 tensor
- * cores; other shapes fall to slabs of eight rows through the GEMV.
+ * (matmul m > 1 arm, k_quants.rs:2518-2585).  All six formats run on tcgen05 tensor cores (the 32-element-block
+ * formats Q8_0, Q4_0, Q5_0 for k a multiple of 128); other shapes fall to slabs of eight rows through the GEMV.
  * Replaces launch_mmq_gguf_* (ffi.rs:583).  `workspace`: lloom_b200_workspace_bytes minus the activation blocks
  * (passing a buffer of the full lloom_b200_workspace_bytes is always enough). */
 int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, float *y, int64_t m, int64_t n,

@@ -43,8 +43,11 @@ cudaError_t opt_in_smem(Kern kern, OnceSmem &st, int bytes) {
 
 int64_t image_bytes_for_rows(int w_dtype, int64_t rows, int64_t k) {
     switch (w_dtype) {
-    case LLOOM_Q4_K: return gemm_weight_layout(rows, k).total;
-    case LLOOM_Q8_0: return planes_weight_bytes(rows, k, 1);
+    case LLOOM_Q4_K:
+    case LLOOM_Q5_K: return gemm_weight_layout(rows, k).total;
+    case LLOOM_Q8_0:
+    case LLOOM_Q4_0:
+    case LLOOM_Q5_0: return planes_weight_bytes(rows, k, 1);
     case LLOOM_Q6_K: return planes_weight_bytes(rows, k, 2);
     }
     return 0;
@@ -52,8 +55,11 @@ int64_t image_bytes_for_rows(int w_dtype, int64_t rows, int64_t k) {
 
 int64_t act_image_bytes(int w_dtype, int64_t m, int64_t k) {
     switch (w_dtype) {
-    case LLOOM_Q4_K: return gemm_act_layout(m, k).total;
-    case LLOOM_Q8_0: return planes_act_layout(m, k, 32, CfgQ8_0::kBM).total;
+    case LLOOM_Q4_K:
+    case LLOOM_Q5_K: return gemm_act_layout(m, k).total;
+    case LLOOM_Q8_0:
+    case LLOOM_Q4_0:
+    case LLOOM_Q5_0: return planes_act_layout(m, k, 32, CfgQ8_0::kBM).total;
     case LLOOM_Q6_K: return planes_act_layout(m, k, 256, q6k_bm(m)).total;
     }
     return 0;
@@ -65,11 +71,20 @@ cudaError_t build_image(int w_dtype, const uint8_t *w, int64_t rows, int64_t k, 
     const int64_t nt = (rows + kGemmBN - 1) / kGemmBN;
     if (w_dtype == LLOOM_Q4_K) {
         static OnceSmem once;
-        cudaError_t e = opt_in_smem(gemm_expand_kernel, once, kExpandSmem);
+        cudaError_t e = opt_in_smem(gemm_expand_kernel<false>, once, kExpandSmem);
         if (e != cudaSuccess) return e;
-        gemm_expand_kernel<<<(unsigned)(nt * (k / 256)), 128, kExpandSmem, stream>>>(w, (int)rows, (int)k, image);
+        gemm_expand_kernel<false><<<(unsigned)(nt * (k / 256)), 128, kExpandSmem, stream>>>(w, (int)rows, (int)k, image);
+    } else if (w_dtype == LLOOM_Q5_K) {
+        static OnceSmem once;
+        cudaError_t e = opt_in_smem(gemm_expand_kernel<true>, once, kExpandSmem);
+        if (e != cudaSuccess) return e;
+        gemm_expand_kernel<true><<<(unsigned)(nt * (k / 256)), 128, kExpandSmem, stream>>>(w, (int)rows, (int)k, image);
     } else if (w_dtype == LLOOM_Q8_0) {
         planes_expand_q8_0_kernel<<<(unsigned)(nt * (k / 64)), 128, 0, stream>>>(w, 0, (int)rows, (int)k, image);
+    } else if (w_dtype == LLOOM_Q4_0) {
+        planes_expand_q4or5_0_kernel<false><<<(unsigned)(nt * (k / 64)), 128, 0, stream>>>(w, 0, (int)rows, (int)k, image);
+    } else if (w_dtype == LLOOM_Q5_0) {
+        planes_expand_q4or5_0_kernel<true><<<(unsigned)(nt * (k / 64)), 128, 0, stream>>>(w, 0, (int)rows, (int)k, image);
     } else if (w_dtype == LLOOM_Q6_K) {
         planes_expand_q6k_kernel<<<(unsigned)(nt * (k / 64)), 128, 0, stream>>>(w, 0, (int)rows, (int)k, image);
     } else {
@@ -92,9 +107,12 @@ cudaError_t launch_planes(const PlanesParams &p, cudaStream_t stream) {
 bool gemm_supported(int w_dtype, int64_t m, int64_t k, int max_smem) {
     if (m <= 8) return false;
     switch (w_dtype) {
-    case LLOOM_Q4_K: return k % 256 == 0 && kGemmSmemBytes <= max_smem;
+    case LLOOM_Q4_K:
+    case LLOOM_Q5_K: return k % 256 == 0 && kGemmSmemBytes <= max_smem;
     case LLOOM_Q6_K: return k % 256 == 0 && CfgQ6K::kSmemBytes <= max_smem && CfgQ6KSmall::kSmemBytes <= max_smem;
-    case LLOOM_Q8_0: return k % 128 == 0 && CfgQ8_0::kSmemBytes <= max_smem;  // a pipeline stage is 128 of K
+    case LLOOM_Q8_0:
+    case LLOOM_Q4_0:
+    case LLOOM_Q5_0: return k % 128 == 0 && CfgQ8_0::kSmemBytes <= max_smem;  // a pipeline stage is 128 of K
     }
     return false;
 }
@@ -129,9 +147,11 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
     uint8_t *act_img = (uint8_t *)scratch;
     const int64_t mt = w_dtype == LLOOM_Q6_K ? (m + q6k_bm(m) - 1) / q6k_bm(m) : gemm_m_tiles(m);
     // activation side, once per call
-    if (w_dtype == LLOOM_Q4_K) {
+    const bool q4k_frame = w_dtype == LLOOM_Q4_K || w_dtype == LLOOM_Q5_K;
+    const bool q8_0_frame = w_dtype == LLOOM_Q8_0 || w_dtype == LLOOM_Q4_0 || w_dtype == LLOOM_Q5_0;
+    if (q4k_frame) {
         gemm_prep_kernel<<<(unsigned)(mt * (k / 256) * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
-    } else if (w_dtype == LLOOM_Q8_0) {
+    } else if (q8_0_frame) {
         planes_prep_kernel<true, CfgQ8_0::kBM><<<(unsigned)(mt * (k / 64)), CfgQ8_0::kBM, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
     } else if (w_dtype == LLOOM_Q6_K) {
         if (q6k_bm(m) == CfgQ6K::kBM)
@@ -156,7 +176,7 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
             img = slab_img;
         }
         const int n_tiles = (int)((rows + kGemmBN - 1) / kGemmBN);
-        if (w_dtype == LLOOM_Q4_K) {
+        if (q4k_frame) {
             static OnceSmem once;
             e = opt_in_smem(gemm_q4k_kernel, once, kGemmSmemBytes);
             if (e != cudaSuccess) return e;
@@ -172,6 +192,7 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
             p.k = (int)k;
             p.n_tiles = n_tiles;
             p.m_tiles = (int)mt;
+            p.blk_bytes = (int)lloom_b200_block_bytes(w_dtype);
             gemm_q4k_kernel<<<(unsigned)(n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
             e = cudaGetLastError();
         } else {
@@ -188,8 +209,8 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
             p.k = (int)k;
             p.n_tiles = n_tiles;
             p.m_tiles = (int)mt;
-            if (w_dtype == LLOOM_Q8_0) {
-                p.scale_stride = Q8_0_BYTES;
+            if (q8_0_frame) {
+                p.scale_stride = (int)lloom_b200_block_bytes(w_dtype);  // the f16 scale opens every 32-element block
                 p.scale_off = 0;
                 e = launch_planes<CfgQ8_0>(p, stream);
             } else {

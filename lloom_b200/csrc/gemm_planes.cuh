@@ -1,4 +1,4 @@
-// Prefill GEMM for Q8_0 and Q6_K weights on tcgen05 tensor cores (sm_100a), exact-integer formulation.
+// Prefill GEMM for Q8_0, Q4_0, Q5_0 and Q6_K weights on tcgen05 tensor cores (sm_100a), exact-integer formulation.
 //
 //   Q8_0 x Q8_0 (k_quants.rs:800-818, avx.rs:71-87):     y[m,n] = sum over 32-element blocks b of (d_w[n,b]*d_a[m,b]) * dot32(q_w, q_a)
 //   Q6_K x Q8_K (k_quants.rs:2115-2172, avx.rs:131-216):  y[m,n] = sum over superblocks b of (d_a[m,b]*d_w[n,b]) * S,
@@ -8,6 +8,8 @@
 // The block sums are integer contractions, so they run on the tensor cores (kind::f16, f32 accumulators in tensor
 // memory) with every operand an integer that f16 represents exactly:
 //   Q8_0: A = q_w, B = q_a (|.| <= 127); one accumulator drain per 32 of K, where the two f16 block scales meet.
+//   Q4_0 / Q5_0 (k_quants.rs:320-392, 602-700; dotted with Q8_0 activations like Q8_0): the same with A = nibble - 8
+//         / (nibble | fifth bit << 4) - 16; only the weight image and the place of the block scale differ.
 //   Q6_K: v = sc_j * (q6 - 32) has up to 13 significant bits, so it is split v = hi + lo with lo = v mod 64 in
 //         [0, 63] and hi a multiple of 64 in [-4096, 4032]: both exact in f16.  The two planes multiply the same
 //         B = q8 codes and add into the same accumulator, which then holds S itself; one drain per 256 of K.
@@ -152,6 +154,53 @@ __global__ void __launch_bounds__(128) planes_expand_q8_0_kernel(const uint8_t *
                 const unsigned short v = __ldg(p16 + 1 + i);
                 q[h * 32 + 2 * i] = (int)(int8_t)(v & 0xff);
                 q[h * 32 + 2 * i + 1] = (int)(int8_t)(v >> 8);
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const uint4 out = make_uint4(f16x2_from_ints(q[8 * c], q[8 * c + 1]), f16x2_from_ints(q[8 * c + 2], q[8 * c + 3]),
+                                     f16x2_from_ints(q[8 * c + 4], q[8 * c + 5]), f16x2_from_ints(q[8 * c + 6], q[8 * c + 7]));
+        *reinterpret_cast<uint4 *>(img + sw128_offset(r, 8 * c)) = out;
+    }
+}
+
+// Q4_0 / Q5_0 weight blocks -> A image (one plane: nibble - 8, or (nibble | fifth bit << 4) - 16, as f16;
+// k_quants.rs:299-318, 578-600: low nibbles are elements 0..15 of a block, high nibbles 16..31).  Same grid as Q8_0.
+template <bool FIVE_BIT>
+__global__ void __launch_bounds__(128) planes_expand_q4or5_0_kernel(const uint8_t *__restrict__ w, int64_t row0, int n_end,
+                                                                    int k, uint8_t *__restrict__ image) {
+    constexpr int kBlk = FIVE_BIT ? Q5_0_BYTES : Q4_0_BYTES;
+    const int atoms = k / 64;
+    const int nt = blockIdx.x / atoms, atom = blockIdx.x % atoms;
+    const int r = threadIdx.x;
+    const int64_t row = row0 + (int64_t)nt * kGemmBN + r;
+    uint8_t *img = image + ((int64_t)nt * atoms + atom) * kGemmAtomBytes;
+    int q[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) q[i] = 0;
+    if (row < n_end) {
+        const uint8_t *blk = w + (row * (k / 32) + atom * 2) * kBlk;  // 2-byte aligned
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const unsigned short *p16 = reinterpret_cast<const unsigned short *>(blk + h * kBlk);
+            uint32_t bits = 0;
+            if (FIVE_BIT) bits = (uint32_t)__ldg(p16 + 1) | ((uint32_t)__ldg(p16 + 2) << 16);
+            const unsigned short *qs = p16 + (FIVE_BIT ? 3 : 1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // bytes 2i, 2i+1: elements 2i, 2i+1 (low nibbles) and 16 + 2i, 17 + 2i (high)
+                const unsigned short v = __ldg(qs + i);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int byte = (v >> (8 * j)) & 0xff, l = 2 * i + j;
+                    if (FIVE_BIT) {
+                        q[h * 32 + l] = ((byte & 0xF) | (int)(((bits >> l) & 1u) << 4)) - 16;
+                        q[h * 32 + 16 + l] = ((byte >> 4) | (int)(((bits >> (16 + l)) & 1u) << 4)) - 16;
+                    } else {
+                        q[h * 32 + l] = (byte & 0xF) - 8;
+                        q[h * 32 + 16 + l] = (byte >> 4) - 8;
+                    }
+                }
             }
         }
     }

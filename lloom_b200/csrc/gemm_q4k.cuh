@@ -148,9 +148,12 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
     }
 }
 
-// Q4_K weight blocks -> the GEMM's A images.  One CTA per (n-tile, superblock), one thread per weight row:
+// Q4_K / Q5_K weight blocks -> the GEMM's A images.  One CTA per (n-tile, superblock), one thread per weight row:
 // the 144-byte block becomes four 128-byte rows of f16 (sc_j * q, exact) in the four swizzle atoms of the
 // superblock, plus the 32-byte min row (m_j duplicated against the two 16-element bsums of sub-block j).
+// FIVE_BIT: Q5_K blocks (176 bytes: the same header, 32 bytes of fifth bits, then the nibbles; k_quants.rs:1778-2077):
+// the code is nibble + 16 * bit, sc_j * q <= 63 * 31 = 1953 is still exact in f16, everything else is Q4_K's.
+template <bool FIVE_BIT>
 __global__ void __launch_bounds__(128) gemm_expand_kernel(const uint8_t *__restrict__ w, int n, int k,
                                                           uint8_t *__restrict__ scratch) {
     // [4 atoms x 16 KB][min tile 4 KB]: assembled in shared memory, written out by two bulk stores
@@ -159,13 +162,20 @@ __global__ void __launch_bounds__(128) gemm_expand_kernel(const uint8_t *__restr
     const int nt = blockIdx.x / nb, b = blockIdx.x % nb;
     const GemmWeightLayout lay = gemm_weight_layout(n, k);
     const int r = threadIdx.x, row = nt * kGemmBN + r;
-    uint4 blk[9];
+    // blk[0]: header; blk[1..8]: the 128 nibble bytes; qh[0..1]: the 32 bytes of fifth bits (Q5_K)
+    uint4 blk[9], qh[2];
 #pragma unroll
     for (int i = 0; i < 9; ++i) blk[i] = make_uint4(0, 0, 0, 0);
+    qh[0] = qh[1] = make_uint4(0, 0, 0, 0);
     if (row < n) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(w + ((int64_t)row * nb + b) * Q4K_BYTES);
+        const uint4 *src = reinterpret_cast<const uint4 *>(w + ((int64_t)row * nb + b) * (FIVE_BIT ? Q5K_BYTES : Q4K_BYTES));
+        blk[0] = __ldg(src);
+        if (FIVE_BIT) {
+            qh[0] = __ldg(src + 1);
+            qh[1] = __ldg(src + 2);
+        }
 #pragma unroll
-        for (int i = 0; i < 9; ++i) blk[i] = __ldg(src + i);
+        for (int i = 1; i < 9; ++i) blk[i] = __ldg(src + i + (FIVE_BIT ? 2 : 0));
     }
     const uint4 hq = blk[0];
     // 6-bit scales / mins (utils.rs:50-60), four per word
@@ -187,8 +197,14 @@ __global__ void __launch_bounds__(128) gemm_expand_kernel(const uint8_t *__restr
         for (int c = 0; c < 8; ++c) {  // 16-byte chunk c of the row: k-elements 8c..8c+7 of the atom
             // chunks 0-3: low nibbles of bytes 8c..8c+7; chunks 4-7: high nibbles of bytes 8(c-4)..
             const uint32_t w0 = qw[2 * (c & 3)], w1 = qw[2 * (c & 3) + 1];
-            const uint32_t n0w = (c < 4) ? (w0 & 0x0f0f0f0fu) : ((w0 >> 4) & 0x0f0f0f0fu);
-            const uint32_t n1w = (c < 4) ? (w1 & 0x0f0f0f0fu) : ((w1 >> 4) & 0x0f0f0f0fu);
+            uint32_t n0w = (c < 4) ? (w0 & 0x0f0f0f0fu) : ((w0 >> 4) & 0x0f0f0f0fu);
+            uint32_t n1w = (c < 4) ? (w1 & 0x0f0f0f0fu) : ((w1 >> 4) & 0x0f0f0f0fu);
+            if (FIVE_BIT) {  // element l of sub-block 2g + (c >= 4) takes bit 2g + (c >= 4) of fifth-bit byte l
+                const uint32_t hw[8] = {qh[0].x, qh[0].y, qh[0].z, qh[0].w, qh[1].x, qh[1].y, qh[1].z, qh[1].w};
+                const int bit = 2 * g + (c >> 2);
+                n0w |= ((hw[2 * (c & 3)] >> bit) & 0x01010101u) << 4;
+                n1w |= ((hw[2 * (c & 3) + 1] >> bit) & 0x01010101u) << 4;
+            }
             const __half2 sc2 = (c < 4) ? s_lo : s_hi, cc2 = (c < 4) ? c_lo : c_hi;
             uint32_t h[4];
             h[0] = __byte_perm(n0w, 0x64646464u, 0x4140);
@@ -311,6 +327,7 @@ struct GemmParams {
     int m, n, k;
     int n_tiles;  // tiles along the weight rows
     int m_tiles;  // tiles along the activation rows
+    int blk_bytes;  // bytes of a weight block (144 for Q4_K, 176 for Q5_K): where the next superblock's d / dmin sit
 };
 
 // Pipeline barriers.  A stage (128 of K of both operands, 64 KB) has one "full" barrier, completed by the
@@ -376,7 +393,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             const int buf = b & 1;
             const uint32_t par = (b >> 1) & 1;
             const uint32_t hdr = hdr_next;
-            if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * Q4K_BYTES));
+            if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * p.blk_bytes));
             const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
             const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
             ok = mbar_wait_abortable<64>(&min_full[buf], par, abort_flag);

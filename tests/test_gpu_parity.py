@@ -435,11 +435,15 @@ def test_decode_stack_shapes_q4k(dev, oracle, n, k, m):
 @pytest.mark.parametrize("dt,n,k,m", [(8, 128, 128, 128), (8, 130, 256, 9), (8, 300, 1024, 64), (8, 8192, 2048, 512),
                                       (8, 77, 2048, 200), (14, 128, 256, 128), (14, 130, 512, 9), (14, 300, 1024, 64),
                                       (14, 2004, 4096, 512), (14, 77, 2048, 200), (8, 64, 192, 40),
-                                      (14, 2004, 4096, 100), (14, 300, 4096, 700), (14, 1100, 2048, 129)])
+                                      (14, 2004, 4096, 100), (14, 300, 4096, 700), (14, 1100, 2048, 129),
+                                      (13, 128, 256, 128), (13, 300, 1024, 64), (13, 2004, 4096, 200), (2, 130, 256, 9),
+                                      (2, 300, 1024, 64), (2, 1030, 2048, 200), (6, 130, 256, 9), (6, 300, 1024, 64),
+                                      (6, 1030, 2048, 200), (2, 64, 192, 40)])
 def test_gemm_q8_0_q6k_tensor_core_path(dev, oracle, dt, n, k, m):
-    """Prefill GEMM (m > 8) for Q8_0 and Q6_K on the tcgen05 kernel: ragged tiles in both directions, one to many
-    drain groups, several CTAs at once; Q6_K with 128-row (m <= 128) and 256-row activation tiles; (Q8_0 with k not a
-    multiple of 128 runs as slabs of the GEMV)."""
+    """Prefill GEMM (m > 8) on the tcgen05 kernels for the formats beside Q4_K -- Q8_0, Q4_0, Q5_0 (one frame), Q6_K,
+    Q5_K (Q4_K's frame): ragged tiles in both directions, one to many drain groups, several CTAs at once; Q6_K with
+    128-row (m <= 128) and 256-row activation tiles; (the 32-element-block formats with k not a multiple of 128 run as
+    slabs of the GEMV)."""
     from lloom_b200 import quantized as Q
 
     _, x, wq = make_case(oracle, dt, n, k, m, seed=dt + n + k + m)
@@ -451,7 +455,7 @@ def test_gemm_q8_0_q6k_tensor_core_path(dev, oracle, dt, n, k, m):
     assert Q.device_status() == 0
 
 
-@pytest.mark.parametrize("dt", [8, 12, 14])
+@pytest.mark.parametrize("dt", [8, 12, 14, 13, 2, 6])
 def test_prefill_image_same_bits(dev, oracle, dt):
     """A forward with the prebuilt weight image equals the per-call expansion bit for bit (m > 8), and decode batches
     ignore the image."""
