@@ -150,8 +150,9 @@ class ClockSampler:
 # CPU legs (the only places this file touches oracle/)
 # --------------------------------------------------------------------------------------------------
 
-CPU_THREADING_NOTE = ("the oracle's flat spin-then-park pthread pool stands in for the reference's two-level "
-                      "utils::BarrierPool; threads = physical cores, as default_num_threads does")
+CPU_THREADING_NOTE = ("the oracle's restatement of utils::BarrierPool (per-worker go / done slots, spin 10,000 then park, "
+                      "flat tree as the reference builds off macOS, the caller takes the last share); "
+                      "threads = physical cores, as default_num_threads does")
 
 
 def cpu_reference_rate(seconds_budget: float = 12.0, copies: int = 8):

@@ -1338,85 +1338,151 @@ static float vec_dot_absum(int w_dtype, int64_t k, const void *w, const void *ac
     return a;
 }
 
-/* ---- a small persistent thread pool (stands in for utils::BarrierPool,
- * lloom-tensor/src/utils.rs:43-307: workers spin briefly, then park; the caller
- * takes the last share itself) ---- */
+/* ---- BarrierPool (lloom-tensor/src/utils.rs:10-307): persistent workers, one 64-byte slot each with a `go`
+ * generation the parent release-stores and a `done` generation the worker release-stores; a two-level tree (main
+ * signals one leader per cluster, leaders signal their followers; completion reduces the same way) that is flat
+ * where the cluster size is unknown (utils.rs:94-103: every platform but macOS); workers spin 10,000 times on `go`,
+ * then park; main runs the last share itself and spins on the roots' `done` (utils.rs:233-275). ---- */
 typedef void (*lo_task_fn)(int tid, void *ctx);
 #define LO_MAX_THREADS 256
-static struct {
+#define LO_SPIN_LIMIT 10000
+struct lo_slot {
+    _Alignas(64) atomic_ulong go;
+    atomic_ulong done;
+    /* park / unpark with a token, like std::thread::park (an unpark before the park makes it return at once) */
     pthread_mutex_t mu;
-    pthread_cond_t wake, done_cv;
-    pthread_mutex_t run_mu; /* one dispatch at a time */
-    int n_workers;
-    atomic_ulong generation;
-    atomic_int pending;
+    pthread_cond_t cv;
+    int token;
+    int n_children;
+    int children[LO_MAX_THREADS / 2];
+};
+static struct {
+    pthread_mutex_t call_lock; /* serializes callers; guards everything below but the slots' atomics */
+    int n_workers;             /* workers of the current tree (threads started: n_started >= n_workers) */
+    int n_started;
+    size_t cluster_size;       /* 0 or 1: flat */
+    unsigned long gen;
     lo_task_fn fn;
     void *ctx;
-    int active; /* workers with tid < active take part */
+    int n_roots;
+    int roots[LO_MAX_THREADS];
     pthread_t th[LO_MAX_THREADS];
-} g_pool = {PTHREAD_MUTEX_INITIALIZER, PTHREAD_COND_INITIALIZER, PTHREAD_COND_INITIALIZER, PTHREAD_MUTEX_INITIALIZER,
-            0, 0, 0, 0, 0, 0, {0}};
+    struct lo_slot slots[LO_MAX_THREADS];
+} g_pool = {.call_lock = PTHREAD_MUTEX_INITIALIZER};
+
+static inline void lo_spin(void) {
+#ifdef LO_X86
+    __builtin_ia32_pause();
+#endif
+}
+static void lo_park(struct lo_slot *s) {
+    pthread_mutex_lock(&s->mu);
+    while (!s->token) pthread_cond_wait(&s->cv, &s->mu);
+    s->token = 0;
+    pthread_mutex_unlock(&s->mu);
+}
+static void lo_unpark(struct lo_slot *s) {
+    pthread_mutex_lock(&s->mu);
+    s->token = 1;
+    pthread_cond_signal(&s->cv);
+    pthread_mutex_unlock(&s->mu);
+}
+
+/* compute_tree (utils.rs:62-92): the first worker of each cluster leads it; the first cluster is main plus
+ * cluster_size - 1 workers, whose first worker stands in as leader for main */
+static void lo_build_tree(int n_workers, size_t cluster_size) {
+    for (int i = 0; i < n_workers; ++i) g_pool.slots[i].n_children = 0;
+    g_pool.n_roots = 0;
+    if (n_workers == 0 || cluster_size <= 1 || cluster_size >= (size_t)LO_MAX_THREADS) {
+        for (int i = 0; i < n_workers; ++i) g_pool.roots[g_pool.n_roots++] = i;
+        return;
+    }
+    int c0 = (int)cluster_size - 1 < n_workers ? (int)cluster_size - 1 : n_workers;
+    g_pool.roots[g_pool.n_roots++] = 0;
+    for (int f = 1; f < c0; ++f) g_pool.slots[0].children[g_pool.slots[0].n_children++] = f;
+    int next = c0;
+    while (next < n_workers) {
+        const int leader = next;
+        g_pool.roots[g_pool.n_roots++] = leader;
+        const int end = n_workers < next + (int)cluster_size ? n_workers : next + (int)cluster_size;
+        for (int f = leader + 1; f < end; ++f) g_pool.slots[leader].children[g_pool.slots[leader].n_children++] = f;
+        next = end;
+    }
+}
 
 static void *pool_worker(void *arg) {
-    int tid = (int)(intptr_t)arg;
-    unsigned long seen = 0;
+    const int tid = (int)(intptr_t)arg;
+    struct lo_slot *slot = &g_pool.slots[tid];
+    unsigned long gen = atomic_load_explicit(&slot->done, memory_order_acquire); /* the generation it was started in */
     for (;;) {
-        int spins = 0;
-        while (atomic_load_explicit(&g_pool.generation, memory_order_acquire) == seen) {
-            if (++spins < 20000) {
-#ifdef LO_X86
-                __builtin_ia32_pause();
-#endif
-                continue;
-            }
-            pthread_mutex_lock(&g_pool.mu);
-            while (atomic_load_explicit(&g_pool.generation, memory_order_acquire) == seen)
-                pthread_cond_wait(&g_pool.wake, &g_pool.mu);
-            pthread_mutex_unlock(&g_pool.mu);
+        unsigned spins = 0;
+        for (;;) { /* spin briefly, then park, waiting for the next work item */
+            const unsigned long g = atomic_load_explicit(&slot->go, memory_order_acquire);
+            if (g != gen) { gen = g; break; }
+            if (++spins < LO_SPIN_LIMIT) lo_spin();
+            else { lo_park(slot); spins = 0; }
         }
-        seen = atomic_load_explicit(&g_pool.generation, memory_order_acquire);
-        if (tid < g_pool.active) {
-            g_pool.fn(tid, g_pool.ctx);
-            if (atomic_fetch_sub_explicit(&g_pool.pending, 1, memory_order_acq_rel) == 1) {
-                pthread_mutex_lock(&g_pool.mu);
-                pthread_cond_signal(&g_pool.done_cv);
-                pthread_mutex_unlock(&g_pool.mu);
-            }
+        /* fan the work out to the children */
+        for (int c = 0; c < slot->n_children; ++c) {
+            struct lo_slot *ch = &g_pool.slots[slot->children[c]];
+            atomic_store_explicit(&ch->go, gen, memory_order_release);
+            lo_unpark(ch);
         }
+        g_pool.fn(tid, g_pool.ctx);
+        /* reduce: all children before the parent hears of it */
+        for (int c = 0; c < slot->n_children; ++c)
+            while (atomic_load_explicit(&g_pool.slots[slot->children[c]].done, memory_order_acquire) != gen) lo_spin();
+        atomic_store_explicit(&slot->done, gen, memory_order_release);
     }
     return 0;
 }
 
-/* runs fn(tid, ctx) for tid in 0..nthreads; the caller is tid nthreads-1 */
+/* cluster size of the tree (utils.rs:94-103 hard-codes 6 on macOS and "flat" elsewhere); 0 = flat.  Takes effect with
+ * the next lo_parallel call. */
+void lo_set_cluster_size(int cluster_size) {
+    pthread_mutex_lock(&g_pool.call_lock);
+    g_pool.cluster_size = cluster_size > 0 ? (size_t)cluster_size : 0;
+    g_pool.n_workers = -1; /* rebuild the tree */
+    pthread_mutex_unlock(&g_pool.call_lock);
+}
+
+/* BarrierPool::execute (utils.rs:233-275): runs fn(tid, ctx) for tid in 0..nthreads; workers are 0..nthreads-2, the
+ * caller takes part as the last tid */
 static void lo_parallel(int nthreads, lo_task_fn fn, void *ctx) {
     if (nthreads > LO_MAX_THREADS) nthreads = LO_MAX_THREADS;
     if (nthreads <= 1) { fn(0, ctx); return; }
-    pthread_mutex_lock(&g_pool.run_mu);
-    while (g_pool.n_workers < nthreads - 1) {
-        int tid = g_pool.n_workers;
+    pthread_mutex_lock(&g_pool.call_lock);
+    int want = nthreads - 1;
+    while (g_pool.n_started < want) {
+        const int tid = g_pool.n_started;
+        struct lo_slot *s = &g_pool.slots[tid];
+        atomic_store(&s->go, g_pool.gen);
+        atomic_store(&s->done, g_pool.gen);
+        pthread_mutex_init(&s->mu, 0);
+        pthread_cond_init(&s->cv, 0);
+        s->token = 0;
+        s->n_children = 0;
         if (pthread_create(&g_pool.th[tid], 0, pool_worker, (void *)(intptr_t)tid) != 0) break;
         pthread_detach(g_pool.th[tid]);
-        ++g_pool.n_workers;
+        ++g_pool.n_started;
     }
-    int workers = g_pool.n_workers < nthreads - 1 ? g_pool.n_workers : nthreads - 1;
+    if (want > g_pool.n_started) want = g_pool.n_started;
+    if (want != g_pool.n_workers) { /* all workers are idle here: nobody reads the tree */
+        lo_build_tree(want, g_pool.cluster_size);
+        g_pool.n_workers = want;
+    }
+    const unsigned long gen = ++g_pool.gen;
     g_pool.fn = fn;
     g_pool.ctx = ctx;
-    g_pool.active = workers;
-    atomic_store_explicit(&g_pool.pending, workers, memory_order_release);
-    pthread_mutex_lock(&g_pool.mu);
-    atomic_fetch_add_explicit(&g_pool.generation, 1, memory_order_acq_rel);
-    pthread_cond_broadcast(&g_pool.wake);
-    pthread_mutex_unlock(&g_pool.mu);
-    for (int t = workers; t < nthreads; ++t) fn(t, ctx); /* the caller's share (and any thread that could not start) */
-    int spins = 0;
-    while (atomic_load_explicit(&g_pool.pending, memory_order_acquire) > 0) {
-        if (++spins < 20000) continue;
-        pthread_mutex_lock(&g_pool.mu);
-        while (atomic_load_explicit(&g_pool.pending, memory_order_acquire) > 0)
-            pthread_cond_wait(&g_pool.done_cv, &g_pool.mu);
-        pthread_mutex_unlock(&g_pool.mu);
+    for (int r = 0; r < g_pool.n_roots; ++r) {
+        struct lo_slot *s = &g_pool.slots[g_pool.roots[r]];
+        atomic_store_explicit(&s->go, gen, memory_order_release);
+        lo_unpark(s);
     }
-    pthread_mutex_unlock(&g_pool.run_mu);
+    for (int t = want; t < nthreads; ++t) fn(t, ctx); /* main's share (and that of any thread that could not start) */
+    for (int r = 0; r < g_pool.n_roots; ++r)
+        while (atomic_load_explicit(&g_pool.slots[g_pool.roots[r]].done, memory_order_acquire) != gen) lo_spin();
+    pthread_mutex_unlock(&g_pool.call_lock);
 }
 
 /* ---- public entry points ---- */

@@ -68,6 +68,9 @@ int lo_matmul(int w_dtype, int64_t m, int64_t k, int64_t n, const float *lhs, co
 /* Same traversal, writing lo_vec_dot_absum per output element. */
 int lo_matmul_absum(int w_dtype, int64_t m, int64_t k, int64_t n, const float *lhs, const void *w,
                     float *dst, int nthreads);
+/* Cluster size of the thread pool's two-level tree (utils::BarrierPool, utils.rs:62-103): the reference hard-codes 6
+ * on macOS and a flat tree elsewhere; 0 or 1 = flat (the default).  Takes effect with the next threaded call. */
+void lo_set_cluster_size(int cluster_size);
 /* Activation quantizer only (what matmul does to lhs first). */
 int lo_quantize_act(int w_dtype, const float *lhs, void *act_blocks, int64_t m, int64_t k);
 

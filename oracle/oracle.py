@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
         L.lo_matmul_absum.argtypes = [C.c_int, i64, i64, i64, vp, vp, vp, C.c_int]
         L.lo_quantize_act.restype = C.c_int
         L.lo_quantize_act.argtypes = [C.c_int, vp, vp, i64, i64]
+        L.lo_set_cluster_size.restype = None
+        L.lo_set_cluster_size.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -179,6 +181,11 @@ def matmul(w_dtype: int, lhs, w_blocks: np.ndarray, n: int, order: int | None = 
     if rc != 0:
         raise ValueError(f"oracle matmul failed rc={rc}")
     return dst[: m * n].reshape(m, n) if dst_len is None else dst
+
+
+def set_cluster_size(cluster_size: int) -> None:
+    """Cluster size of the thread pool's two-level tree (utils::BarrierPool; 0 = flat, the reference's choice off macOS)."""
+    lib().lo_set_cluster_size(int(cluster_size))
 
 
 def matmul_absum(w_dtype: int, lhs, w_blocks: np.ndarray, n: int, nthreads: int = 1) -> np.ndarray:

@@ -250,3 +250,26 @@ def test_committed_fixtures_match_oracle(oracle):
         np.testing.assert_array_equal(oracle.quantize_act(dt, z[key + "_x"]), z[key + "_aq"])
         y = oracle.matmul(dt, z[key + "_x"], wq, n, order=oracle.ORDER_AVX2_EMU)
         assert y.tobytes() == z[key + "_y"].tobytes()
+
+
+def test_barrier_pool_tree_shapes_give_the_same_result():
+    """The oracle's thread pool restates utils::BarrierPool (utils.rs:10-307): flat (the reference's tree off macOS) and
+    two-level trees of several cluster sizes, growing and shrinking thread counts, many generations -- the matmul's
+    output does not depend on any of it."""
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(11)
+    n, k, m = 203, 512, 3
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    wq = O.quantize(12, w, nthreads=1)
+    want = O.matmul(12, x, wq, n, nthreads=1).tobytes()
+    try:
+        for cluster in (0, 2, 3, 6, 64):
+            O.set_cluster_size(cluster)
+            for nthreads in (2, 7, 16, 5, 1, 12):
+                for _ in range(20):
+                    assert O.matmul(12, x, wq, n, nthreads=nthreads).tobytes() == want, (cluster, nthreads)
+            assert O.quantize(12, w, nthreads=9).tobytes() == wq.tobytes()
+    finally:
+        O.set_cluster_size(0)
