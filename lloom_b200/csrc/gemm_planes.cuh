@@ -344,14 +344,33 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         uint64_t out2[kCW / 2];
 #pragma unroll
         for (int j = 0; j < kCW / 2; ++j) out2[j] = 0ull;
-        unsigned short hdr_next = row_ok ? __ldg(reinterpret_cast<const unsigned short *>(wrow)) : (unsigned short)0;
+        // the row's weight scales, a batch of groups at a time, the next batch in flight while this one is used: eight
+        // per batch where a drain every 32 of K is shorter than a trip to L2, one where a group is 256 of K
+        constexpr int kScaleBatch = Cfg::kGroupK >= 256 ? 1 : 8;
+        unsigned short hdr_cur[kScaleBatch], hdr_nxt[kScaleBatch];
+#pragma unroll
+        for (int i = 0; i < kScaleBatch; ++i) {
+            hdr_cur[i] = 0;
+            hdr_nxt[i] = (row_ok && i < ngroups) ? __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)i * p.scale_stride))
+                                                 : (unsigned short)0;
+        }
         bool ok = true;
         for (int g = 0; g < ngroups && ok; ++g) {
             const int buf = g % Cfg::kAccBufs;
             const uint32_t par = (g / Cfg::kAccBufs) & 1;
-            const unsigned short hdr = hdr_next;
-            if (g + 1 < ngroups && row_ok)
-                hdr_next = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)(g + 1) * p.scale_stride));
+            if (g % kScaleBatch == 0) {
+#pragma unroll
+                for (int i = 0; i < kScaleBatch; ++i) {
+                    hdr_cur[i] = hdr_nxt[i];
+                    const int gn = g + kScaleBatch + i;
+                    if (row_ok && gn < ngroups)
+                        hdr_nxt[i] = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)gn * p.scale_stride));
+                }
+            }
+            unsigned short hdr = hdr_cur[0];
+#pragma unroll
+            for (int i = 1; i < kScaleBatch; ++i)
+                if (g % kScaleBatch == i) hdr = hdr_cur[i];
             const float dw = f16_bits_to_f32(hdr);
             const uint64_t dw2 = pack2f(dw, dw);
             ok = mbar_wait_abortable<64>(&da_full[buf], par, abort_flag) && mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
