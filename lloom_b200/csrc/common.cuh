@@ -70,6 +70,14 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Makes `v` a value the compiler must have computed at this point of the program (no instruction of its own).  Used
+// before a shared-memory stage is handed back to the bulk-copy engine: when every running sum the stage's loads feed
+// has been computed, those loads have returned -- the hardware only issues an instruction whose operands have arrived,
+// and issues in program order -- so the release that follows cannot overtake them.  (A consumer that released a
+// buffer while a load from it was still in flight read the next copy's bytes: seen in the GEMM epilogue, whose
+// scale-tile reads are therefore fenced with fence.proxy.async.)
+__device__ __forceinline__ void pin_value(float &v) { asm volatile("" : "+f"(v)); }
+__device__ __forceinline__ void pin_value(int &v) { asm volatile("" : "+r"(v)); }
 
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");

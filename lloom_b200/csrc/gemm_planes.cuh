@@ -402,8 +402,11 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
                     d2[2 * j + 1] = mul_f32x2(t.y, dw2);
                 }
                 if (c == kCW / 64 - 1) {
-                    // everything this warp needs from tensor memory and from the scale tile is in registers now
+                    // everything this warp needs from tensor memory and from the scale tile is in registers now; the
+                    // scale tile is rewritten by a bulk copy (async proxy) right after the arrivals, so this warp's
+                    // reads of it (generic proxy) are fenced first
                     tc_fence_before();
+                    fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }

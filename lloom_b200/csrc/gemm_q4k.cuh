@@ -432,8 +432,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             for (int j = 0; j < 16; ++j)
                 out2[16 + j] = fma_f32x2(mul_f32x2(da2[16 + j], dw2), (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[16 + j]);
             tmem_ld_wait();
-            // everything this warp needs from tensor memory and from the scale tile is in registers now
+            // everything this warp needs from tensor memory and from the scale tile is in registers now; the tile is
+            // rewritten by a bulk copy (async proxy) after the arrivals, so this warp's reads of it are fenced first
             tc_fence_before();
+            fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
 #pragma unroll

@@ -914,7 +914,13 @@ __global__ void __launch_bounds__(32 * (CW + 1), RW == 1 ? 2 : 1) gemv_kernel(co
                         }
                     }
                 }
-                // this warp is done reading the stage
+                // this warp is done reading the stage once every sum its loads feed has been computed
+#pragma unroll
+                for (int pass = 0; pass < NPASS; ++pass)
+#pragma unroll
+                    for (int r = 0; r < RW; ++r)
+#pragma unroll
+                        for (int m = 0; m < MC; ++m) pin_value(accs[pass][r][m]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
             }

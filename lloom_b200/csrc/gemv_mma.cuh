@@ -300,7 +300,9 @@ __global__ void __launch_bounds__(32 * (kMmaWarps + 1), 1) gemv_mma_q4k_kernel(c
             out[3] = fmaf(__fmul_rn(da1, dwb), (float)S[3], out[3]);
             out[3] = fmaf(__fmul_rn(-da1, dmb), (float)(ml[3] + 64 * mh[3]), out[3]);
         }
-        // this warp is done reading the stage
+        // this warp is done reading the stage once the sums its loads feed have been computed
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pin_value(out[i]);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
         }  // chunks
