@@ -193,7 +193,7 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
             p.n_tiles = n_tiles;
             p.m_tiles = (int)mt;
             p.blk_bytes = (int)lloom_b200_block_bytes(w_dtype);
-            gemm_q4k_kernel<<<(unsigned)(n_tiles * mt), kGemmThreads, kGemmSmemBytes, stream>>>(p);
+            gemm_q4k_kernel<<<(unsigned)(n_tiles * mt), kQ4kThreads, kGemmSmemBytes, stream>>>(p);
             e = cudaGetLastError();
         } else {
             PlanesParams p;

@@ -22,10 +22,10 @@
 //                        re-unpacking its 128 weight rows on CUDA cores beside the MMAs
 //   gemm_q4k_kernel      one CTA per 128 x 128 output tile; all operands arrive as ready-made shared-memory
 //                        images (128-byte-swizzled K-major UMMA layout) by bulk copies.  Warp roles:
-//                          warps 0-7  epilogue: tcgen05.ld -> f32x2 FMAs; warp w reads TMEM lanes 32*(w%4)..,
-//                                     columns 64*(w/4)..
-//                          warp 8     bulk-copy (TMA engine) producer
-//                          warp 9     MMA issuer (one elected lane): 8 x tcgen05.mma.kind::f16 (K = 16) per stage
+//                          warps 0-15 epilogue: tcgen05.ld -> f32x2 FMAs; warp w reads TMEM lanes 32*(w%4)..,
+//                                     columns 32*(w/4)..
+//                          warp 16    bulk-copy (TMA engine) producer
+//                          warp 17    MMA issuer (one elected lane): 8 x tcgen05.mma.kind::f16 (K = 16) per stage
 // All mbarrier waits are bounded and abortable; on a time-out the status word is set, every role
 // leaves its loop, and tensor memory is still released.
 #pragma once
@@ -43,8 +43,12 @@ constexpr int kGemmStageBytes = 2 * kGemmAtomBytes;  // a pipeline stage covers 
 constexpr int kGemmMinBytes = 128 * 16 * 2;    // min-term operand tile (K = 16), f16
 constexpr int kGemmDaBytes = 128 * 4;
 constexpr int kGemmStages = 3;
-constexpr int kGemmThreads = 320;  // 8 epilogue warps + bulk-copy warp + MMA warp
+constexpr int kGemmThreads = 320;  // 8 epilogue warps + bulk-copy warp + MMA warp (plane GEMMs)
 constexpr int kGemmEpiWarps = 8;
+// Q4_K kernel: sixteen epilogue warps (four per tensor-memory lane quarter, 32 accumulator columns each): with S and Mn
+// to drain per superblock, eight warps at two per scheduler left part of the drain exposed
+constexpr int kQ4kEpiWarps = 16;
+constexpr int kQ4kThreads = 32 * (kQ4kEpiWarps + 2);
 
 // ---- shared memory map (offsets from a 1024-byte aligned base) ----
 constexpr int kOffA = 0;
@@ -278,6 +282,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
           "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
@@ -336,7 +348,7 @@ struct GemmParams {
 // stage.  Per superblock parity (two of each): min_full (min tiles + activation scales landed), acc_full
 // (commit after the superblock's last MMA: accumulators ready, min tiles free), acc_empty (the eight
 // epilogue warps have read the accumulators out of tensor memory and hold the scales in registers).
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBars);
@@ -361,12 +373,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
         for (int i = 0; i < 2; ++i) {
             mbar_init(&min_full[i], 1);
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], kGemmEpiWarps);
+            mbar_init(&acc_empty[i], kQ4kEpiWarps);
         }
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == kGemmEpiWarps + 1) {  // tensor memory: all 512 columns, two (S, Mn) accumulator pairs
+    if (warp == kQ4kEpiWarps + 1) {  // tensor memory: all 512 columns, two (S, Mn) accumulator pairs
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -376,17 +388,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < kGemmEpiWarps) {
+    if (warp < kQ4kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
-        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 64*(w/4)..
-        const int q = warp & 3, half = warp >> 2;
+        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 32*(w/4)..
+        const int q = warp & 3, part = warp >> 2;
         const int r = q * 32 + lane;  // row of the tile == TMEM lane
         const int n = n0 + r;
         const bool row_ok = n < p.n;
         const uint8_t *wrow = p.w + (int64_t)(row_ok ? n : 0) * p.row_bytes;
-        uint64_t out2[32];
+        uint64_t out2[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) out2[j] = 0ull;
+        for (int j = 0; j < 16; ++j) out2[j] = 0ull;
         uint32_t hdr_next = row_ok ? __ldg(reinterpret_cast<const uint32_t *>(wrow)) : 0u;
         bool ok = true;
         for (int b = 0; b < nb && ok; ++b) {
@@ -398,59 +410,52 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
             ok = mbar_wait_abortable<64>(&min_full[buf], par, abort_flag);
             if (!ok) break;
-            // the 64 activation scales of this warp's columns, as f32 pairs
-            uint64_t da2[32];
-            {
-                const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + kOffDa + buf * kGemmDaBytes + half * 256);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const ulonglong2 t = dap[j];
-                    da2[2 * j] = t.x;
-                    da2[2 * j + 1] = t.y;
-                }
-            }
+            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + kOffDa + buf * kGemmDaBytes + part * 128);
             ok = mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + half * 64);
-            uint32_t va[32], vb[32];
-            // loads run one chunk ahead of the FMAs: S0 | Mn0 | S1 | Mn1
-            tmem_ld32(t_main, va);
+            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + part * 32);
+            // two halves of 16 columns: S and Mn of a half are loaded together, the next half's loads run under this half's FMAs
+            uint32_t va[2][16], vb[2][16];
+            tmem_ld16(t_main, va[0]);
+            tmem_ld16(t_main + 128, vb[0]);
             tmem_ld_wait();
-            tmem_ld32(t_main + 128, vb);
+            tmem_ld16(t_main + 16, va[1]);
+            tmem_ld16(t_main + 128 + 16, vb[1]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                out2[j] = fma_f32x2(mul_f32x2(da2[j], dw2), (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[j]);
-            tmem_ld_wait();
-            tmem_ld32(t_main + 32, va);
+            for (int h = 0; h < 2; ++h) {
+                if (h == 1) {
+                    tmem_ld_wait();
+                    // everything this warp needs from tensor memory is in registers now
+                    tc_fence_before();
+                }
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                out2[j] = fma_f32x2(mul_f32x2(da2[j], ndmin2), (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[j]);
-            tmem_ld_wait();
-            tmem_ld32(t_main + 128 + 32, vb);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                out2[16 + j] = fma_f32x2(mul_f32x2(da2[16 + j], dw2), (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[16 + j]);
-            tmem_ld_wait();
-            // everything this warp needs from tensor memory and from the scale tile is in registers now; the tile is
-            // rewritten by a bulk copy (async proxy) after the arrivals, so this warp's reads of it are fenced first
-            tc_fence_before();
+                for (int j = 0; j < 4; ++j) {
+                    const ulonglong2 t = dap[4 * h + j];
+                    const uint32_t *a = va[h] + 4 * j, *m = vb[h] + 4 * j;
+                    uint64_t o = out2[8 * h + 2 * j];
+                    o = fma_f32x2(mul_f32x2(t.x, dw2), (uint64_t)a[0] | ((uint64_t)a[1] << 32), o);
+                    out2[8 * h + 2 * j] = fma_f32x2(mul_f32x2(t.x, ndmin2), (uint64_t)m[0] | ((uint64_t)m[1] << 32), o);
+                    o = out2[8 * h + 2 * j + 1];
+                    o = fma_f32x2(mul_f32x2(t.y, dw2), (uint64_t)a[2] | ((uint64_t)a[3] << 32), o);
+                    out2[8 * h + 2 * j + 1] = fma_f32x2(mul_f32x2(t.y, ndmin2), (uint64_t)m[2] | ((uint64_t)m[3] << 32), o);
+                }
+            }
+            // the scale tile is rewritten by a bulk copy (async proxy) after the arrivals, so this warp's reads of it
+            // (generic proxy) are fenced first
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                out2[16 + j] = fma_f32x2(mul_f32x2(da2[16 + j], ndmin2), (uint64_t)vb[2 * j] | ((uint64_t)vb[2 * j + 1] << 32), out2[16 + j]);
         }
         if (ok && row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int mrow = m0 + half * 64 + 2 * j;
+            for (int j = 0; j < 16; ++j) {
+                const int mrow = m0 + part * 32 + 2 * j;
                 if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] & 0xffffffffu));
                 if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
             }
         }
-    } else if (warp == kGemmEpiWarps) {
+    } else if (warp == kQ4kEpiWarps) {
         // ------------------------------ operand tiles: bulk copies ------------------------------
         // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
         const uint8_t *aimg = p.w_img + wlay.aimg + (int64_t)nt * (p.k / 64) * kGemmAtomBytes;
@@ -486,7 +491,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
             }
             __syncwarp();
         }
-    } else if (warp == kGemmEpiWarps + 1) {
+    } else if (warp == kQ4kEpiWarps + 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp walks the loop; lane 0 issues the MMAs and commits.
         // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
@@ -533,7 +538,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q4k_kernel(const GemmPar
     // ------------------------------ teardown ------------------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == kGemmEpiWarps + 1) {
+    if (warp == kQ4kEpiWarps + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
