@@ -141,15 +141,20 @@ cudaError_t gemm_weight_image_build(int w_dtype, const void *w, int64_t n, int64
     return build_image(w_dtype, (const uint8_t *)w, n, k, (uint8_t *)image, stream);
 }
 
-cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image, const void *act, float *y, int64_t m,
-                         int64_t n, int64_t k, int64_t ldy, void *scratch, cudaStream_t stream) {
+bool gemm_takes_f32(int w_dtype) { return w_dtype == LLOOM_Q4_K || w_dtype == LLOOM_Q5_K; }
+
+cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image, const void *act, const float *x, float *y,
+                         int64_t m, int64_t n, int64_t k, int64_t ldy, void *scratch, cudaStream_t stream) {
+    if ((act == nullptr) == (x == nullptr) || (x && !gemm_takes_f32(w_dtype))) return cudaErrorInvalidValue;
     const uint8_t *w = (const uint8_t *)w_blocks;
     uint8_t *act_img = (uint8_t *)scratch;
     const int64_t mt = w_dtype == LLOOM_Q6_K ? (m + q6k_bm(m) - 1) / q6k_bm(m) : gemm_m_tiles(m);
     // activation side, once per call
     const bool q4k_frame = w_dtype == LLOOM_Q4_K || w_dtype == LLOOM_Q5_K;
     const bool q8_0_frame = w_dtype == LLOOM_Q8_0 || w_dtype == LLOOM_Q4_0 || w_dtype == LLOOM_Q5_0;
-    if (q4k_frame) {
+    if (q4k_frame && x) {
+        gemm_prep_f32_kernel<<<(unsigned)(mt * kGemmBM * (k / 256) / 8), 256, 0, stream>>>(x, (int)m, (int)k, act_img);
+    } else if (q4k_frame) {
         gemm_prep_kernel<<<(unsigned)(mt * (k / 256) * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
     } else if (q8_0_frame) {
         planes_prep_kernel<true, CfgQ8_0::kBM><<<(unsigned)(mt * (k / 64)), CfgQ8_0::kBM, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);

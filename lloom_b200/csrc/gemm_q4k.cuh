@@ -33,6 +33,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "quantize_act.cuh"
 
 namespace lloom {
 
@@ -150,6 +151,51 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const uint8_t *__restric
         const int row = mt * kGemmBM + t;
         dat[t] = row < m ? *reinterpret_cast<const float *>(act + ((int64_t)row * nb + b) * Q8K_BYTES) : 0.0f;
     }
+}
+
+// f32 activations -> the same operand images in one pass (the forward entries: no canonical blocks in between).  One
+// warp per (activation row, superblock): BlockQ8K::from_float by the warp function every other kernel uses (so the
+// codes, sums and scale are those of the canonical block), lane l holding elements 8l..8l+7, i.e. exactly one 16-byte
+// chunk of the B image.
+__global__ void __launch_bounds__(256) gemm_prep_f32_kernel(const float *__restrict__ x, int m, int k, uint8_t *__restrict__ scratch) {
+    const int nb = k / 256;
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (padded row, superblock)
+    const int64_t prow = item / nb;
+    const int b = (int)(item % nb);
+    const int64_t mt = prow / kGemmBM;
+    const int t = (int)(prow % kGemmBM);
+    if (mt >= gemm_m_tiles(m)) return;  // whole warp
+    const GemmActLayout lay = gemm_act_layout(m, k);
+    uint8_t *bimg = scratch + lay.bimg + (mt * (k / 64) + (int64_t)b * 4) * kGemmAtomBytes;
+    uint8_t *minb = scratch + lay.minb + (mt * nb + b) * kGemmMinBytes;
+    float *dat = reinterpret_cast<float *>(scratch + lay.dat) + (mt * nb + b) * 128;
+    uint32_t q_lo = 0, q_hi = 0;
+    float d = 0.0f;
+    int sum16 = 0;
+    if (prow < m) {  // rows of the last tile past m stay zero
+        float v[8];
+        load8(x + prow * k + (int64_t)b * 256 + lane * 8, v);
+        q8k_quantize_warp(v, lane, q_lo, q_hi, d, sum16);
+    }
+    auto cvt2 = [](uint32_t w, int sh) -> uint32_t {
+        const __half2 h = __floats2half2_rn((float)(int)(int8_t)(w >> sh), (float)(int)(int8_t)(w >> (sh + 8)));
+        return *reinterpret_cast<const uint32_t *>(&h);
+    };
+    const int ks = lane >> 3, e = (lane & 7) * 8;
+    *reinterpret_cast<uint4 *>(bimg + (int64_t)ks * kGemmAtomBytes + sw128_offset(t, e)) =
+        make_uint4(cvt2(q_lo, 0), cvt2(q_lo, 16), cvt2(q_hi, 0), cvt2(q_hi, 16));
+    // the 16 bsums sit on lane pairs (group j on lanes 2j, 2j+1); lanes 0 and 1 collect eight each
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j0 = 8 * (lane & 1) + 2 * i;
+        const int s0 = __shfl_sync(0xffffffffu, sum16, 2 * j0), s1 = __shfl_sync(0xffffffffu, sum16, 2 * (j0 + 1));
+        const __half2 h = __floats2half2_rn((float)s0, (float)s1);
+        w[i] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    if (lane < 2) *reinterpret_cast<uint4 *>(minb + min_tile_offset(t, lane * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+    if (lane == 0) dat[t] = d;
 }
 
 // Q4_K / Q5_K weight blocks -> the GEMM's A images.  One CTA per (n-tile, superblock), one thread per weight row:

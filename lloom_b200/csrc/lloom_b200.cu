@@ -420,14 +420,24 @@ static int decode_fwd(int w_dtype, const void *w_blocks, const float *x, float *
     return gemv_launch(w_dtype, w_blocks, workspace, nullptr, y, m, n, k, ldy, (cudaStream_t)stream, false, out);
 }
 
-// Prefill forward (m > 8) after argument checks: canonical activation blocks are in `act`; `scratch` follows them.
-static int gemm_dispatch(int w_dtype, const void *w_blocks, const void *w_image, const void *act, float *y, int64_t m,
-                         int64_t n, int64_t k, int64_t ldy, void *scratch, void *stream) {
+// Prefill forward (m > 8) after argument checks.  Activations: canonical blocks in `act`, or f32 in `x` with `act_ws` the
+// place to quantize them to where a kernel needs canonical blocks (the Q4_K / Q5_K GEMM takes the f32 itself).
+// `scratch` follows the activation blocks in the caller's workspace.
+static int gemm_dispatch(int w_dtype, const void *w_blocks, const void *w_image, const void *act, const float *x, void *act_ws,
+                         float *y, int64_t m, int64_t n, int64_t k, int64_t ldy, void *scratch, void *stream) {
     DeviceInfo di;
     int rc = device_info(di);
     if (rc != LLOOM_OK) return rc;
-    if (gemm_supported(w_dtype, m, k, di.max_smem_optin))
-        return launch_status(gemm_forward(w_dtype, w_blocks, w_image, act, y, m, n, k, ldy, scratch, (cudaStream_t)stream));
+    const bool tensor = gemm_supported(w_dtype, m, k, di.max_smem_optin);
+    if (tensor && !act && gemm_takes_f32(w_dtype))
+        return launch_status(gemm_forward(w_dtype, w_blocks, w_image, nullptr, x, y, m, n, k, ldy, scratch, (cudaStream_t)stream));
+    if (!act) {
+        rc = lloom_b200_quantize_act(w_dtype, x, m, k, act_ws, stream);
+        if (rc != LLOOM_OK) return rc;
+        act = act_ws;
+    }
+    if (tensor)
+        return launch_status(gemm_forward(w_dtype, w_blocks, w_image, act, nullptr, y, m, n, k, ldy, scratch, (cudaStream_t)stream));
     // Shapes no tensor-core kernel takes: slabs of up to 8 activation rows through the GEMV.
     const int64_t arow = lloom_b200_act_row_bytes(w_dtype, k);
     for (int64_t r = 0; r < m; r += 8) {
@@ -597,7 +607,7 @@ int lloom_b200_gemm(int w_dtype, const void *w_blocks, const void *act_blocks, f
     const int64_t need = gemm_scratch_bytes(w_dtype, m, n, k, false);
     if (need > 0 && (!workspace || workspace_bytes < need)) return LLOOM_ERR_WORKSPACE;
     if (need > 0 && !aligned(workspace, 256)) return LLOOM_ERR_ALIGN;
-    return gemm_dispatch(w_dtype, w_blocks, nullptr, act_blocks, y, m, n, k, ldy, workspace, stream);
+    return gemm_dispatch(w_dtype, w_blocks, nullptr, act_blocks, nullptr, nullptr, y, m, n, k, ldy, workspace, stream);
 }
 
 int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, float *y, int64_t m, int64_t n,
@@ -606,9 +616,7 @@ int lloom_b200_qmatmul_fwd(int w_dtype, const void *w_blocks, const float *x, fl
     int rc = fwd_checks(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, workspace_bytes, need);
     if (rc != LLOOM_OK) return rc;
     if (m <= 8) return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, nullptr);
-    rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
-    if (rc != LLOOM_OK) return rc;
-    return gemm_dispatch(w_dtype, w_blocks, nullptr, workspace, y, m, n, k, ldy,
+    return gemm_dispatch(w_dtype, w_blocks, nullptr, nullptr, x, workspace, y, m, n, k, ldy,
                          (uint8_t *)workspace + act_blocks_bytes(w_dtype, m, k), stream);
 }
 
@@ -622,9 +630,7 @@ int lloom_b200_qmatmul_fwd_image(int w_dtype, const void *w_blocks, const void *
     if (!aligned(w_image, 1024)) return LLOOM_ERR_ALIGN;
     if (m <= 8) return decode_fwd(w_dtype, w_blocks, x, y, m, n, k, ldy, workspace, need, stream, nullptr);
     if (lloom_b200_weight_image_bytes(w_dtype, n, k) <= 0) return LLOOM_ERR_SHAPE;  // no image exists for this shape
-    rc = lloom_b200_quantize_act(w_dtype, x, m, k, workspace, stream);
-    if (rc != LLOOM_OK) return rc;
-    return gemm_dispatch(w_dtype, w_blocks, w_image, workspace, y, m, n, k, ldy,
+    return gemm_dispatch(w_dtype, w_blocks, w_image, nullptr, x, workspace, y, m, n, k, ldy,
                          (uint8_t *)workspace + act_blocks_bytes(w_dtype, m, k), stream);
 }
 

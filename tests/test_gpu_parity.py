@@ -455,6 +455,24 @@ def test_gemm_q8_0_q6k_tensor_core_path(dev, oracle, dt, n, k, m):
     assert Q.device_status() == 0
 
 
+@pytest.mark.parametrize("dt,n,k,m", [(12, 520, 2048, 70), (12, 300, 1024, 300), (13, 200, 512, 9), (14, 300, 1024, 40)])
+def test_prefill_forward_equals_quantizer_plus_gemm(dev, oracle, dt, n, k, m):
+    """The forward entry of the Q4_K / Q5_K prefill quantizes the activations in the pass that builds the GEMM's
+    operand images; the result equals the explicit route -- lloom_b200_quantize_act, then lloom_b200_gemm on the
+    canonical blocks -- bit for bit (as it does for the formats whose forward takes that route itself)."""
+    import lloom_b200 as lb
+    from lloom_b200 import quantized as Q
+
+    _, x, wq = make_case(oracle, dt, n, k, m, seed=dt + n + m)
+    x[m // 2] = 0.0  # an all-zero activation row: d = 0, codes and sums 0
+    qt = lb.QTensor.from_data(wq.tobytes(), dt, (n, k), dev)
+    xt = torch.from_numpy(x).to(dev)
+    fwd = lb.QMatMul.from_qtensor(qt).forward(xt)
+    two_step = Q.gemm(qt, Q.quantize_act(lb.GgmlDType(dt), xt), m)
+    assert torch.equal(fwd, two_step)
+    assert Q.device_status() == 0
+
+
 @pytest.mark.parametrize("dt", [8, 12, 14, 13, 2, 6])
 def test_prefill_image_same_bits(dev, oracle, dt):
     """A forward with the prebuilt weight image equals the per-call expansion bit for bit (m > 8), and decode batches
