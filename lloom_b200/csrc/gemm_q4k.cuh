@@ -16,7 +16,8 @@
 // of superblock b+1.
 //
 // Three launches per call:
-//   gemm_prep_kernel     canonical Q8_K activation blocks -> f16 operand images (B, B_min) + scale planes
+//   gemm_prep_f32_kernel f32 activations -> f16 operand images (B, B_min) + scale planes, quantizing on the way (the
+//                        forward entries); gemm_prep_kernel: the same from canonical Q8_K blocks (lloom_b200_gemm)
 //   gemm_expand_kernel   Q4_K weight blocks -> f16 operand images (A = sc*q, A_min = m_j); a bandwidth pass
 //                        (33 MB in, 125 MB out for [14336, 4096]) that spares every output tile from
 //                        re-unpacking its 128 weight rows on CUDA cores beside the MMAs
