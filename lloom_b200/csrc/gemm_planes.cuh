@@ -27,8 +27,9 @@
 
 namespace lloom {
 
-template <int GROUP_K, int PLANES, int BM>
+template <int GROUP_K, int PLANES, int BM, int EPI_WARPS = 8>
 struct PlanesCfg {
+    static constexpr int kEpiWarps = EPI_WARPS;        // 8 or 16: BM / (EPI_WARPS / 4) accumulator columns per warp
     static constexpr int kGroupK = GROUP_K;            // K elements per accumulator drain
     static constexpr int kPlanes = PLANES;             // f16 images per weight element
     static constexpr int kBM = BM;                     // activation rows per tile (UMMA N): 128 or 256
@@ -39,16 +40,28 @@ struct PlanesCfg {
     static constexpr int kStageABytes = kAtomsPerStage * PLANES * kGemmAtomBytes;
     static constexpr int kStageBBytes = kAtomsPerStage * kBAtomBytes;
     static constexpr int kAccBufs = 512 / BM;
-    static constexpr int kDaBytes = BM * 4;
+    static constexpr int kDaBytes = BM * 4;             // activation scales of one drain group
+    // The scale tiles travel in a ring of their own: a slot holds the scales of kDaGroups consecutive drain groups.
+    // With a drain every 32 of K a slot covers eight groups, so a copy's trip to L2 is paid once per 256 of K and is
+    // not on the path from one drain of an accumulator to its next use.
+    static constexpr int kDaGroups = GROUP_K >= 256 ? 1 : 8;
+    static constexpr int kDaSlots = GROUP_K >= 256 ? kAccBufs : 3;
+    static constexpr int kDaSlotBytes = kDaGroups * kDaBytes;
+    // Where a group is 32 of K the weight rows' scales ride in the same ring (gathered from the canonical blocks by the
+    // scale warp, 128 f32 per group); where a group is 256 of K each epilogue thread fetches its row's scale itself.
+    static constexpr bool kSmemW = GROUP_K < 256;
+    static constexpr int kDwSlotBytes = kSmemW ? kDaGroups * kGemmBN * 4 : 0;
     // BM = 256: 128 running sums per epilogue thread; three whole warpgroups, so that the two epilogue warpgroups can
     // take registers from the third (setmaxnreg)
-    static constexpr int kThreads = BM == 256 ? 384 : 352;  // 8 epilogue warps + operand copies + MMA issuer + scale copies
+    static constexpr int kThreads = BM == 256 ? 384 : 32 * (EPI_WARPS + 3);  // epilogue warps + operand copies + MMA issuer + scale copies
+    static_assert(EPI_WARPS == 8 || (EPI_WARPS == 16 && BM == 128), "epilogue warps");
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int kOffA = 0;
     static constexpr int kOffB = kOffA + kStages * kStageABytes;
     static constexpr int kOffDa = kOffB + kStages * kStageBBytes;
-    static constexpr int kOffBars = kOffDa + kAccBufs * kDaBytes;
-    static constexpr int kNumBars = 2 * kStages + 3 * kAccBufs;
+    static constexpr int kOffDw = kOffDa + kDaSlots * kDaSlotBytes;
+    static constexpr int kOffBars = kOffDw + kDaSlots * kDwSlotBytes;
+    static constexpr int kNumBars = 2 * kStages + 2 * kAccBufs + 2 * kDaSlots;
     static constexpr int kOffMisc = kOffBars + kNumBars * 8;
     static constexpr int kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 };
@@ -293,7 +306,8 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::kOffBars);
     uint64_t *full = bars, *empty = bars + Cfg::kStages;
-    uint64_t *acc_full = bars + 2 * Cfg::kStages, *acc_empty = acc_full + Cfg::kAccBufs, *da_full = acc_empty + Cfg::kAccBufs;
+    uint64_t *acc_full = bars + 2 * Cfg::kStages, *acc_empty = acc_full + Cfg::kAccBufs;
+    uint64_t *da_full = acc_empty + Cfg::kAccBufs, *da_empty = da_full + Cfg::kDaSlots;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + Cfg::kOffMisc);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + Cfg::kOffMisc + 4);
 
@@ -313,13 +327,16 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         }
         for (int i = 0; i < Cfg::kAccBufs; ++i) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], kGemmEpiWarps);
-            mbar_init(&da_full[i], 1);
+            mbar_init(&acc_empty[i], Cfg::kEpiWarps);
+        }
+        for (int i = 0; i < Cfg::kDaSlots; ++i) {
+            mbar_init(&da_full[i], Cfg::kSmemW ? 2 : 1);  // the copy's bytes (+ the gathered weight scales)
+            mbar_init(&da_empty[i], Cfg::kEpiWarps);
         }
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == kGemmEpiWarps + 1) {  // tensor memory: all 512 columns, 512 / BM accumulators
+    if (warp == Cfg::kEpiWarps + 1) {  // tensor memory: all 512 columns, 512 / BM accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -331,11 +348,11 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
 
     // BM = 256, per scheduler: two epilogue warps of 216 registers and one other warp of 72.  One setmaxnreg per
     // warpgroup, executed by all of its warps at the top of the branch that holds all of the warpgroup's code.
-    if (warp < kGemmEpiWarps) {
+    if (warp < Cfg::kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
         // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns (BM/2)*(w/4)..
         if (Cfg::kBM == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
-        constexpr int kCW = Cfg::kBM / 2;  // columns per warp
+        constexpr int kCW = Cfg::kBM / (Cfg::kEpiWarps / 4);  // columns per warp
         const int q = warp & 3, half = warp >> 2;
         const int r = q * 32 + lane;  // row of the tile == TMEM lane
         const int64_t n = n0 + r;
@@ -344,41 +361,55 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         uint64_t out2[kCW / 2];
 #pragma unroll
         for (int j = 0; j < kCW / 2; ++j) out2[j] = 0ull;
-        // the row's weight scales, a batch of groups at a time, the next batch in flight while this one is used: eight
-        // per batch where a drain every 32 of K is shorter than a trip to L2, one where a group is 256 of K
-        constexpr int kScaleBatch = Cfg::kGroupK >= 256 ? 1 : 8;
-        unsigned short hdr_cur[kScaleBatch], hdr_nxt[kScaleBatch];
-#pragma unroll
-        for (int i = 0; i < kScaleBatch; ++i) {
-            hdr_cur[i] = 0;
-            hdr_nxt[i] = (row_ok && i < ngroups) ? __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)i * p.scale_stride))
-                                                 : (unsigned short)0;
-        }
+        // group >= 256 of K: the row's weight scale of the next group is fetched while this group is drained
+        unsigned short hdr_nxt = 0;
+        if (!Cfg::kSmemW && row_ok) hdr_nxt = __ldg(reinterpret_cast<const unsigned short *>(wrow));
         bool ok = true;
         for (int g = 0; g < ngroups && ok; ++g) {
             const int buf = g % Cfg::kAccBufs;
             const uint32_t par = (g / Cfg::kAccBufs) & 1;
-            if (g % kScaleBatch == 0) {
-#pragma unroll
-                for (int i = 0; i < kScaleBatch; ++i) {
-                    hdr_cur[i] = hdr_nxt[i];
-                    const int gn = g + kScaleBatch + i;
-                    if (row_ok && gn < ngroups)
-                        hdr_nxt[i] = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)gn * p.scale_stride));
-                }
+            const int slot_i = g / Cfg::kDaGroups, in_slot = g % Cfg::kDaGroups, slot = slot_i % Cfg::kDaSlots;
+            if (in_slot == 0) ok = mbar_wait_abortable<64>(&da_full[slot], (slot_i / Cfg::kDaSlots) & 1, abort_flag);
+            if (!ok) break;
+            float dw;
+            if (Cfg::kSmemW) {
+                dw = *reinterpret_cast<const float *>(smem + Cfg::kOffDw + slot * Cfg::kDwSlotBytes + (in_slot * kGemmBN + r) * 4);
+            } else {
+                dw = f16_bits_to_f32(hdr_nxt);
+                if (row_ok && g + 1 < ngroups)
+                    hdr_nxt = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)(g + 1) * p.scale_stride));
             }
-            unsigned short hdr = hdr_cur[0];
-#pragma unroll
-            for (int i = 1; i < kScaleBatch; ++i)
-                if (g % kScaleBatch == i) hdr = hdr_cur[i];
-            const float dw = f16_bits_to_f32(hdr);
             const uint64_t dw2 = pack2f(dw, dw);
-            ok = mbar_wait_abortable<64>(&da_full[buf], par, abort_flag) && mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
+            ok = mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kBM + half * kCW);
             // the activation scales of this warp's columns, as f32 pairs, times the weight scale: (d_a * d_w)
-            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + Cfg::kOffDa + buf * Cfg::kDaBytes + half * kCW * 4);
+            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + Cfg::kOffDa + slot * Cfg::kDaSlotBytes +
+                                                                         in_slot * Cfg::kDaBytes + half * kCW * 4);
+            if (kCW == 32) {  // sixteen epilogue warps: one load of 32 columns
+                uint32_t va[32];
+                tmem_ld32(t_main, va);
+                uint64_t d2[16];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const ulonglong2 t = dap[j];
+                    d2[2 * j] = mul_f32x2(t.x, dw2);
+                    d2[2 * j + 1] = mul_f32x2(t.y, dw2);
+                }
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (in_slot == Cfg::kDaGroups - 1 || g == ngroups - 1) {
+                    fence_proxy_async();  // as below: the slot's next writer is a bulk copy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&da_empty[slot]);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    out2[j] = fma_f32x2(d2[j], (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[j]);
+            }
 #pragma unroll
             for (int c = 0; c < kCW / 64; ++c) {  // 64 columns at a time: two loads in flight
                 uint32_t va[32], vb[32];
@@ -402,13 +433,17 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
                     d2[2 * j + 1] = mul_f32x2(t.y, dw2);
                 }
                 if (c == kCW / 64 - 1) {
-                    // everything this warp needs from tensor memory and from the scale tile is in registers now; the
-                    // scale tile is rewritten by a bulk copy (async proxy) right after the arrivals, so this warp's
-                    // reads of it (generic proxy) are fenced first
+                    // everything this warp needs from tensor memory and from the scale tiles is in registers now
                     tc_fence_before();
-                    fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (in_slot == Cfg::kDaGroups - 1 || g == ngroups - 1) {
+                        // the slot is rewritten by a bulk copy (async proxy) right after the arrivals, so this warp's
+                        // reads of it (generic proxy) are fenced first
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&da_empty[slot]);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
@@ -425,7 +460,7 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         }
     } else {
     if (Cfg::kBM == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
-    if (warp == kGemmEpiWarps) {
+    if (warp == Cfg::kEpiWarps) {
         // ------------------------------ operand tiles: bulk copies ------------------------------
         // The whole warp walks the loop (lanes stay converged); lane 0 issues the copies.
         const uint8_t *aimg = p.w_img + (int64_t)nt * atoms * Cfg::kPlanes * kGemmAtomBytes;
@@ -442,26 +477,51 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
             }
             __syncwarp();
         }
-    } else if (warp == kGemmEpiWarps + 2) {
-        // ------------------------------ activation scales of each drain group ------------------------------
+    } else if (warp == Cfg::kEpiWarps + 2) {
+        // ------------------------------ activation scales, a slot of drain groups at a time ------------------------------
         const PlanesActLayout lay = planes_act_layout(p.m, p.k, Cfg::kGroupK, Cfg::kBM);
         const uint8_t *dat = p.act_img + lay.dat + (int64_t)mt * ngroups * Cfg::kDaBytes;
+        const int nslots = (ngroups + Cfg::kDaGroups - 1) / Cfg::kDaGroups;
         bool ok = true;
-        for (int g = 0; g < ngroups && ok; ++g) {
-            const int buf = g % Cfg::kAccBufs;
-            if (g >= Cfg::kAccBufs) ok = mbar_wait_abortable<32>(&acc_empty[buf], ((g / Cfg::kAccBufs) - 1) & 1, abort_flag);
+        for (int si = 0; si < nslots && ok; ++si) {
+            const int slot = si % Cfg::kDaSlots;
+            if (si >= Cfg::kDaSlots) ok = mbar_wait_abortable<32>(&da_empty[slot], ((si / Cfg::kDaSlots) - 1) & 1, abort_flag);
             if (!ok) break;
             if (lane == 0) {
-                mbar_arrive_expect_tx(&da_full[buf], Cfg::kDaBytes);
-                bulk_g2s(smem + Cfg::kOffDa + buf * Cfg::kDaBytes, dat + (int64_t)g * Cfg::kDaBytes, Cfg::kDaBytes, &da_full[buf]);
+                const int groups = min(Cfg::kDaGroups, ngroups - si * Cfg::kDaGroups);
+                const uint32_t bytes = (uint32_t)(groups * Cfg::kDaBytes);
+                mbar_arrive_expect_tx(&da_full[slot], bytes);
+                bulk_g2s(smem + Cfg::kOffDa + slot * Cfg::kDaSlotBytes, dat + (int64_t)si * Cfg::kDaSlotBytes, bytes, &da_full[slot]);
+            }
+            if (Cfg::kSmemW) {
+                // the f16 scales of the tile's 128 weight rows for the slot's groups: lane l gathers rows l, l + 32, ...
+                const int groups = min(Cfg::kDaGroups, ngroups - si * Cfg::kDaGroups);
+                float *dws = reinterpret_cast<float *>(smem + Cfg::kOffDw + slot * Cfg::kDwSlotBytes);
+#pragma unroll
+                for (int j = 0; j < kGemmBN / 32; ++j) {
+                    const int rr = lane + 32 * j;
+                    const bool rok = n0 + rr < p.n_end;
+                    const uint8_t *wp = p.w + (rok ? n0 + rr : 0) * p.row_bytes + p.scale_off +
+                                        (int64_t)si * Cfg::kDaGroups * p.scale_stride;
+                    unsigned short h[Cfg::kDaGroups];
+#pragma unroll
+                    for (int gi = 0; gi < Cfg::kDaGroups; ++gi)
+                        h[gi] = (rok && gi < groups) ? __ldg(reinterpret_cast<const unsigned short *>(wp + (int64_t)gi * p.scale_stride))
+                                                     : (unsigned short)0;
+#pragma unroll
+                    for (int gi = 0; gi < Cfg::kDaGroups; ++gi) dws[gi * kGemmBN + rr] = f16_bits_to_f32(h[gi]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&da_full[slot]);
             }
             __syncwarp();
         }
-    } else if (warp == kGemmEpiWarps + 1) {
+    } else if (warp == Cfg::kEpiWarps + 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp walks the loop; lane 0 issues the MMAs and commits.
         // instruction descriptor: D = f32, A = B = f16, both K-major, N = BM, M = 128
         const uint32_t idesc = (1u << 4) | ((uint32_t)(Cfg::kBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
+        const uint32_t a_lo0 = umma_desc_lo(smem_u32(smem + Cfg::kOffA), 16), b_lo0 = umma_desc_lo(smem_u32(smem + Cfg::kOffB), 16);
         constexpr int kStepsPerStage = Cfg::kStageK / 16;
         constexpr int kStepsPerGroup = Cfg::kGroupK / 16;
         bool ok = true;
@@ -470,8 +530,8 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
             ok = mbar_wait_abortable<0>(&full[s], (it / Cfg::kStages) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t a_addr = smem_u32(smem + Cfg::kOffA + s * Cfg::kStageABytes);
-            const uint32_t b_addr = smem_u32(smem + Cfg::kOffB + s * Cfg::kStageBBytes);
+            const uint32_t a_lo = a_lo0 + (uint32_t)(s * (Cfg::kStageABytes >> 4));
+            const uint32_t b_lo = b_lo0 + (uint32_t)(s * (Cfg::kStageBBytes >> 4));
 #pragma unroll
             for (int kk = 0; kk < kStepsPerStage; ++kk) {  // K = 16 per instruction: atom kk/4, 32 bytes along its swizzled row
                 const int step = it * kStepsPerStage + kk;
@@ -484,12 +544,12 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
                 }
                 if (lane == 0) {
                     const uint32_t d_acc = tmem_base + (uint32_t)(buf * Cfg::kBM);
-                    const uint32_t boff = (uint32_t)((kk >> 2) * Cfg::kBAtomBytes + (kk & 3) * 32);
+                    const uint32_t boff = (uint32_t)((kk >> 2) * (Cfg::kBAtomBytes >> 4) + (kk & 3) * 2);
 #pragma unroll
                     for (int pl = 0; pl < Cfg::kPlanes; ++pl) {
-                        const uint32_t aoff = (uint32_t)(((kk >> 2) * Cfg::kPlanes + pl) * kGemmAtomBytes + (kk & 3) * 32);
-                        umma_f16(d_acc, umma_desc(a_addr + aoff, 16, 1024, 2), umma_desc(b_addr + boff, 16, 1024, 2), idesc,
-                                 (in_group | pl) != 0 ? 1u : 0u);
+                        const uint32_t aoff = (uint32_t)(((kk >> 2) * Cfg::kPlanes + pl) * (kGemmAtomBytes >> 4) + (kk & 3) * 2);
+                        if (pl != 0 || (kk % kStepsPerGroup) != 0) umma_f16_lo<true>(d_acc, a_lo + aoff, b_lo + boff, idesc);
+                        else umma_f16_lo_rt(d_acc, a_lo + aoff, b_lo + boff, idesc, in_group != 0 ? 1u : 0u);
                     }
                     if (in_group == kStepsPerGroup - 1) umma_commit(&acc_full[buf]);
                 }
@@ -504,7 +564,7 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
     // ------------------------------ teardown ------------------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == kGemmEpiWarps + 1) {
+    if (warp == Cfg::kEpiWarps + 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }

@@ -313,6 +313,42 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
+// The issue loop's form of the same: for a K-major, 128-byte-swizzled operand only the low word of the descriptor
+// (address and leading offset) changes from step to step, by a compile-time amount; the high word (stride 1024 bytes,
+// version, swizzle mode) is a constant.  Built this way an MMA costs its issuing thread a handful of instructions; with
+// the descriptors rebuilt from addresses for every instruction the issuing thread, not the tensor pipe, set the pace
+// (about 200 cycles per M = 128, N = 128, K = 16 instruction against 65 when issued back to back).
+constexpr uint32_t kUmmaDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(kUmmaDescHiSw128), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_lo_rt(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(kUmmaDescHiSw128), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -543,6 +579,7 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
         // The whole warp walks the loop; lane 0 issues the MMAs and commits.
         // instruction descriptor: D = f32, A = B = f16, both K-major, N = 128, M = 128
         const uint32_t idesc = (1u << 4) | ((uint32_t)(kGemmBM >> 3) << 17) | ((uint32_t)(kGemmBN >> 4) << 24);
+        const uint32_t a_lo0 = umma_desc_lo(smem_u32(smem + kOffA), 16), b_lo0 = umma_desc_lo(smem_u32(smem + kOffB), 16);
         bool ok = true;
         for (int b = 0; b < nb && ok; ++b) {
             const int buf = b & 1;
@@ -551,19 +588,22 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
-            for (int h = 0; h < 2 && ok; ++h) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (!ok) break;
                 const int it = b * 2 + h, s = it % kGemmStages;
                 ok = mbar_wait_abortable<0>(&full[s], (it / kGemmStages) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a_addr = smem_u32(smem + kOffA + s * kGemmStageBytes);
-                    const uint32_t b_addr = smem_u32(smem + kOffB + s * kGemmStageBytes);
+                    const uint32_t a_lo = a_lo0 + (uint32_t)(s * (kGemmStageBytes >> 4));
+                    const uint32_t b_lo = b_lo0 + (uint32_t)(s * (kGemmStageBytes >> 4));
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {  // K = 16 per instruction: atom kk/4, 32 bytes along its swizzled row
-                        const uint32_t off = (uint32_t)((kk >> 2) * kGemmAtomBytes + (kk & 3) * 32);
-                        umma_f16(d_main, umma_desc(a_addr + off, 16, 1024, 2), umma_desc(b_addr + off, 16, 1024, 2), idesc,
-                                 (h | kk) != 0 ? 1u : 0u);
+                        constexpr int kAtom16 = kGemmAtomBytes >> 4;
+                        const uint32_t off = (uint32_t)((kk >> 2) * kAtom16 + (kk & 3) * 2);
+                        if (h == 0 && kk == 0) umma_f16_lo<false>(d_main, a_lo + off, b_lo + off, idesc);
+                        else umma_f16_lo<true>(d_main, a_lo + off, b_lo + off, idesc);
                     }
                     umma_commit(&empty[s]);
                 }
