@@ -287,6 +287,20 @@ __global__ void __launch_bounds__(128) planes_expand_q6k_kernel(const uint8_t *_
     }
 }
 
+// 16 lanes x 64 columns of tensor memory as the MMA accumulator fragment: thread T = 4*g + c holds, for each block i of
+// eight columns, v[4i], v[4i+1] = lane g, columns 8i + 2c, 8i + 2c + 1 and v[4i+2], v[4i+3] = lane g + 8, same columns.
+__device__ __forceinline__ void tmem_ld_frag64(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
 struct PlanesParams {
     const uint8_t *w;        // canonical weight blocks of the whole matrix (for the per-group f16 scales)
     const uint8_t *act_img;  // planes_prep_kernel output
@@ -354,6 +368,79 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         if (Cfg::kBM == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
         constexpr int kCW = Cfg::kBM / (Cfg::kEpiWarps / 4);  // columns per warp
         const int q = warp & 3, half = warp >> 2;
+        if (Cfg::kSmemW && kCW == 64) {
+            // A drain every 32 of K: the scales, not the sums, set the cost.  With a tensor-memory lane per thread every
+            // thread would fetch all 64 activation scales of its columns for every group (the same words in all 32
+            // lanes, 64 shared-memory wavefronts per warp and group); in the accumulator-fragment layout a thread
+            // holds 4 rows x 16 columns, so it needs 16 activation scales and 4 weight scales (20 wavefronts).
+            const int fg = lane >> 2, fc = lane & 3;
+            float acc[4][16];  // [row j: 32q + fg + 8j][2i + e: column 64*half + 8i + 2fc + e]
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[j][i] = 0.0f;
+            bool ok = true;
+            for (int g = 0; g < ngroups && ok; ++g) {
+                const int buf = g % Cfg::kAccBufs;
+                const uint32_t par = (g / Cfg::kAccBufs) & 1;
+                const int slot_i = g / Cfg::kDaGroups, in_slot = g % Cfg::kDaGroups, slot = slot_i % Cfg::kDaSlots;
+                if (in_slot == 0) ok = mbar_wait_abortable<64>(&da_full[slot], (slot_i / Cfg::kDaSlots) & 1, abort_flag);
+                if (!ok) break;
+                const float *dws = reinterpret_cast<const float *>(smem + Cfg::kOffDw + slot * Cfg::kDwSlotBytes) +
+                                   in_slot * kGemmBN + q * 32 + fg;
+                const float2 *das = reinterpret_cast<const float2 *>(smem + Cfg::kOffDa + slot * Cfg::kDaSlotBytes +
+                                                                     in_slot * Cfg::kDaBytes + half * kCW * 4) + fc;
+                float dw[4];
+                float2 da2[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dw[j] = dws[8 * j];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) da2[i] = das[4 * i];
+                ok = mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * Cfg::kBM + half * kCW);
+                uint32_t va[32], vb[32];
+                tmem_ld_frag64(t_main, va);                     // lanes 32q .. 32q + 15
+                tmem_ld_frag64(t_main + (16u << 16), vb);       // lanes 32q + 16 .. 32q + 31
+                tmem_ld_wait();
+                // everything this warp needs from tensor memory and from the scale tiles is in registers now
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (in_slot == Cfg::kDaGroups - 1 || g == ngroups - 1) {
+                    // the slot is rewritten by a bulk copy (async proxy) right after the arrivals, so this warp's reads
+                    // of it (generic proxy) are fenced first
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&da_empty[slot]);
+                }
+                // scalar multiplies and fused multiply-adds: they issue on both FMA pipes, the packed f32x2 forms on one
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t *v = (j < 2) ? va : vb;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int ix = 4 * i + 2 * (j & 1);
+                        acc[j][2 * i] = __fmaf_rn(__fmul_rn(da2[i].x, dw[j]), __uint_as_float(v[ix]), acc[j][2 * i]);
+                        acc[j][2 * i + 1] = __fmaf_rn(__fmul_rn(da2[i].y, dw[j]), __uint_as_float(v[ix + 1]), acc[j][2 * i + 1]);
+                    }
+                }
+            }
+            if (ok) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t n = n0 + q * 32 + fg + 8 * j;
+                    if (n >= p.n_end) continue;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int mrow = m0 + half * kCW + 8 * i + 2 * fc;
+                        if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = acc[j][2 * i];
+                        if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = acc[j][2 * i + 1];
+                    }
+                }
+            }
+        } else {
         const int r = q * 32 + lane;  // row of the tile == TMEM lane
         const int64_t n = n0 + r;
         const bool row_ok = n < p.n_end;
@@ -457,6 +544,7 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
                 if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] & 0xffffffffu));
                 if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
             }
+        }
         }
     } else {
     if (Cfg::kBM == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
