@@ -16,10 +16,16 @@
 // The kernel is the Q4_K GEMM's frame (gemm_q4k.cuh) with the drain group, the plane count and the activation rows
 // per tile (BM, the UMMA N) as parameters: 128 x BM output tile per CTA; operands arrive as ready-made
 // 128-byte-swizzled K-major images by bulk copies; 512 / BM accumulators in tensor memory, so the drain of group g
-// overlaps the MMAs of the following groups.  A tcgen05.mma of M = 128, K = 16 takes the same time for N = 128 and
-// N = 256, so BM = 256 doubles the tensor rate where the epilogue keeps up: Q6_K (one drain per 256 of K) runs at
-// BM = 256, Q8_0 (one drain per 32 of K, epilogue-bound) stays at 128.
-// Warp roles: 0-7 epilogue, 8 operand copies, 9 MMA issuer (one elected lane), 10 activation-scale copies.
+// overlaps the MMAs of the following groups.  An MMA reads both operands from shared memory (8 KB per M = 128,
+// N = 128, K = 16 instruction, 12 KB for twice the work at N = 256) and the bulk copies write as much again, so with
+// the instruction stream kept short the shared-memory port sets the pace of the MMA side: Q6_K (one drain per 256 of
+// K) runs at BM = 256; Q8_0 / Q4_0 / Q5_0 (one drain per 32 of K) are bound by their epilogue and stay at 128.
+// Warp roles: 0-7 epilogue, 8 operand copies, 9 MMA issuer (one elected lane), 10 scale tiles (bulk copy of the
+// activation scales; for the 32-of-K formats also the gather of the weight rows' f16 scales from the canonical blocks).
+// The scale tiles travel in their own ring (a slot = 8 drain groups for the 32-of-K formats), released by the epilogue
+// warps separately from the accumulators.  Epilogue of the 32-of-K formats: accumulators are read in the MMA fragment
+// layout (tcgen05.ld.16x256b: 4 rows x 16 columns per thread), so a thread needs 16 + 4 scale words per group instead
+// of 64 + 1; per output one exact product d_w * d_a and one fused multiply-add, the AVX2 arm's two operations.
 // All waits are bounded and abortable; tensor memory is released on every path.
 #pragma once
 

@@ -41,10 +41,12 @@ namespace lloom {
 constexpr int kGemmBN = 128;          // weight rows per tile (UMMA M)
 constexpr int kGemmBM = 128;          // activation rows per tile (UMMA N)
 constexpr int kGemmAtomBytes = 128 * 64 * 2;   // one swizzle atom: 128 rows x 64 of K, f16
-constexpr int kGemmStageBytes = 2 * kGemmAtomBytes;  // a pipeline stage covers 128 of K: two atoms per operand
+constexpr int kGemmStageAtoms = 2;                   // swizzle atoms per operand and pipeline stage (64 of K each); one atom per stage and six stages measured 13% slower
+constexpr int kGemmStageBytes = kGemmStageAtoms * kGemmAtomBytes;
+constexpr int kGemmStagesPerSb = 4 / kGemmStageAtoms;  // stages per 256-element superblock
 constexpr int kGemmMinBytes = 128 * 16 * 2;    // min-term operand tile (K = 16), f16
 constexpr int kGemmDaBytes = 128 * 4;
-constexpr int kGemmStages = 3;
+constexpr int kGemmStages = 6 / kGemmStageAtoms;     // 192 KB of operand stages
 constexpr int kGemmThreads = 320;  // 8 epilogue warps + bulk-copy warp + MMA warp (plane GEMMs)
 constexpr int kGemmEpiWarps = 8;
 // Q4_K kernel: sixteen epilogue warps (four per tensor-memory lane quarter, 32 accumulator columns each): with S and Mn
@@ -548,8 +550,8 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
         const uint8_t *dat = p.act_img + alay.dat + (int64_t)mt * nb * kGemmDaBytes;
         bool ok = true;
         for (int b = 0; b < nb && ok; ++b) {
-            for (int h = 0; h < 2 && ok; ++h) {
-                const int it = b * 2 + h, s = it % kGemmStages;
+            for (int h = 0; h < kGemmStagesPerSb && ok; ++h) {
+                const int it = b * kGemmStagesPerSb + h, s = it % kGemmStages;
                 if (it >= kGemmStages) ok = mbar_wait_abortable<32>(&empty[s], ((it / kGemmStages) - 1) & 1, abort_flag);
                 if (!ok) break;
                 if (lane == 0) {
@@ -589,9 +591,9 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
             tc_fence_after();
             const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < kGemmStagesPerSb; ++h) {
                 if (!ok) break;
-                const int it = b * 2 + h, s = it % kGemmStages;
+                const int it = b * kGemmStagesPerSb + h, s = it % kGemmStages;
                 ok = mbar_wait_abortable<0>(&full[s], (it / kGemmStages) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
@@ -599,7 +601,7 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
                     const uint32_t a_lo = a_lo0 + (uint32_t)(s * (kGemmStageBytes >> 4));
                     const uint32_t b_lo = b_lo0 + (uint32_t)(s * (kGemmStageBytes >> 4));
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {  // K = 16 per instruction: atom kk/4, 32 bytes along its swizzled row
+                    for (int kk = 0; kk < 4 * kGemmStageAtoms; ++kk) {  // K = 16 per instruction: atom kk/4, 32 bytes along its swizzled row
                         constexpr int kAtom16 = kGemmAtomBytes >> 4;
                         const uint32_t off = (uint32_t)((kk >> 2) * kAtom16 + (kk & 3) * 2);
                         if (h == 0 && kk == 0) umma_f16_lo<false>(d_main, a_lo + off, b_lo + off, idesc);
