@@ -375,6 +375,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr));
 }
+// 16 lanes x 32 columns of tensor memory as the MMA accumulator fragment: thread T = 4*g + c holds, for each block i of
+// eight columns, v[4i], v[4i+1] = lane g, columns 8i + 2c, 8i + 2c + 1 and v[4i+2], v[4i+3] = lane g + 8, same columns.
+__device__ __forceinline__ void tmem_ld_frag32(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
@@ -475,38 +485,58 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
 
     if (warp < kQ4kEpiWarps) {
         // ------------------------------ epilogue ------------------------------
-        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 32*(w/4)..
+        // warp w: TMEM lanes 32*(w%4).. (hardware rule), accumulator columns 32*(w/4)..  The accumulators are read in
+        // the MMA fragment layout: thread 4*fg + fc holds rows 32q + fg + 8j (j < 4) and columns 32*part + 8i + 2fc, + 1
+        // (i < 4), so it needs 8 activation scales per superblock instead of the 32 a thread owning one tensor-memory
+        // lane would fetch (the same words in all 32 lanes: a quarter of the shared-memory port, which the MMA operand
+        // reads and the bulk copies already fill).
         const int q = warp & 3, part = warp >> 2;
-        const int r = q * 32 + lane;  // row of the tile == TMEM lane
-        const int n = n0 + r;
-        const bool row_ok = n < p.n;
-        const uint8_t *wrow = p.w + (int64_t)(row_ok ? n : 0) * p.row_bytes;
-        uint64_t out2[16];
+        const int fg = lane >> 2, fc = lane & 3;
+        const uint8_t *wrow[4];
+        bool row_ok[4];
+        uint32_t hdr_next[4];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) out2[j] = 0ull;
-        uint32_t hdr_next = row_ok ? __ldg(reinterpret_cast<const uint32_t *>(wrow)) : 0u;
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + q * 32 + fg + 8 * j;
+            row_ok[j] = n < p.n;
+            wrow[j] = p.w + (int64_t)(row_ok[j] ? n : 0) * p.row_bytes;
+            hdr_next[j] = row_ok[j] ? __ldg(reinterpret_cast<const uint32_t *>(wrow[j])) : 0u;
+        }
+        uint64_t out2[4][4];  // [row j][column pair i]
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out2[j][i] = 0ull;
         bool ok = true;
         for (int b = 0; b < nb && ok; ++b) {
             const int buf = b & 1;
             const uint32_t par = (b >> 1) & 1;
-            const uint32_t hdr = hdr_next;
-            if (b + 1 < nb && row_ok) hdr_next = __ldg(reinterpret_cast<const uint32_t *>(wrow + (int64_t)(b + 1) * p.blk_bytes));
-            const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
-            const uint64_t dw2 = pack2f(dw, dw), ndmin2 = pack2f(ndmin, ndmin);
+            uint64_t dw2[4], ndmin2[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t hdr = hdr_next[j];
+                if (b + 1 < nb && row_ok[j]) hdr_next[j] = __ldg(reinterpret_cast<const uint32_t *>(wrow[j] + (int64_t)(b + 1) * p.blk_bytes));
+                const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
+                dw2[j] = pack2f(dw, dw);
+                ndmin2[j] = pack2f(ndmin, ndmin);
+            }
             ok = mbar_wait_abortable<64>(&min_full[buf], par, abort_flag);
             if (!ok) break;
-            const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + kOffDa + buf * kGemmDaBytes + part * 128);
+            const uint64_t *dap = reinterpret_cast<const uint64_t *>(smem + kOffDa + buf * kGemmDaBytes + part * 128) + fc;
+            uint64_t da2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) da2[i] = dap[4 * i];
             ok = mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + part * 32);
-            // two halves of 16 columns: S and Mn of a half are loaded together, the next half's loads run under this half's FMAs
+            // two halves of 16 lanes: S and Mn of a half are loaded together, the next half's loads run under this half's FMAs
             uint32_t va[2][16], vb[2][16];
-            tmem_ld16(t_main, va[0]);
-            tmem_ld16(t_main + 128, vb[0]);
+            tmem_ld_frag32(t_main, va[0]);
+            tmem_ld_frag32(t_main + 128, vb[0]);
             tmem_ld_wait();
-            tmem_ld16(t_main + 16, va[1]);
-            tmem_ld16(t_main + 128 + 16, vb[1]);
+            tmem_ld_frag32(t_main + (16u << 16), va[1]);
+            tmem_ld_frag32(t_main + (16u << 16) + 128, vb[1]);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 if (h == 1) {
@@ -515,15 +545,15 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
                     tc_fence_before();
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const ulonglong2 t = dap[4 * h + j];
-                    const uint32_t *a = va[h] + 4 * j, *m = vb[h] + 4 * j;
-                    uint64_t o = out2[8 * h + 2 * j];
-                    o = fma_f32x2(mul_f32x2(t.x, dw2), (uint64_t)a[0] | ((uint64_t)a[1] << 32), o);
-                    out2[8 * h + 2 * j] = fma_f32x2(mul_f32x2(t.x, ndmin2), (uint64_t)m[0] | ((uint64_t)m[1] << 32), o);
-                    o = out2[8 * h + 2 * j + 1];
-                    o = fma_f32x2(mul_f32x2(t.y, dw2), (uint64_t)a[2] | ((uint64_t)a[3] << 32), o);
-                    out2[8 * h + 2 * j + 1] = fma_f32x2(mul_f32x2(t.y, ndmin2), (uint64_t)m[2] | ((uint64_t)m[3] << 32), o);
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int j = 2 * h + jj;
+                        const uint32_t *a = va[h] + 4 * i + 2 * jj, *m = vb[h] + 4 * i + 2 * jj;
+                        uint64_t o = out2[j][i];
+                        o = fma_f32x2(mul_f32x2(da2[i], dw2[j]), (uint64_t)a[0] | ((uint64_t)a[1] << 32), o);
+                        out2[j][i] = fma_f32x2(mul_f32x2(da2[i], ndmin2[j]), (uint64_t)m[0] | ((uint64_t)m[1] << 32), o);
+                    }
                 }
             }
             // the scale tile is rewritten by a bulk copy (async proxy) after the arrivals, so this warp's reads of it
@@ -532,12 +562,17 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        if (ok && row_ok) {
+        if (ok) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int mrow = m0 + part * 32 + 2 * j;
-                if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] & 0xffffffffu));
-                if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j] >> 32));
+            for (int j = 0; j < 4; ++j) {
+                if (!row_ok[j]) continue;
+                const int n = n0 + q * 32 + fg + 8 * j;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int mrow = m0 + part * 32 + 8 * i + 2 * fc;
+                    if (mrow < p.m) p.y[(int64_t)mrow * p.ldy + n] = __uint_as_float((uint32_t)(out2[j][i] & 0xffffffffu));
+                    if (mrow + 1 < p.m) p.y[(int64_t)(mrow + 1) * p.ldy + n] = __uint_as_float((uint32_t)(out2[j][i] >> 32));
+                }
             }
         }
     } else if (warp == kQ4kEpiWarps) {
