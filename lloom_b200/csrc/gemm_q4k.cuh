@@ -52,7 +52,7 @@ constexpr int kGemmEpiWarps = 8;
 // Q4_K kernel: sixteen epilogue warps (four per tensor-memory lane quarter, 32 accumulator columns each): with S and Mn
 // to drain per superblock, eight warps at two per scheduler left part of the drain exposed
 constexpr int kQ4kEpiWarps = 16;
-constexpr int kQ4kThreads = 32 * (kQ4kEpiWarps + 2);
+constexpr int kQ4kThreads = 32 * (kQ4kEpiWarps + 3);  // + copy warp, MMA warp, row-scale warp
 
 // ---- shared memory map (offsets from a 1024-byte aligned base) ----
 constexpr int kOffA = 0;
@@ -60,7 +60,9 @@ constexpr int kOffB = kOffA + kGemmStages * kGemmStageBytes;
 constexpr int kOffMinA = kOffB + kGemmStages * kGemmStageBytes;
 constexpr int kOffMinB = kOffMinA + 2 * kGemmMinBytes;
 constexpr int kOffDa = kOffMinB + 2 * kGemmMinBytes;
-constexpr int kOffBars = kOffDa + 2 * kGemmDaBytes;
+constexpr int kOffHdr = kOffDa + 2 * kGemmDaBytes;   // (d_w, -dmin_w) of the tile's 128 weight rows, per superblock
+constexpr int kGemmHdrBytes = 128 * 8;
+constexpr int kOffBars = kOffHdr + 2 * kGemmHdrBytes;
 constexpr int kGemmNumBars = 2 * kGemmStages + 6;
 constexpr int kOffMisc = kOffBars + kGemmNumBars * 8;
 constexpr int kGemmSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
@@ -466,7 +468,7 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
             mbar_init(&empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&min_full[i], 1);
+            mbar_init(&min_full[i], 2);  // the copies' bytes + the gathered row scales
             mbar_init(&acc_full[i], 1);
             mbar_init(&acc_empty[i], kQ4kEpiWarps);
         }
@@ -492,16 +494,9 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
         // reads and the bulk copies already fill).
         const int q = warp & 3, part = warp >> 2;
         const int fg = lane >> 2, fc = lane & 3;
-        const uint8_t *wrow[4];
         bool row_ok[4];
-        uint32_t hdr_next[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + q * 32 + fg + 8 * j;
-            row_ok[j] = n < p.n;
-            wrow[j] = p.w + (int64_t)(row_ok[j] ? n : 0) * p.row_bytes;
-            hdr_next[j] = row_ok[j] ? __ldg(reinterpret_cast<const uint32_t *>(wrow[j])) : 0u;
-        }
+        for (int j = 0; j < 4; ++j) row_ok[j] = n0 + q * 32 + fg + 8 * j < p.n;
         uint64_t out2[4][4];  // [row j][column pair i]
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -511,17 +506,19 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
         for (int b = 0; b < nb && ok; ++b) {
             const int buf = b & 1;
             const uint32_t par = (b >> 1) & 1;
-            uint64_t dw2[4], ndmin2[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t hdr = hdr_next[j];
-                if (b + 1 < nb && row_ok[j]) hdr_next[j] = __ldg(reinterpret_cast<const uint32_t *>(wrow[j] + (int64_t)(b + 1) * p.blk_bytes));
-                const float dw = f16_bits_to_f32(hdr & 0xffffu), ndmin = -f16_bits_to_f32(hdr >> 16);
-                dw2[j] = pack2f(dw, dw);
-                ndmin2[j] = pack2f(ndmin, ndmin);
-            }
             ok = mbar_wait_abortable<64>(&min_full[buf], par, abort_flag);
             if (!ok) break;
+            // the rows' (d_w, -dmin_w), gathered once per tile and superblock by the copy warp
+            uint64_t dw2[4], ndmin2[4];
+            {
+                const float2 *hp = reinterpret_cast<const float2 *>(smem + kOffHdr + buf * kGemmHdrBytes) + q * 32 + fg;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 h = hp[8 * j];
+                    dw2[j] = pack2f(h.x, h.x);
+                    ndmin2[j] = pack2f(h.y, h.y);
+                }
+            }
             const uint64_t *dap = reinterpret_cast<const uint64_t *>(smem + kOffDa + buf * kGemmDaBytes + part * 128) + fc;
             uint64_t da2[4];
 #pragma unroll
@@ -609,6 +606,35 @@ __global__ void __launch_bounds__(kQ4kThreads, 1) gemm_q4k_kernel(const GemmPara
                 bulk_g2s(smem + kOffMinB + buf * kGemmMinBytes, minb + (int64_t)b * kGemmMinBytes, kGemmMinBytes, &min_full[buf]);
                 bulk_g2s(smem + kOffDa + buf * kGemmDaBytes, dat + (int64_t)b * kGemmDaBytes, kGemmDaBytes, &min_full[buf]);
             }
+            __syncwarp();
+        }
+    } else if (warp == kQ4kEpiWarps + 2) {
+        // ------------------------------ row scales ------------------------------
+        // The block headers (f16 d | f16 dmin) of the tile's 128 weight rows, once per tile and superblock instead of once
+        // per epilogue warp: lane l gathers rows l, l + 32, l + 64, l + 96; the next superblock's loads are in flight
+        // while this one's values go to shared memory as (d_w, -dmin_w).
+        const uint8_t *hrow[4];
+        uint32_t hdr_next[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + lane + 32 * j;
+            hrow[j] = n < p.n ? p.w + (int64_t)n * p.row_bytes : nullptr;
+            hdr_next[j] = hrow[j] ? __ldg(reinterpret_cast<const uint32_t *>(hrow[j])) : 0u;
+        }
+        bool ok = true;
+        for (int b = 0; b < nb && ok; ++b) {
+            const int buf = b & 1;
+            if (b >= 2) ok = mbar_wait_abortable<32>(&acc_empty[buf], ((b >> 1) - 1) & 1, abort_flag);  // the epilogue of b-2 has read its scales
+            if (!ok) break;
+            float2 *hp = reinterpret_cast<float2 *>(smem + kOffHdr + buf * kGemmHdrBytes);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t hdr = hdr_next[j];
+                if (b + 1 < nb && hrow[j]) hdr_next[j] = __ldg(reinterpret_cast<const uint32_t *>(hrow[j] + (int64_t)(b + 1) * p.blk_bytes));
+                hp[lane + 32 * j] = make_float2(f16_bits_to_f32(hdr & 0xffffu), -f16_bits_to_f32(hdr >> 16));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&min_full[buf]);
             __syncwarp();
         }
     } else if (warp == kQ4kEpiWarps + 1) {
