@@ -33,9 +33,10 @@
 
 namespace lloom {
 
-template <int GROUP_K, int PLANES, int BM, int EPI_WARPS = 8>
+template <int GROUP_K, int PLANES, int BM>
 struct PlanesCfg {
-    static constexpr int kEpiWarps = EPI_WARPS;        // 8 or 16: BM / (EPI_WARPS / 4) accumulator columns per warp
+    static constexpr int kEpiWarps = 8;                // BM / 2 accumulator columns per warp (sixteen warps of BM / 4
+                                                       // columns measured 1.6x slower on the 32-of-K formats)
     static constexpr int kGroupK = GROUP_K;            // K elements per accumulator drain
     static constexpr int kPlanes = PLANES;             // f16 images per weight element
     static constexpr int kBM = BM;                     // activation rows per tile (UMMA N): 128 or 256
@@ -59,8 +60,7 @@ struct PlanesCfg {
     static constexpr int kDwSlotBytes = kSmemW ? kDaGroups * kGemmBN * 4 : 0;
     // BM = 256: 128 running sums per epilogue thread; three whole warpgroups, so that the two epilogue warpgroups can
     // take registers from the third (setmaxnreg)
-    static constexpr int kThreads = BM == 256 ? 384 : 32 * (EPI_WARPS + 3);  // epilogue warps + operand copies + MMA issuer + scale copies
-    static_assert(EPI_WARPS == 8 || (EPI_WARPS == 16 && BM == 128), "epilogue warps");
+    static constexpr int kThreads = BM == 256 ? 384 : 32 * (kEpiWarps + 3);  // epilogue warps + operand copies + MMA issuer + scale copies
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int kOffA = 0;
     static constexpr int kOffB = kOffA + kStages * kStageABytes;
@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         if (Cfg::kBM == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
         constexpr int kCW = Cfg::kBM / (Cfg::kEpiWarps / 4);  // columns per warp
         const int q = warp & 3, half = warp >> 2;
-        if (Cfg::kSmemW && kCW == 64) {
+        if (Cfg::kSmemW) {
             // A drain every 32 of K: the scales, not the sums, set the cost.  With a tensor-memory lane per thread every
             // thread would fetch all 64 activation scales of its columns for every group (the same words in all 32
             // lanes, 64 shared-memory wavefronts per warp and group); in the accumulator-fragment layout a thread
@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
         for (int j = 0; j < kCW / 2; ++j) out2[j] = 0ull;
         // group >= 256 of K: the row's weight scale of the next group is fetched while this group is drained
         unsigned short hdr_nxt = 0;
-        if (!Cfg::kSmemW && row_ok) hdr_nxt = __ldg(reinterpret_cast<const unsigned short *>(wrow));
+        if (row_ok) hdr_nxt = __ldg(reinterpret_cast<const unsigned short *>(wrow));
         bool ok = true;
         for (int g = 0; g < ngroups && ok; ++g) {
             const int buf = g % Cfg::kAccBufs;
@@ -464,14 +464,9 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
             const int slot_i = g / Cfg::kDaGroups, in_slot = g % Cfg::kDaGroups, slot = slot_i % Cfg::kDaSlots;
             if (in_slot == 0) ok = mbar_wait_abortable<64>(&da_full[slot], (slot_i / Cfg::kDaSlots) & 1, abort_flag);
             if (!ok) break;
-            float dw;
-            if (Cfg::kSmemW) {
-                dw = *reinterpret_cast<const float *>(smem + Cfg::kOffDw + slot * Cfg::kDwSlotBytes + (in_slot * kGemmBN + r) * 4);
-            } else {
-                dw = f16_bits_to_f32(hdr_nxt);
-                if (row_ok && g + 1 < ngroups)
-                    hdr_nxt = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)(g + 1) * p.scale_stride));
-            }
+            const float dw = f16_bits_to_f32(hdr_nxt);
+            if (row_ok && g + 1 < ngroups)
+                hdr_nxt = __ldg(reinterpret_cast<const unsigned short *>(wrow + (int64_t)(g + 1) * p.scale_stride));
             const uint64_t dw2 = pack2f(dw, dw);
             ok = mbar_wait_abortable<64>(&acc_full[buf], par, abort_flag);
             if (!ok) break;
@@ -480,29 +475,6 @@ __global__ void __launch_bounds__(Cfg::kThreads, 1) gemm_planes_kernel(const Pla
             // the activation scales of this warp's columns, as f32 pairs, times the weight scale: (d_a * d_w)
             const ulonglong2 *dap = reinterpret_cast<const ulonglong2 *>(smem + Cfg::kOffDa + slot * Cfg::kDaSlotBytes +
                                                                          in_slot * Cfg::kDaBytes + half * kCW * 4);
-            if (kCW == 32) {  // sixteen epilogue warps: one load of 32 columns
-                uint32_t va[32];
-                tmem_ld32(t_main, va);
-                uint64_t d2[16];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const ulonglong2 t = dap[j];
-                    d2[2 * j] = mul_f32x2(t.x, dw2);
-                    d2[2 * j + 1] = mul_f32x2(t.y, dw2);
-                }
-                tmem_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                if (in_slot == Cfg::kDaGroups - 1 || g == ngroups - 1) {
-                    fence_proxy_async();  // as below: the slot's next writer is a bulk copy
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&da_empty[slot]);
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    out2[j] = fma_f32x2(d2[j], (uint64_t)va[2 * j] | ((uint64_t)va[2 * j + 1] << 32), out2[j]);
-            }
 #pragma unroll
             for (int c = 0; c < kCW / 64; ++c) {  // 64 columns at a time: two loads in flight
                 uint32_t va[32], vb[32];
