@@ -23,10 +23,14 @@
 //                        re-unpacking its 128 weight rows on CUDA cores beside the MMAs
 //   gemm_q4k_kernel      one CTA per 128 x 128 output tile; all operands arrive as ready-made shared-memory
 //                        images (128-byte-swizzled K-major UMMA layout) by bulk copies.  Warp roles:
-//                          warps 0-15 epilogue: tcgen05.ld -> f32x2 FMAs; warp w reads TMEM lanes 32*(w%4)..,
-//                                     columns 32*(w/4)..
+//                          warps 0-15 epilogue: tcgen05.ld in the MMA fragment layout -> f32x2 FMAs; warp w reads
+//                                     TMEM lanes 32*(w%4).., columns 32*(w/4)..
 //                          warp 16    bulk-copy (TMA engine) producer
 //                          warp 17    MMA issuer (one elected lane): 8 x tcgen05.mma.kind::f16 (K = 16) per stage
+//                          warp 18    the tile's 128 row headers (d, dmin) per superblock -> shared memory
+// An MMA reads its 8 KB of operands from shared memory in 65 cycles and the bulk copies write the same bytes first:
+// the shared-memory port, not the tensor pipe, bounds this tile shape, so everything else is kept off that port
+// (row headers gathered once per tile, activation scales loaded once per fragment column pair).
 // All mbarrier waits are bounded and abortable; on a time-out the status word is set, every role
 // leaves its loop, and tensor memory is still released.
 #pragma once
