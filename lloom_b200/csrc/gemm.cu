@@ -141,7 +141,10 @@ cudaError_t gemm_weight_image_build(int w_dtype, const void *w, int64_t n, int64
     return build_image(w_dtype, (const uint8_t *)w, n, k, (uint8_t *)image, stream);
 }
 
-bool gemm_takes_f32(int w_dtype) { return w_dtype == LLOOM_Q4_K || w_dtype == LLOOM_Q5_K; }
+bool gemm_takes_f32(int w_dtype) {
+    return w_dtype == LLOOM_Q4_K || w_dtype == LLOOM_Q5_K || w_dtype == LLOOM_Q6_K || w_dtype == LLOOM_Q8_0 || w_dtype == LLOOM_Q4_0 ||
+           w_dtype == LLOOM_Q5_0;
+}
 
 cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image, const void *act, const float *x, float *y,
                          int64_t m, int64_t n, int64_t k, int64_t ldy, void *scratch, cudaStream_t stream) {
@@ -156,6 +159,13 @@ cudaError_t gemm_forward(int w_dtype, const void *w_blocks, const void *w_image,
         gemm_prep_f32_kernel<<<(unsigned)(mt * kGemmBM * (k / 256) / 8), 256, 0, stream>>>(x, (int)m, (int)k, act_img);
     } else if (q4k_frame) {
         gemm_prep_kernel<<<(unsigned)(mt * (k / 256) * 4), 256, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
+    } else if (q8_0_frame && x) {
+        planes_prep_f32_kernel<true, CfgQ8_0::kBM><<<(unsigned)(mt * CfgQ8_0::kBM * ((k + 255) / 256) / 8), 256, 0, stream>>>(x, (int)m, (int)k, act_img);
+    } else if (w_dtype == LLOOM_Q6_K && x) {
+        if (q6k_bm(m) == CfgQ6K::kBM)
+            planes_prep_f32_kernel<false, CfgQ6K::kBM><<<(unsigned)(mt * CfgQ6K::kBM * (k / 256) / 8), 256, 0, stream>>>(x, (int)m, (int)k, act_img);
+        else
+            planes_prep_f32_kernel<false, CfgQ6KSmall::kBM><<<(unsigned)(mt * CfgQ6KSmall::kBM * (k / 256) / 8), 256, 0, stream>>>(x, (int)m, (int)k, act_img);
     } else if (q8_0_frame) {
         planes_prep_kernel<true, CfgQ8_0::kBM><<<(unsigned)(mt * (k / 64)), CfgQ8_0::kBM, 0, stream>>>((const uint8_t *)act, (int)m, (int)k, act_img);
     } else if (w_dtype == LLOOM_Q6_K) {

@@ -151,6 +151,51 @@ __global__ void __launch_bounds__(BM) planes_prep_kernel(const uint8_t *__restri
     }
 }
 
+// f32 activations -> the same B image + scale plane in one pass (the forward entries: no canonical blocks in between).
+// One warp per (padded activation row, 256-element span of K), lane l holding elements 8l .. 8l + 7 of the span, i.e.
+// one 16-byte chunk of the image; the quantizers are the warp functions of the stand-alone quantizer kernels, so the
+// codes and scales are those of the canonical blocks bit for bit.  ACT_Q8_0: eight 32-element blocks per span (four
+// lanes each; k may end in the middle of a span); else one Q8_K block.
+template <bool ACT_Q8_0, int BM>
+__global__ void __launch_bounds__(256) planes_prep_f32_kernel(const float *__restrict__ x, int m, int k, uint8_t *__restrict__ scratch) {
+    const int spans = (k + 255) / 256, atoms = k / 64;
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (padded row, span)
+    const int64_t prow = item / spans;
+    const int sp = (int)(item % spans);
+    const int64_t mt = prow / BM;
+    const int t = (int)(prow % BM);
+    if (mt >= (m + BM - 1) / BM) return;  // whole warp
+    const int group_k = ACT_Q8_0 ? 32 : 256;
+    const PlanesActLayout lay = planes_act_layout(m, k, group_k, BM);
+    const int e0 = sp * 256 + lane * 8;      // first of the lane's elements
+    const bool in_k = e0 < k;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    if (prow < m && in_k) load8(x + prow * k + e0, v);  // rows of the last tile past m stay zero
+    uint32_t q_lo = 0, q_hi = 0;
+    float *dat = reinterpret_cast<float *>(scratch + lay.dat) + mt * (k / group_k) * BM;
+    if (ACT_Q8_0) {
+        unsigned short d16;
+        q8_0_quantize_quad(v, q_lo, q_hi, d16);
+        if (in_k && (lane & 3) == 0) dat[(int64_t)(sp * 8 + (lane >> 2)) * BM + t] = f16_bits_to_f32(d16);
+    } else {
+        float d;
+        int sum16;
+        q8k_quantize_warp(v, lane, q_lo, q_hi, d, sum16);
+        if (lane == 0) dat[(int64_t)sp * BM + t] = d;
+    }
+    if (!in_k) return;
+    auto cvt2 = [](uint32_t w, int sh) -> uint32_t {
+        const __half2 h = __floats2half2_rn((float)(int)(int8_t)(w >> sh), (float)(int)(int8_t)(w >> (sh + 8)));
+        return *reinterpret_cast<const uint32_t *>(&h);
+    };
+    const int atom = sp * 4 + (lane >> 3), e = (lane & 7) * 8;
+    uint8_t *img = scratch + lay.bimg + (mt * atoms + atom) * (int64_t)(BM * 128);
+    *reinterpret_cast<uint4 *>(img + sw128_offset(t, e)) = make_uint4(cvt2(q_lo, 0), cvt2(q_lo, 16), cvt2(q_hi, 0), cvt2(q_hi, 16));
+}
+
 // Q8_0 weight blocks -> A image (one plane: the codes as f16).  One CTA per (n-tile, 64-element atom), one thread
 // per weight row; rows past n are zero.  `row0` is the first row of the image's slab within the matrix.
 __global__ void __launch_bounds__(128) planes_expand_q8_0_kernel(const uint8_t *__restrict__ w, int64_t row0, int n_end,

@@ -455,11 +455,14 @@ def test_gemm_q8_0_q6k_tensor_core_path(dev, oracle, dt, n, k, m):
     assert Q.device_status() == 0
 
 
-@pytest.mark.parametrize("dt,n,k,m", [(12, 520, 2048, 70), (12, 300, 1024, 300), (13, 200, 512, 9), (14, 300, 1024, 40)])
+@pytest.mark.parametrize("dt,n,k,m", [(12, 520, 2048, 70), (12, 300, 1024, 300), (13, 200, 512, 9), (14, 300, 1024, 40),
+                                      (14, 200, 2048, 300), (8, 300, 1024, 70), (8, 200, 1152, 300), (2, 200, 640, 40),
+                                      (6, 130, 384, 9)])
 def test_prefill_forward_equals_quantizer_plus_gemm(dev, oracle, dt, n, k, m):
-    """The forward entry of the Q4_K / Q5_K prefill quantizes the activations in the pass that builds the GEMM's
-    operand images; the result equals the explicit route -- lloom_b200_quantize_act, then lloom_b200_gemm on the
-    canonical blocks -- bit for bit (as it does for the formats whose forward takes that route itself)."""
+    """The forward entry of the prefill quantizes the activations in the pass that builds the GEMM's operand images;
+    the result equals the explicit route -- lloom_b200_quantize_act, then lloom_b200_gemm on the canonical blocks --
+    bit for bit (Q8_K activations for the K-quants; Q8_0 activations, with k ending in the middle of a 256-element
+    span, for the 32-element formats)."""
     import lloom_b200 as lb
     from lloom_b200 import quantized as Q
 
